@@ -1,0 +1,113 @@
+/*
+ * o1d — oriented 1D depthwise convolution for NVIDIA B200 (sm_100a).  C ABI.
+ *
+ * This is the boundary a binding of the reference project would call instead of its
+ * JIT-compiled extension modules.  Every entry point
+ *   - takes plain pointers and sizes (no torch types),
+ *   - works on CALLER-ALLOCATED device buffers, allocates nothing and never
+ *     synchronises the device,
+ *   - launches on the CUDA stream passed as `stream` (a cudaStream_t; NULL = default),
+ *   - returns an int status (O1D_OK or an O1D_ERR_* code; see o1d_strerror()).
+ *
+ * Operator definition (reference: models/dwoconv1d_reference/kernels/kernels.cpp:20-129).
+ * For channel c with angle theta[c], tap k in [0,K), pad = K/2, j = k - pad:
+ *     dh[c,k] = (int)(-sinf(theta[c]) * j),   dw[c,k] = (int)(cosf(theta[c]) * j)
+ *     y [n,c,p,q] = bias[c] + sum_k w'[c,k] * x[n,c,p*s+dh, q*s+dw]       (zero outside)
+ *     dx[n,c,h,w] = sum_k w'[c,k] * dy[n,c,(h-dh)/s,(w-dw)/s]   (divisible, in range)
+ *     dw[c,k]     = sum_{n,p,q} x[n,c,p*s+dh, q*s+dw] * dy[n,c,p,q];   db[c] = sum dy
+ * with w' = w + (k == pad) when add_identity is set (the reference's `resid`,
+ * models/dwoconv1d/dwoconv1d.py:22-23,136-141).  H, W are always the INPUT extents;
+ * the output extents are P = ceil(H/s), Q = ceil(W/s) (the reference's forward()
+ * requires divisibility, kernels.cu:19-20; its forward_safe() pads and crops to the
+ * same ceil sizes, dwoconv1d.py:154-187).
+ *
+ * Tensors x, y, dy, dx are fp32 or bf16 (`dtype`), NCHW or NHWC contiguous (`layout`).
+ * w [C,K], bias [C], dw [C,K], db [C] are always fp32; accumulation is fp32.
+ */
+#ifndef O1D_H_
+#define O1D_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define O1D_ABI_VERSION 1
+
+enum {
+    O1D_OK = 0,
+    O1D_ERR_INVALID = 1,      /* null pointer, non-positive size, even K, bad enum ...   */
+    O1D_ERR_UNSUPPORTED = 2,  /* valid request this build has no kernel for              */
+    O1D_ERR_CUDA = 3,         /* a CUDA call or launch failed; see o1d_last_error()      */
+    O1D_ERR_WORKSPACE = 4,    /* workspace pointer missing or too small                  */
+    O1D_ERR_PLAN = 5          /* plan blob does not match C / K or is corrupt            */
+};
+
+enum { O1D_NCHW = 0, O1D_NHWC = 1 };
+enum { O1D_F32 = 0, O1D_BF16 = 1 };
+
+/* Library identification.  (No counterpart in the reference: its modules are found by
+ * name in the torch extension cache, models/dwoconv1d/dwoconv1d_kernel.py:76-90.) */
+int o1d_abi_version(void);
+const char *o1d_strerror(int status);
+/* Text of the last CUDA failure seen by the calling thread ("" if none). */
+const char *o1d_last_error(void);
+
+/* Rasterised tap offsets of C channels, computed on the host exactly as the reference's
+ * CPU loops do (kernels.cpp:37,43-44).  theta_host: C floats (radians, fp32);
+ * dh, dw: C*K int8 each.  Requires K odd, K <= 255. */
+int o1d_offsets(const float *theta_host, int C, int K, int8_t *dh, int8_t *dw);
+
+/* A "plan" is the per-layer tap table in the form the kernels consume: channels with
+ * identical rasterised lines share one orientation class.  It replaces the per-thread
+ * sincosf() + float->int conversion the reference kernels redo for every tap of every
+ * output (models/dwoconv1d/kernels/kernels.h:239-240,285).  The caller allocates
+ * o1d_plan_bytes() bytes on the host, fills them with o1d_plan_build(), and uploads a
+ * byte-for-byte copy to the device; the operators take both pointers (the host copy
+ * steers kernel selection, the device copy is read by the kernels). */
+size_t o1d_plan_bytes(int C, int K);
+int o1d_plan_build(const float *theta_host, int C, int K, void *plan_host);
+/* Number of distinct orientation classes in a built plan (negative on a bad blob). */
+int o1d_plan_num_classes(const void *plan_host);
+
+/* Forward.  Replaces fprop(x, w, theta) of the reference's extension module
+ * (models/dwoconv1d/kernels/kernels.cu:15-27, kernels.h:207-310; specialized:
+ * models/dwoconv1d_specialized/kernels/kernels.cu:17-30) together with the separate
+ * bias add and w+resid passes of its Python wrapper (dwoconv1d.py:22-23,34-35).
+ * bias may be NULL. */
+int o1d_fprop(const void *x, const float *w, const float *bias,
+              const void *plan_host, const void *plan_dev, void *y,
+              int N, int H, int W, int C, int K, int stride,
+              int layout, int dtype, int add_identity, void *stream);
+
+/* Input gradient.  Replaces dgrad(dy, w, theta) (kernels.cu:29-40, kernels.h:312-399).
+ * dy has extents ceil(H/s) x ceil(W/s); dx has extents H x W. */
+int o1d_dgrad(const void *dy, const float *w,
+              const void *plan_host, const void *plan_dev, void *dx,
+              int N, int H, int W, int C, int K, int stride,
+              int layout, int dtype, int add_identity, void *stream);
+
+/* Weight gradient (and bias gradient when db != NULL).  Replaces wgrad(dy, x, theta)
+ * (kernels.cu:42-54, kernels.h:402-518) and the separate dy.sum([0,2,3]) pass
+ * (dwoconv1d.py:66-67).  Deterministic: per-block partial sums go to `workspace`
+ * (o1d_wgrad_workspace_bytes() bytes, caller-allocated, contents need no
+ * initialisation) and are combined in a fixed order; no atomics. */
+size_t o1d_wgrad_workspace_bytes(int N, int H, int W, int C, int K, int stride,
+                                 int layout, int dtype);
+int o1d_wgrad(const void *dy, const void *x,
+              const void *plan_host, const void *plan_dev,
+              float *dw, float *db, void *workspace, size_t workspace_bytes,
+              int N, int H, int W, int C, int K, int stride,
+              int layout, int dtype, void *stream);
+
+/* Batched 2-D transpose [n, a, b] -> [n, b, a].  Replaces nhwc_to_nchw / nchw_to_nhwc
+ * (kernels.cu:56-68, nhwc_utils.h:46-110): NHWC->NCHW is (n=N, a=H*W, b=C),
+ * NCHW->NHWC is (n=N, a=C, b=H*W). */
+int o1d_transpose(const void *in, void *out, int n, int a, int b, int dtype, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* O1D_H_ */

@@ -1,0 +1,75 @@
+"""ctypes binding of libo1d.so (declared in include/o1d.h).
+
+There is no fallback: if the shared library is missing and cannot be built, importing
+this module raises.  ctypes releases the GIL for the duration of each call.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from . import build as _build
+
+_c_int = ctypes.c_int
+_c_void_p = ctypes.c_void_p
+_c_size_t = ctypes.c_size_t
+_f32p = ctypes.POINTER(ctypes.c_float)
+_i8p = ctypes.POINTER(ctypes.c_int8)
+
+# name -> (restype, argtypes); one entry per declaration in include/o1d.h
+SIGNATURES = {
+    "o1d_abi_version": (_c_int, []),
+    "o1d_strerror": (ctypes.c_char_p, [_c_int]),
+    "o1d_last_error": (ctypes.c_char_p, []),
+    "o1d_offsets": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p]),
+    "o1d_plan_bytes": (_c_size_t, [_c_int, _c_int]),
+    "o1d_plan_build": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p]),
+    "o1d_plan_num_classes": (_c_int, [_c_void_p]),
+    "o1d_fprop": (_c_int, [_c_void_p] * 6 + [_c_int] * 9 + [_c_void_p]),
+    "o1d_dgrad": (_c_int, [_c_void_p] * 5 + [_c_int] * 9 + [_c_void_p]),
+    "o1d_wgrad_workspace_bytes": (_c_size_t, [_c_int] * 8),
+    "o1d_wgrad": (_c_int, [_c_void_p] * 7 + [_c_size_t] + [_c_int] * 8 + [_c_void_p]),
+    "o1d_transpose": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p]),
+}
+
+ABI_VERSION = 1
+NCHW, NHWC = 0, 1
+F32, BF16 = 0, 1
+
+
+class O1dError(RuntimeError):
+    pass
+
+
+def _load() -> ctypes.CDLL:
+    path = _build.LIB
+    if not os.path.exists(path):
+        try:
+            _build.build()
+        except Exception as e:  # no CPU path exists: fail loudly
+            raise RuntimeError(
+                f"libo1d.so is missing and could not be built ({e}); "
+                "run `python -m oriented1d_b200.build`") from e
+    lib = ctypes.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)          # AttributeError if the library lacks a symbol
+        fn.restype, fn.argtypes = res, args
+    if lib.o1d_abi_version() != ABI_VERSION:
+        raise RuntimeError(f"libo1d.so has ABI {lib.o1d_abi_version()}, binding expects {ABI_VERSION}")
+    return lib
+
+
+lib = _load()
+
+
+def check(status: int, what: str = "o1d") -> None:
+    """Turn a non-zero status into an exception (ValueError for bad arguments,
+    O1dError otherwise), like the reference's TORCH_CHECK -> RuntimeError."""
+    if status == 0:
+        return
+    msg = lib.o1d_strerror(status).decode()
+    if status == 3:
+        msg += ": " + lib.o1d_last_error().decode()
+    if status == 1:
+        raise ValueError(f"{what}: {msg}")
+    raise O1dError(f"{what}: {msg}")

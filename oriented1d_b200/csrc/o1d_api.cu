@@ -1,0 +1,312 @@
+// C ABI of libo1d (see include/o1d.h): argument checks, plan building, kernel selection,
+// launches.  No allocation, no synchronisation, no global mutable state besides a
+// per-device attribute cache and a thread-local error string.
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <vector>
+
+#include "o1d_common.cuh"
+#include "o1d_generic.cuh"
+#include "o1d_transpose.cuh"
+
+using namespace o1d;
+
+namespace {
+
+thread_local char g_err[256] = "";
+
+int cuda_fail(cudaError_t e, const char *what) {
+    snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
+    return O1D_ERR_CUDA;
+}
+#define O1D_CUDA(call)                                              \
+    do {                                                            \
+        cudaError_t e_ = (call);                                    \
+        if (e_ != cudaSuccess) return cuda_fail(e_, #call);         \
+    } while (0)
+
+struct DeviceInfo { int sms; int smem_optin; };
+
+// Attributes of the current device, queried once per device.
+int device_info(DeviceInfo *out) {
+    static DeviceInfo cache[64];
+    static bool have[64];
+    int dev = 0;
+    O1D_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return O1D_ERR_UNSUPPORTED;
+    if (!have[dev]) {
+        DeviceInfo d;
+        O1D_CUDA(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev));
+        O1D_CUDA(cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        cache[dev] = d;
+        have[dev] = true;
+    }
+    *out = cache[dev];
+    return O1D_OK;
+}
+
+bool bad_common(int N, int H, int W, int C, int K, int stride, int layout, int dtype) {
+    return N <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0 || (K & 1) == 0 || K > 255 || stride <= 0 ||
+           (layout != O1D_NCHW && layout != O1D_NHWC) || (dtype != O1D_F32 && dtype != O1D_BF16);
+}
+
+int check_plan(const void *plan_host, int C, int K, PlanHeader *h) {
+    if (!plan_host) return O1D_ERR_INVALID;
+    memcpy(h, plan_host, sizeof(PlanHeader));
+    if (h->magic != kPlanMagic || h->C != C || h->K != K || h->ncls <= 0 || h->ncls > C) return O1D_ERR_PLAN;
+    return O1D_OK;
+}
+
+// The reference's rasterisation, kernels.cpp:37,43-44.
+void raster(float theta, int K, int8_t *dh, int8_t *dw) {
+    const int pad = K / 2;
+    const float sin_ = sinf(theta), cos_ = cosf(theta);
+    for (int k = 0; k < K; k++) {
+        dh[k] = (int8_t)(int)(-sin_ * (k - pad));
+        dw[k] = (int8_t)(int)(cos_ * (k - pad));
+    }
+}
+
+int grid_for(int64_t total, int threads, const DeviceInfo &d, int waves) {
+    int64_t blocks = (total + threads - 1) / threads;
+    int64_t cap = (int64_t)d.sms * waves;
+    return (int)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+// ---- generic launches --------------------------------------------------------------
+
+template <typename T, int LAYOUT>
+int launch_generic_fprop(const void *x, const float *w, const float *bias, const PlanHeader &ph,
+                         const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride,
+                         int add_identity, cudaStream_t st, const DeviceInfo &d) {
+    const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
+    PlanView pv = plan_view(plan_dev, ph);
+    const int tap_bytes = ph.ncls * K * 2;
+    const int staged = tap_bytes <= kTapSmemBudget;
+    const int grid = grid_for((int64_t)N * P * Q * C, kGenericThreads, d, 16);
+    generic_fprop_kernel<T, LAYOUT><<<grid, kGenericThreads, staged ? tap_bytes : 0, st>>>(
+        (const T *)x, w, bias, pv.cls, pv.taps, ph.ncls, staged, (T *)y, N, H, W, C, K, stride, P, Q,
+        add_identity);
+    O1D_CUDA(cudaGetLastError());
+    return O1D_OK;
+}
+
+template <typename T, int LAYOUT>
+int launch_generic_dgrad(const void *dy, const float *w, const PlanHeader &ph, const void *plan_dev,
+                         void *dx, int N, int H, int W, int C, int K, int stride, int add_identity,
+                         cudaStream_t st, const DeviceInfo &d) {
+    const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
+    PlanView pv = plan_view(plan_dev, ph);
+    const int tap_bytes = ph.ncls * K * 2;
+    const int staged = tap_bytes <= kTapSmemBudget;
+    const int grid = grid_for((int64_t)N * H * W * C, kGenericThreads, d, 16);
+    generic_dgrad_kernel<T, LAYOUT><<<grid, kGenericThreads, staged ? tap_bytes : 0, st>>>(
+        (const T *)dy, w, pv.cls, pv.taps, ph.ncls, staged, (T *)dx, N, H, W, C, K, stride, P, Q,
+        add_identity);
+    O1D_CUDA(cudaGetLastError());
+    return O1D_OK;
+}
+
+// Number of output slices of the general weight-gradient: enough blocks for ~4 per SM,
+// never fewer than 64 outputs per slice.  Depends on the shape only (B200 has 148 SMs),
+// so the summation order — and the result, bit for bit — is reproducible.
+int generic_wgrad_slices(int N, int P, int Q, int C, int layout) {
+    const int cl = layout == O1D_NHWC ? 32 : 1;
+    const int chunks = ceil_div(C, cl);
+    const int64_t npq = (int64_t)N * P * Q;
+    int64_t s = (4 * 148 + chunks - 1) / chunks;
+    const int64_t cap = (npq + 63) / 64;
+    if (s > cap) s = cap;
+    if (s < 1) s = 1;
+    return (int)s;
+}
+
+template <typename T, int LAYOUT>
+int launch_generic_wgrad(const void *dy, const void *x, const PlanHeader &ph, const void *plan_dev,
+                         float *dw, float *db, float *partial, int N, int H, int W, int C, int K,
+                         int stride, cudaStream_t st) {
+    const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
+    PlanView pv = plan_view(plan_dev, ph);
+    const int slices = generic_wgrad_slices(N, P, Q, C, LAYOUT);
+    dim3 grid(ceil_div(C, WgradShape<LAYOUT>::CL), slices);
+    generic_wgrad_partial_kernel<T, LAYOUT><<<grid, kGenericThreads, 0, st>>>(
+        (const T *)dy, (const T *)x, pv.cls, pv.taps, partial, N, H, W, C, K, stride, P, Q, slices);
+    O1D_CUDA(cudaGetLastError());
+    const int tot = C * (K + 1);
+    wgrad_final_kernel<<<ceil_div(tot, 256), 256, 0, st>>>(partial, dw, db, C, K, slices);
+    O1D_CUDA(cudaGetLastError());
+    return O1D_OK;
+}
+
+#define O1D_DISPATCH(fn, ...)                                                                    \
+    (dtype == O1D_F32                                                                            \
+         ? (layout == O1D_NHWC ? fn<float, O1D_NHWC>(__VA_ARGS__) : fn<float, O1D_NCHW>(__VA_ARGS__)) \
+         : (layout == O1D_NHWC ? fn<__nv_bfloat16, O1D_NHWC>(__VA_ARGS__)                        \
+                               : fn<__nv_bfloat16, O1D_NCHW>(__VA_ARGS__)))
+
+}  // namespace
+
+extern "C" {
+
+int o1d_abi_version(void) { return O1D_ABI_VERSION; }
+
+const char *o1d_strerror(int status) {
+    switch (status) {
+        case O1D_OK: return "ok";
+        case O1D_ERR_INVALID: return "invalid argument";
+        case O1D_ERR_UNSUPPORTED: return "unsupported configuration";
+        case O1D_ERR_CUDA: return "CUDA error";
+        case O1D_ERR_WORKSPACE: return "workspace missing or too small";
+        case O1D_ERR_PLAN: return "plan does not match the call";
+        default: return "unknown status";
+    }
+}
+
+const char *o1d_last_error(void) { return g_err; }
+
+int o1d_offsets(const float *theta_host, int C, int K, int8_t *dh, int8_t *dw) {
+    if (!theta_host || !dh || !dw || C <= 0 || K <= 0 || (K & 1) == 0 || K > 255) return O1D_ERR_INVALID;
+    for (int c = 0; c < C; c++) raster(theta_host[c], K, dh + (size_t)c * K, dw + (size_t)c * K);
+    return O1D_OK;
+}
+
+// Worst case: every channel its own class.
+size_t o1d_plan_bytes(int C, int K) {
+    if (C <= 0 || K <= 0) return 0;
+    return sizeof(PlanHeader) + align16((uint32_t)C * 2) + align16((uint32_t)C * K * 2) + align16((uint32_t)C);
+}
+
+int o1d_plan_build(const float *theta_host, int C, int K, void *plan_host) {
+    if (!theta_host || !plan_host || C <= 0 || C > 65535 || K <= 0 || (K & 1) == 0 || K > 255)
+        return O1D_ERR_INVALID;
+    std::vector<int8_t> line((size_t)2 * K), dh(K), dw(K);
+    std::vector<int8_t> tables;   // ncls * K * 2
+    std::vector<uint16_t> cls(C);
+    int ncls = 0, max_dh = 0, max_dw = 0;
+    for (int c = 0; c < C; c++) {
+        // channels with bit-identical angles share a class without re-rasterising
+        if (c > 0 && memcmp(theta_host + c, theta_host + c - 1, sizeof(float)) == 0) {
+            cls[c] = cls[c - 1];
+            continue;
+        }
+        raster(theta_host[c], K, dh.data(), dw.data());
+        for (int k = 0; k < K; k++) { line[2 * k] = dh[k]; line[2 * k + 1] = dw[k]; }
+        int found = -1;
+        for (int i = 0; i < ncls && found < 0; i++)
+            if (memcmp(tables.data() + (size_t)i * 2 * K, line.data(), 2 * K) == 0) found = i;
+        if (found < 0) {
+            found = ncls++;
+            tables.insert(tables.end(), line.begin(), line.end());
+            for (int k = 0; k < K; k++) {
+                if (abs(dh[k]) > max_dh) max_dh = abs(dh[k]);
+                if (abs(dw[k]) > max_dw) max_dw = abs(dw[k]);
+            }
+        }
+        cls[c] = (uint16_t)found;
+    }
+    PlanHeader h;
+    memset(&h, 0, sizeof(h));
+    h.magic = kPlanMagic; h.C = C; h.K = K; h.ncls = ncls; h.max_dh = max_dh; h.max_dw = max_dw;
+    h.cls_off = sizeof(PlanHeader);
+    h.taps_off = h.cls_off + align16((uint32_t)C * 2);
+    h.canon_off = h.taps_off + align16((uint32_t)ncls * K * 2);
+    h.total_bytes = h.canon_off + align16((uint32_t)ncls);
+    char *b = static_cast<char *>(plan_host);
+    memset(b, 0, o1d_plan_bytes(C, K));
+    memcpy(b + h.cls_off, cls.data(), (size_t)C * 2);
+    memcpy(b + h.taps_off, tables.data(), tables.size());
+    // canonical orientation of each class: the line of angle i*pi/8 rounded to fp32
+    int all_canon = 1;
+    for (int i = 0; i < ncls; i++) {
+        int8_t canon = -1;
+        for (int o = 0; o < 8 && canon < 0; o++) {
+            raster((float)(o * M_PI / 8.0), K, dh.data(), dw.data());
+            bool same = true;
+            for (int k = 0; k < K && same; k++)
+                same = tables[(size_t)i * 2 * K + 2 * k] == dh[k] && tables[(size_t)i * 2 * K + 2 * k + 1] == dw[k];
+            if (same) canon = (int8_t)o;
+        }
+        b[h.canon_off + i] = canon;
+        if (canon < 0) all_canon = 0;
+    }
+    h.all_canon = all_canon;
+    memcpy(b, &h, sizeof(h));
+    return O1D_OK;
+}
+
+int o1d_plan_num_classes(const void *plan_host) {
+    if (!plan_host) return -1;
+    PlanHeader h;
+    memcpy(&h, plan_host, sizeof(h));
+    return h.magic == kPlanMagic ? h.ncls : -1;
+}
+
+int o1d_fprop(const void *x, const float *w, const float *bias, const void *plan_host,
+              const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride, int layout,
+              int dtype, int add_identity, void *stream) {
+    if (!x || !w || !y || !plan_dev || bad_common(N, H, W, C, K, stride, layout, dtype)) return O1D_ERR_INVALID;
+    PlanHeader ph;
+    int rc = check_plan(plan_host, C, K, &ph);
+    if (rc) return rc;
+    DeviceInfo d;
+    if ((rc = device_info(&d))) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    return O1D_DISPATCH(launch_generic_fprop, x, w, bias, ph, plan_dev, y, N, H, W, C, K, stride,
+                        add_identity, st, d);
+}
+
+int o1d_dgrad(const void *dy, const float *w, const void *plan_host, const void *plan_dev, void *dx,
+              int N, int H, int W, int C, int K, int stride, int layout, int dtype, int add_identity,
+              void *stream) {
+    if (!dy || !w || !dx || !plan_dev || bad_common(N, H, W, C, K, stride, layout, dtype)) return O1D_ERR_INVALID;
+    PlanHeader ph;
+    int rc = check_plan(plan_host, C, K, &ph);
+    if (rc) return rc;
+    DeviceInfo d;
+    if ((rc = device_info(&d))) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    return O1D_DISPATCH(launch_generic_dgrad, dy, w, ph, plan_dev, dx, N, H, W, C, K, stride,
+                        add_identity, st, d);
+}
+
+size_t o1d_wgrad_workspace_bytes(int N, int H, int W, int C, int K, int stride, int layout, int dtype) {
+    if (bad_common(N, H, W, C, K, stride, layout, dtype)) return 0;
+    const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
+    return (size_t)generic_wgrad_slices(N, P, Q, C, layout) * C * (K + 1) * sizeof(float);
+}
+
+int o1d_wgrad(const void *dy, const void *x, const void *plan_host, const void *plan_dev, float *dw,
+              float *db, void *workspace, size_t workspace_bytes, int N, int H, int W, int C, int K,
+              int stride, int layout, int dtype, void *stream) {
+    if (!dy || !x || !dw || !plan_dev || bad_common(N, H, W, C, K, stride, layout, dtype)) return O1D_ERR_INVALID;
+    PlanHeader ph;
+    int rc = check_plan(plan_host, C, K, &ph);
+    if (rc) return rc;
+    if (!workspace || workspace_bytes < o1d_wgrad_workspace_bytes(N, H, W, C, K, stride, layout, dtype))
+        return O1D_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    return O1D_DISPATCH(launch_generic_wgrad, dy, x, ph, plan_dev, dw, db, (float *)workspace, N, H, W,
+                        C, K, stride, st);
+}
+
+int o1d_transpose(const void *in, void *out, int n, int a, int b, int dtype, void *stream) {
+    if (!in || !out || n <= 0 || a <= 0 || b <= 0 || (dtype != O1D_F32 && dtype != O1D_BF16)) return O1D_ERR_INVALID;
+    if (n > 65535) return O1D_ERR_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool al_in = ((uintptr_t)in & 15) == 0, al_out = ((uintptr_t)out & 15) == 0;
+    if (dtype == O1D_F32) {
+        dim3 grid(ceil_div(b, 32), ceil_div(a, 32), n);
+        transpose_kernel<uint32_t><<<grid, kTransposeThreads, 0, st>>>(
+            (const uint32_t *)in, (uint32_t *)out, a, b, al_in && b % 4 == 0, al_out && a % 4 == 0);
+    } else {
+        dim3 grid(ceil_div(b, 64), ceil_div(a, 64), n);
+        transpose_kernel<uint16_t><<<grid, kTransposeThreads, 0, st>>>(
+            (const uint16_t *)in, (uint16_t *)out, a, b, al_in && b % 8 == 0, al_out && a % 8 == 0);
+    }
+    O1D_CUDA(cudaGetLastError());
+    return O1D_OK;
+}
+
+}  // extern "C"

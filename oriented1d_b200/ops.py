@@ -1,0 +1,155 @@
+"""torch-facing wrappers of the C ABI: tensors in, tensors out.
+
+torch is used for device memory (its caching allocator owns every buffer) and for the
+current stream; all arithmetic happens in libo1d.so.  There is no CPU path: every
+function raises on a non-CUDA tensor, as the reference's extension does
+(CHECK_CUDA, models/dwoconv1d/kernels/kernels.cu:11).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import lib, check
+
+_DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"oriented1d_b200 supports float32 and bfloat16 tensors, got {t.dtype}") from None
+
+
+def _need_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("tensor must be a CUDA tensor (oriented1d_b200 has no CPU path)")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def offsets(theta, K: int):
+    """Rasterised tap offsets (dh, dw), int8 arrays [C, K], from fp32 angles
+    (reference rule: models/dwoconv1d_reference/kernels/kernels.cpp:37,43-44)."""
+    th = np.ascontiguousarray(np.asarray(theta, dtype=np.float32).reshape(-1))
+    C = th.shape[0]
+    dh = np.empty((C, K), np.int8)
+    dw = np.empty((C, K), np.int8)
+    check(lib.o1d_offsets(th.ctypes.data, C, K, dh.ctypes.data, dw.ctypes.data), "o1d_offsets")
+    return dh, dw
+
+
+class Plan:
+    """Per-layer tap table (orientation classes) on the host plus one copy per device."""
+
+    def __init__(self, theta, K: int):
+        th = torch.as_tensor(theta).detach().to(device="cpu", dtype=torch.float32).reshape(-1).contiguous()
+        self.C, self.K = int(th.numel()), int(K)
+        nbytes = lib.o1d_plan_bytes(self.C, self.K)
+        if nbytes == 0:
+            raise ValueError("o1d_plan_bytes: invalid C or K")
+        self.host = torch.zeros(nbytes, dtype=torch.uint8)
+        check(lib.o1d_plan_build(th.data_ptr(), self.C, self.K, self.host.data_ptr()), "o1d_plan_build")
+        self.num_classes = lib.o1d_plan_num_classes(self.host.data_ptr())
+        self._dev: dict[torch.device, torch.Tensor] = {}
+
+    def on(self, device: torch.device) -> torch.Tensor:
+        d = self._dev.get(device)
+        if d is None:
+            d = self.host.to(device)
+            self._dev[device] = d
+        return d
+
+
+def _dims(t: torch.Tensor, nhwc: bool):
+    if t.dim() != 4:
+        raise ValueError("expected a 4-D tensor")
+    if nhwc:
+        n, h, w, c = t.shape
+    else:
+        n, c, h, w = t.shape
+    return n, c, h, w
+
+
+def fprop(x, w, bias, plan: Plan, stride: int = 1, nhwc: bool = False, add_identity: bool = False):
+    """y = oriented conv of x.  x: [N,C,H,W] (or [N,H,W,C] if nhwc), contiguous."""
+    _need_cuda(x, w, bias)
+    x = x.contiguous()
+    N, C, H, W = _dims(x, nhwc)
+    K = plan.K
+    w32 = w.detach().reshape(C, K).to(torch.float32).contiguous()
+    b32 = bias.detach().to(torch.float32).contiguous() if bias is not None else None
+    P, Q = -(-H // stride), -(-W // stride)
+    y = torch.empty((N, P, Q, C) if nhwc else (N, C, P, Q), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.o1d_fprop(x.data_ptr(), w32.data_ptr(), b32.data_ptr() if b32 is not None else None,
+                            plan.host.data_ptr(), plan.on(x.device).data_ptr(), y.data_ptr(),
+                            N, H, W, C, K, stride, int(nhwc), _dtype_code(x), int(add_identity),
+                            _stream()), "o1d_fprop")
+    return y
+
+
+def dgrad(dy, w, plan: Plan, H: int, W: int, stride: int = 1, nhwc: bool = False,
+          add_identity: bool = False):
+    """dx [.., H, W ..] from dy [.., ceil(H/s), ceil(W/s) ..]."""
+    _need_cuda(dy, w)
+    dy = dy.contiguous()
+    N, C, P, Q = _dims(dy, nhwc)
+    if P != -(-H // stride) or Q != -(-W // stride):
+        raise ValueError("dy extents do not match ceil(H/stride) x ceil(W/stride)")
+    K = plan.K
+    w32 = w.detach().reshape(C, K).to(torch.float32).contiguous()
+    dx = torch.empty((N, H, W, C) if nhwc else (N, C, H, W), dtype=dy.dtype, device=dy.device)
+    with torch.cuda.device(dy.device):
+        check(lib.o1d_dgrad(dy.data_ptr(), w32.data_ptr(), plan.host.data_ptr(),
+                            plan.on(dy.device).data_ptr(), dx.data_ptr(), N, H, W, C, K, stride,
+                            int(nhwc), _dtype_code(dy), int(add_identity), _stream()), "o1d_dgrad")
+    return dx
+
+
+def wgrad(dy, x, plan: Plan, stride: int = 1, nhwc: bool = False, with_bias: bool = False):
+    """(dw [C,1,1,K] fp32, db [C] fp32 or None).  Deterministic."""
+    _need_cuda(dy, x)
+    dy, x = dy.contiguous(), x.contiguous()
+    if dy.dtype != x.dtype:
+        raise TypeError("dy and x must have the same dtype")
+    N, C, H, W = _dims(x, nhwc)
+    K = plan.K
+    code = _dtype_code(x)
+    dw = torch.empty((C, 1, 1, K), dtype=torch.float32, device=x.device)
+    db = torch.empty((C,), dtype=torch.float32, device=x.device) if with_bias else None
+    nbytes = lib.o1d_wgrad_workspace_bytes(N, H, W, C, K, stride, int(nhwc), code)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.o1d_wgrad(dy.data_ptr(), x.data_ptr(), plan.host.data_ptr(),
+                            plan.on(x.device).data_ptr(), dw.data_ptr(),
+                            db.data_ptr() if db is not None else None, ws.data_ptr(), ws.numel(),
+                            N, H, W, C, K, stride, int(nhwc), code, _stream()), "o1d_wgrad")
+    return dw, db
+
+
+def _transpose(t: torch.Tensor, n: int, a: int, b: int, out_shape):
+    _need_cuda(t)
+    t = t.contiguous()
+    out = torch.empty(out_shape, dtype=t.dtype, device=t.device)
+    with torch.cuda.device(t.device):
+        check(lib.o1d_transpose(t.data_ptr(), out.data_ptr(), n, a, b, _dtype_code(t), _stream()),
+              "o1d_transpose")
+    return out
+
+
+def nhwc_to_nchw(x):
+    """[N,H,W,C] -> [N,C,H,W], contiguous (reference: kernels.cu:56-61)."""
+    N, H, W, C = x.shape
+    return _transpose(x, N, H * W, C, (N, C, H, W))
+
+
+def nchw_to_nhwc(x):
+    """[N,C,H,W] -> [N,H,W,C], contiguous (reference: kernels.cu:63-68)."""
+    N, C, H, W = x.shape
+    return _transpose(x, N, C, H * W, (N, H, W, C))

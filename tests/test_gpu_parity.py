@@ -1,0 +1,259 @@
+"""Parity of the CUDA path (called through the C ABI) with the CPU oracle and with the
+reference's own golden outputs.  Needs a B200: run with `-m gpu`.
+
+Tolerances: fp32  max|a-b|/max|b| <= 1e-5 (fprop, dgrad), 1e-4 (wgrad, reduction order
+differs); bf16  every output within 2 bf16 ulp of the fp32-accumulated result computed
+from the same bf16-rounded inputs."""
+import numpy as np
+import pytest
+import torch
+
+import oriented1d_b200 as o1d
+from oracle import oracle as O
+from tests.util import (TOL_DGRAD, TOL_FPROP, TOL_WGRAD, angle_list, assert_bf16_close, bf16_round,
+                        make_inputs, rel_err)
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _seed(shape):
+    return sum(int(v) * m for v, m in zip(shape[:6], (1000003, 1009, 31, 7, 3, 1)))
+
+
+def _to_dev(a_nchw, nhwc, dtype=torch.float32):
+    t = torch.from_numpy(np.ascontiguousarray(a_nchw))
+    if nhwc:
+        t = t.permute(0, 2, 3, 1).contiguous()
+    return t.to(DEV).to(dtype)
+
+
+def _to_nchw(t, nhwc):
+    t = t.float().cpu()
+    if nhwc:
+        t = t.permute(0, 3, 1, 2)
+    return t.contiguous().numpy()
+
+
+def _golden_cases(golden, prefix):
+    return sorted({k.split("_")[0] for k in golden.files if k.startswith(prefix)})
+
+
+@pytest.mark.parametrize("nhwc", [False, True])
+def test_golden_loops(golden, nhwc):
+    """The reference's own outputs for fprop / dgrad / wgrad."""
+    for name in _golden_cases(golden, "case"):
+        N, C, H, W, K, s = (int(v) for v in golden[name + "_meta"])
+        x, w, th, dy = (golden[f"{name}_{k}"] for k in ("x", "w", "theta", "dy"))
+        plan = o1d.Plan(th, K)
+        wd = torch.from_numpy(w).to(DEV)
+        y = o1d.fprop(_to_dev(x, nhwc), wd, None, plan, s, nhwc)
+        dx = o1d.dgrad(_to_dev(dy, nhwc), wd, plan, H, W, s, nhwc)
+        dw, _ = o1d.wgrad(_to_dev(dy, nhwc), _to_dev(x, nhwc), plan, s, nhwc)
+        assert rel_err(_to_nchw(y, nhwc), golden[name + "_y"]) <= TOL_FPROP, name
+        assert rel_err(_to_nchw(dx, nhwc), golden[name + "_dx"]) <= TOL_DGRAD, name
+        assert rel_err(dw.cpu().numpy(), golden[name + "_dw"]) <= TOL_WGRAD, name
+
+
+def test_golden_module(golden):
+    """Forward + backward of the nn.Module against the reference's autograd function."""
+    for name in _golden_cases(golden, "mod"):
+        N, C, H, W, K, s, nhwc, resid = (int(v) for v in golden[name + "_meta"])
+        g = {k: golden[f"{name}_{k}"] for k in ("x", "w", "theta", "bias", "dy", "y", "dx", "dw", "db")}
+        m = o1d.DepthwiseOrientedConv1d(C, C, K, groups=C, stride=s, padding=K // 2, bias=True,
+                                        angle=[float(a) for a in g["theta"]], nhwc=bool(nhwc),
+                                        resid=bool(resid)).to(DEV)
+        with torch.no_grad():
+            m.weight.copy_(torch.from_numpy(g["w"]))
+            m.bias.copy_(torch.from_numpy(g["bias"]))
+        x = torch.from_numpy(g["x"]).to(DEV).requires_grad_(True)
+        y = m(x)
+        y.backward(torch.from_numpy(g["dy"]).to(DEV))
+        assert rel_err(y.detach().cpu().numpy(), g["y"]) <= TOL_FPROP, name
+        assert rel_err(x.grad.cpu().numpy(), g["dx"]) <= TOL_DGRAD, name
+        assert rel_err(m.weight.grad.cpu().numpy(), g["dw"]) <= TOL_WGRAD, name
+        assert rel_err(m.bias.grad.cpu().numpy(), g["db"]) <= TOL_WGRAD, name
+        assert m.theta.grad is None
+
+
+def test_impulse_response(golden):
+    """x = delta, w[k] = k+1 reproduces the reference's tap table exactly (small integers)."""
+    x = np.zeros((1, 8, 33, 33), np.float32)
+    x[:, :, 16, 16] = 1
+    w = np.tile(np.arange(1, 32, dtype=np.float32), (8, 1)).reshape(8, 1, 1, 31)
+    plan = o1d.Plan(angle_list("rr", 8), 31)
+    for nhwc in (False, True):
+        y = o1d.fprop(_to_dev(x, nhwc), torch.from_numpy(w).to(DEV), None, plan, 1, nhwc)
+        assert np.array_equal(_to_nchw(y, nhwc), golden["impulse_y"])
+
+
+SHAPES = [
+    # N, C, H, W, K, stride, angles
+    (2, 96, 56, 56, 31, 1, "rr"),          # the reference's CPU-runnable configuration
+    (2, 96, 56, 56, 31, 1, "model"),
+    (3, 192, 28, 28, 31, 1, "rr"),
+    (3, 384, 14, 14, 31, 1, "model+"),
+    (4, 768, 7, 7, 31, 1, "rr"),
+    (2, 64, 32, 48, 31, 2, "model"),       # stem-like: stride 2
+    (2, 64, 32, 48, 15, 2, "model+"),
+    (2, 16, 20, 28, 15, 1, "random"),
+    (1, 24, 25, 40, 13, 1, "model+"),      # odd sizes
+    (2, 16, 14, 14, 27, 1, "model"),
+    (1, 40, 9, 5, 7, 1, "random"),
+    (1, 8, 16, 16, 5, 4, "rr"),
+    (1, 3, 5, 70, 63, 1, "random"),        # K wider than the register tap chunk
+    (1, 8, 1, 1, 31, 1, "rr"),             # single pixel
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s[:6])) + s[6])
+@pytest.mark.parametrize("nhwc", [False, True], ids=["nchw", "nhwc"])
+def test_fp32_parity(oracle, shape, nhwc):
+    N, C, H, W, K, s, mode = shape
+    x, w, dy = make_inputs(_seed(shape), N, C, H, W, K, s)
+    th = angle_list(mode, C, seed=C)
+    bias = np.linspace(-1, 1, C).astype(np.float32)
+    plan = o1d.Plan(th, K)
+    wd, bd = torch.from_numpy(w).to(DEV), torch.from_numpy(bias).to(DEV)
+    for resid in (False, True):
+        y = o1d.fprop(_to_dev(x, nhwc), wd, bd, plan, s, nhwc, resid)
+        dx = o1d.dgrad(_to_dev(dy, nhwc), wd, plan, H, W, s, nhwc, resid)
+        ry = O.forward_safe(oracle, x, w, th, bias, s, False, resid)
+        rdx, rdw, rdb = O.backward_safe(oracle, x, w, th, dy, bias, s, False, resid)
+        assert rel_err(_to_nchw(y, nhwc), ry) <= TOL_FPROP
+        assert rel_err(_to_nchw(dx, nhwc), rdx) <= TOL_DGRAD
+    dw, db = o1d.wgrad(_to_dev(dy, nhwc), _to_dev(x, nhwc), plan, s, nhwc, with_bias=True)
+    # anchor for the reduction: the same sum in double precision
+    rdw64 = oracle.wgrad_f64(*_pad_for_stride(dy, x, s), th, K, s)
+    assert rel_err(dw.cpu().numpy(), rdw64) <= TOL_WGRAD
+    assert rel_err(dw.cpu().numpy(), rdw) <= 2 * TOL_WGRAD     # the fp32 loops carry their own error
+    assert rel_err(db.cpu().numpy(), dy.sum(axis=(0, 2, 3), dtype=np.float64)) <= TOL_WGRAD
+
+
+def _pad_for_stride(dy, x, s):
+    """Zero-extend x (and dy) so that H, W divide by s; contributes nothing to the sums."""
+    H, W = x.shape[2], x.shape[3]
+    ph, pw = (-H) % s, (-W) % s
+    xp = np.pad(x, ((0, 0), (0, 0), (0, ph), (0, pw)))
+    return dy, xp
+
+
+@pytest.mark.parametrize("shape", [SHAPES[0], SHAPES[2], SHAPES[4], SHAPES[5], SHAPES[8]],
+                         ids=lambda s: "x".join(map(str, s[:6])) + s[6])
+@pytest.mark.parametrize("nhwc", [False, True], ids=["nchw", "nhwc"])
+def test_bf16_parity(oracle, shape, nhwc):
+    N, C, H, W, K, s, mode = shape
+    x, w, dy = make_inputs(_seed(shape) + 1, N, C, H, W, K, s)
+    x, w, dy = bf16_round(x), bf16_round(w), bf16_round(dy)
+    th = angle_list(mode, C, seed=C)
+    plan = o1d.Plan(th, K)
+    wd = torch.from_numpy(w).to(DEV)
+    y = o1d.fprop(_to_dev(x, nhwc, torch.bfloat16), wd, None, plan, s, nhwc)
+    dx = o1d.dgrad(_to_dev(dy, nhwc, torch.bfloat16), wd, plan, H, W, s, nhwc)
+    dw, db = o1d.wgrad(_to_dev(dy, nhwc, torch.bfloat16), _to_dev(x, nhwc, torch.bfloat16), plan, s, nhwc,
+                       with_bias=True)
+    assert y.dtype == torch.bfloat16 and dx.dtype == torch.bfloat16 and dw.dtype == torch.float32
+    ry = O.forward_safe(oracle, x, w, th, None, s, False, False)
+    rdx, _, _ = O.backward_safe(oracle, x, w, th, dy, None, s, False, False)
+    assert_bf16_close(_to_nchw(y, nhwc), ry, "fprop")
+    assert_bf16_close(_to_nchw(dx, nhwc), rdx, "dgrad")
+    rdw64 = oracle.wgrad_f64(*_pad_for_stride(dy, x, s), th, K, s)
+    assert rel_err(dw.cpu().numpy(), rdw64) <= TOL_WGRAD      # dw is accumulated and emitted in fp32
+    assert rel_err(db.cpu().numpy(), dy.sum(axis=(0, 2, 3), dtype=np.float64)) <= TOL_WGRAD
+
+
+def test_wgrad_is_deterministic():
+    x, w, dy = make_inputs(7, 8, 96, 56, 56, 31)
+    plan = o1d.Plan(angle_list("rr", 96), 31)
+    for nhwc in (False, True):
+        xd, dyd = _to_dev(x, nhwc), _to_dev(dy, nhwc)
+        a = o1d.wgrad(dyd, xd, plan, 1, nhwc, True)
+        for _ in range(3):
+            b = o1d.wgrad(dyd, xd, plan, 1, nhwc, True)
+            assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_transposes(dtype):
+    for shape in [(2, 56, 56, 96), (3, 7, 7, 768), (1, 5, 9, 3), (2, 13, 17, 40), (1, 1, 1, 1), (1, 64, 64, 64)]:
+        x = torch.randn(shape, device=DEV).to(dtype)
+        y = o1d.nhwc_to_nchw(x)
+        assert y.is_contiguous() and torch.equal(y, x.permute(0, 3, 1, 2).contiguous())
+        z = o1d.nchw_to_nhwc(y)
+        assert z.is_contiguous() and torch.equal(z, x)
+
+
+def test_five_callable_surface(oracle):
+    """The reference loader's fprop/dgrad/wgrad/nhwc_to_nchw/nchw_to_nhwc contract."""
+    fprop, dgrad, wgrad, to_nchw, to_nhwc = o1d.oriented_dwconv1d_get_module_from_params("float", 15, 2, 7, Sb=1)
+    x, w, dy = make_inputs(21, 2, 16, 12, 20, 15, 2)
+    th = angle_list("model", 16)
+    xd, wd, dyd, thd = (torch.from_numpy(a).to(DEV) for a in (x, w, dy, th))
+    assert rel_err(fprop(xd, wd, thd).cpu().numpy(), oracle.fprop(x, w, th, 2)) <= TOL_FPROP
+    assert rel_err(dgrad(dyd, wd, thd).cpu().numpy(), oracle.dgrad(dy, w, th, 2)) <= TOL_DGRAD
+    assert rel_err(wgrad(dyd, xd, thd).cpu().numpy(), oracle.wgrad_f64(dy, x, th, 15, 2)) <= TOL_WGRAD
+    assert torch.equal(to_nhwc(to_nchw(xd.permute(0, 2, 3, 1).contiguous())), xd.permute(0, 2, 3, 1).contiguous())
+    with pytest.raises(RuntimeError, match="divisible"):
+        fprop(xd[:, :, :11], wd, thd)
+
+
+def test_module_arbitrary_size_and_bf16_theta(oracle):
+    """forward_safe on sizes the reference would pad (dwoconv1d.py:154-187), and a module
+    cast to bfloat16 still rasterises from its fp32 angles."""
+    C, K = 24, 13
+    th = angle_list("model+", C)
+    m = o1d.DepthwiseOrientedConv1d(C, C, K, groups=C, stride=2, padding=K // 2, angle=[float(a) for a in th],
+                                    nhwc=True, arbitrary_size=True).to(DEV)
+    x, w, _ = make_inputs(4, 1, C, 25, 40, K, 2)
+    with torch.no_grad():
+        m.weight.copy_(torch.from_numpy(w))
+        m.bias.zero_()
+    y = m(_to_dev(x, True))
+    assert tuple(y.shape) == (1, 13, 20, C)
+    ry = O.forward_safe(oracle, x, w, th, None, 2, False, False)
+    assert rel_err(_to_nchw(y, True), ry) <= TOL_FPROP
+    # bf16 module: theta is rounded by .bfloat16(), the plan must not be
+    mb = o1d.DepthwiseOrientedConv1d(8, 8, 31, groups=8, padding=15, angle=[float(a) for a in angle_list("rr", 8)]
+                                     ).to(DEV).bfloat16()
+    xi = np.zeros((1, 8, 33, 33), np.float32)
+    xi[:, :, 16, 16] = 1
+    with torch.no_grad():
+        mb.weight.copy_(torch.arange(1, 32).float().repeat(8, 1).reshape(8, 1, 1, 31))
+        mb.bias.zero_()
+    yi = mb(torch.from_numpy(xi).to(DEV).bfloat16()).float().cpu().numpy()
+    dh, dw = oracle.offsets(angle_list("rr", 8), 31)
+    for c in range(8):
+        expect = np.zeros((33, 33), np.float32)
+        for k in range(31):
+            expect[16 - dh[c, k], 16 - dw[c, k]] += k + 1
+        assert np.array_equal(yi[0, c], expect), c
+
+
+@pytest.mark.parametrize("hw,C", [(56, 96), (28, 192), (14, 384), (7, 768)])
+def test_full_size_properties(hw, C):
+    """Batch-128 stage shapes, where the CPU oracle would take minutes: size-independent
+    properties instead — linearity in x, exact adjointness identities between the three
+    kernels, and agreement of a sampled sub-batch with the rest."""
+    N, K = 128, 31
+    g = torch.Generator(device="cpu").manual_seed(hw)
+    plan = o1d.Plan(angle_list("rr", C), K)
+    x1 = torch.randn((N, hw, hw, C), generator=g).to(DEV)
+    x2 = torch.randn((N, hw, hw, C), generator=g).to(DEV)
+    dy = torch.randn((N, hw, hw, C), generator=g).to(DEV)
+    w = (0.02 * torch.randn((C, 1, 1, K), generator=g)).to(DEV)
+    y1 = o1d.fprop(x1, w, None, plan, 1, True)
+    y2 = o1d.fprop(x2, w, None, plan, 1, True)
+    y12 = o1d.fprop(x1 + 2 * x2, w, None, plan, 1, True)
+    assert float((y12 - (y1 + 2 * y2)).abs().max()) <= 1e-5 * float(y12.abs().max())
+    # <fprop(x), dy> = <x, dgrad(dy)> = <w, wgrad(dy, x)>
+    dx = o1d.dgrad(dy, w, plan, hw, hw, 1, True)
+    dw, db = o1d.wgrad(dy, x1, plan, 1, True, True)
+    a = float((y1.double() * dy.double()).sum())
+    b = float((x1.double() * dx.double()).sum())
+    c = float((w.double() * dw.double()).sum())
+    scale = float((y1.double() * dy.double()).abs().sum())
+    assert abs(a - b) <= 1e-6 * scale and abs(a - c) <= 1e-6 * scale
+    assert float((db.double() - dy.double().sum(dim=(0, 1, 2))).abs().max()) <= 1e-4 * float(db.abs().max())
+    # the batch is independent per image: a 2-image slice reproduces its part bit for bit
+    ys = o1d.fprop(x1[5:7].contiguous(), w, None, plan, 1, True)
+    assert torch.equal(ys, y1[5:7])
