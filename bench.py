@@ -1,0 +1,375 @@
+#!/usr/bin/env python
+"""Benchmark of the oriented 1D depthwise convolution on B200.
+
+Workload ("stage sweep"): the operator at the four ConvNeXt-T stage shapes
+(H=W, C) = (56,96), (28,192), (14,384), (7,768), batch 128 per GPU, K=31, stride 1,
+NHWC, 8 orientations assigned round-robin, fp32, synthetic N(0,1) inputs.  One step runs
+fprop, dgrad and wgrad once at each shape (12 operator calls).  Throughput is images/s:
+128 images x GPUs per step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]      # this implementation
+    python bench.py --impl reference ...                      # the reference's CPU operator
+
+Prints ONE JSON line.  Extra keys: `kernels` (per-kernel time, algorithmic GB/s and
+fraction of the measured HBM copy rate, fp32 and bf16), `roofline` (the kernel that takes
+the most time), `cpu_baseline`, `e2e` (same work through the nn.Module with host buffers:
+H2D of inputs and D2H of all results inside the timed region), `clocks`.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+STAGES = [(56, 96), (28, 192), (14, 384), (7, 768)]
+BATCH = 128
+K = 31
+L2_BYTES = 126 * 1024 * 1024
+METRIC = "dwoconv1d stage-sweep throughput (fprop+dgrad+wgrad at the 4 ConvNeXt-T stage shapes)"
+HBM_FALLBACK_GBS = 6650.0
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return HBM_FALLBACK_GBS, "fallback"
+
+
+def round_robin_angles(C, n=8):
+    """theta[c] = (c mod n) * pi / n as fp32: the sweep's channel -> orientation assignment."""
+    import numpy as np
+    return np.array([(c % n) * np.pi / n for c in range(C)], dtype=np.float64).astype(np.float32)
+
+
+def algorithmic_bytes(hw, C, esize, n=BATCH):
+    """One tensor in, one tensor out (or two in for wgrad) plus the fp32 taps."""
+    return 2 * n * hw * hw * C * esize + C * K * 4
+
+
+# --------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except Exception:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------
+# reference arm / cpu baseline: the reference's own CPU loops (oracle/_ref), else the port
+# --------------------------------------------------------------------------------------
+def cpu_loops():
+    from oracle.oracle import Oracle, Reference
+    if Reference.available():
+        return Reference(), "reference"
+    return Oracle(), "port"
+
+
+def cpu_step(loops, n_img, seed=0):
+    """fprop + dgrad + wgrad at the four stage shapes on n_img images; returns seconds."""
+    import numpy as np
+    from oracle.oracle import round_robin_angles
+    rng = np.random.default_rng(seed)
+    total = 0.0
+    for hw, C in STAGES:
+        x = rng.standard_normal((n_img, C, hw, hw)).astype(np.float32)
+        dy = rng.standard_normal((n_img, C, hw, hw)).astype(np.float32)
+        w = (0.02 * rng.standard_normal((C, 1, 1, K))).astype(np.float32)
+        th = round_robin_angles(C)
+        t0 = time.perf_counter()
+        loops.fprop(x, w, th, 1)
+        loops.dgrad(dy, w, th, 1)
+        loops.wgrad(dy, x, th, K, 1)
+        total += time.perf_counter() - t0
+    return total
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    loops, kind = cpu_loops()
+    n_img = 8
+    for _ in range(args.warmup):
+        cpu_step(loops, n_img)
+    t = sum(cpu_step(loops, n_img, seed=i) for i in range(args.steps))
+    value = n_img * args.steps / t
+    sample = f"{n_img} images per step at each of the 4 stage shapes, fp32 NCHW, single thread as written"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "img/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "stage-sweep: (56,96),(28,192),(14,384),(7,768) x batch 128, K=31, stride 1, "
+                               "8 orientations round-robin; fprop+dgrad+wgrad per shape",
+                   "sample_images_per_step": n_img},
+        "cpu_baseline": {"value": value, "unit": "img/s", "cores": 1, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "img/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------
+# this implementation
+# --------------------------------------------------------------------------------------
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import oriented1d_b200 as o1d
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    peak, peak_src = measured_peak()
+    g = torch.Generator(device="cpu").manual_seed(rank)
+
+    class Layer:
+        """One stage shape: rotating input sets so that successive launches never find
+        their inputs in L2 (each set is touched once per `nsets` launches and the sets
+        together exceed 4x the L2 size)."""
+
+        def __init__(self, hw, C, dtype):
+            self.hw, self.C, self.dtype = hw, C, dtype
+            es = 4 if dtype == torch.float32 else 2
+            per_set = 2 * BATCH * hw * hw * C * es
+            self.nsets = max(2, -(-4 * L2_BYTES // per_set))
+            self.plan = o1d.Plan(round_robin_angles(C), K)
+            self.w = (0.02 * torch.randn((C, 1, 1, K), generator=g)).to(dev)
+            base_x = torch.randn((BATCH, hw, hw, C), generator=g)
+            base_dy = torch.randn((BATCH, hw, hw, C), generator=g)
+            self.x = [base_x.to(dev).to(dtype).clone() for _ in range(self.nsets)]
+            self.dy = [base_dy.to(dev).to(dtype).clone() for _ in range(self.nsets)]
+            self.i = 0
+
+        def next(self):
+            self.i = (self.i + 1) % self.nsets
+            return self.x[self.i], self.dy[self.i]
+
+    layers32 = [Layer(hw, C, torch.float32) for hw, C in STAGES]
+    launches = {"n": 0}
+
+    def step(layers):
+        grads = []
+        for L in layers:
+            x, dy = L.next()
+            o1d.fprop(x, L.w, None, L.plan, 1, True)
+            o1d.dgrad(dy, L.w, L.plan, L.hw, L.hw, 1, True)
+            dw, db = o1d.wgrad(dy, x, L.plan, 1, True, True)
+            grads += [dw.reshape(-1), db]
+            launches["n"] += o1d.ops.KERNELS_PER_CALL["fprop"] + o1d.ops.KERNELS_PER_CALL["dgrad"] + \
+                o1d.ops.KERNELS_PER_CALL["wgrad"]
+        if world > 1:   # data-parallel training sums the weight gradients across ranks
+            flat = torch.cat(grads)
+            dist.all_reduce(flat)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    # ---- headline: device-resident inputs --------------------------------------------
+    with ClockSampler(local) as clk:
+        launches["n"] = 0
+        warm = max(args.warmup, 3)
+        ms = timed(lambda: step(layers32), args.steps, warm)
+        n_launch = launches["n"] * args.steps // (args.steps + warm)
+        time.sleep(0.25)
+    clocks = clk.summary()
+    value = BATCH * world * args.steps / (ms / 1e3)
+
+    # ---- per-kernel timings (rank 0 only, after the headline) -------------------------
+    kernels, roof = {}, None
+    if rank == 0:
+        reps = 20
+        for dtype, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+            layers = layers32 if dtype == torch.float32 else [Layer(hw, C, dtype) for hw, C in STAGES]
+            for L in layers:
+                es = 4 if dtype == torch.float32 else 2
+                ab = algorithmic_bytes(L.hw, L.C, es)
+
+                def f_fprop(L=L):
+                    x, _ = L.next()
+                    o1d.fprop(x, L.w, None, L.plan, 1, True)
+
+                def f_dgrad(L=L):
+                    _, dy = L.next()
+                    o1d.dgrad(dy, L.w, L.plan, L.hw, L.hw, 1, True)
+
+                def f_wgrad(L=L):
+                    x, dy = L.next()
+                    o1d.wgrad(dy, x, L.plan, 1, True, True)
+
+                for name, fn in (("fprop", f_fprop), ("dgrad", f_dgrad), ("wgrad", f_wgrad)):
+                    t_ms = timed(fn, reps, 3) / reps
+                    gbs = ab / (t_ms * 1e-3) / 1e9
+                    kernels[f"{name}_{tag}_{L.hw}x{L.hw}x{L.C}"] = {
+                        "us": round(t_ms * 1e3, 2), "alg_bytes": ab, "gbs": round(gbs, 1),
+                        "frac": round(gbs / peak, 4)}
+            if dtype != torch.float32:
+                del layers
+                torch.cuda.empty_cache()
+        top = max((k for k in kernels if "_f32_" in k), key=lambda k: kernels[k]["us"])
+        traffic = None
+        try:
+            with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+                traffic = json.load(f).get(top)
+        except Exception:
+            pass
+        roof = {"kernel": top, "bound": "hbm", "achieved": kernels[top]["gbs"], "peak": peak, "unit": "GB/s",
+                "frac": kernels[top]["frac"], "traffic": traffic, "peak_source": peak_src,
+                "alg_bytes_per_launch": kernels[top]["alg_bytes"], "us_per_launch": kernels[top]["us"]}
+
+    # ---- end to end: the nn.Module on host buffers ------------------------------------
+    mods, host = [], []
+    for hw, C in STAGES:
+        m = o1d.DepthwiseOrientedConv1d(C, C, K, groups=C, padding=K // 2, nhwc=True,
+                                        angle=[float(a) for a in round_robin_angles(C)]).to(dev)
+        mods.append(m)
+        hx = torch.randn((BATCH, hw, hw, C), generator=g).pin_memory()
+        hdy = torch.randn((BATCH, hw, hw, C), generator=g).pin_memory()
+        hy, hdx = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
+        hdw = torch.empty((C, 1, 1, K)).pin_memory()
+        hdb = torch.empty((C,)).pin_memory()
+        host.append((hx, hdy, hy, hdx, hdw, hdb))
+    h2d = sum(t[0].numel() * 4 + t[1].numel() * 4 for t in host)
+    d2h = sum(t[2].numel() * 4 + t[3].numel() * 4 + t[4].numel() * 4 + t[5].numel() * 4 for t in host)
+
+    def e2e_step():
+        for m, (hx, hdy, hy, hdx, hdw, hdb) in zip(mods, host):
+            m.weight.grad = None
+            m.bias.grad = None
+            x = hx.to(dev, non_blocking=True).requires_grad_(True)
+            dy = hdy.to(dev, non_blocking=True)
+            y = m(x)
+            y.backward(dy)
+            hy.copy_(y.detach(), non_blocking=True)
+            hdx.copy_(x.grad, non_blocking=True)
+            hdw.copy_(m.weight.grad, non_blocking=True)
+            hdb.copy_(m.bias.grad, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_ms = timed(e2e_step, e2e_steps, 2)
+    e2e_value = BATCH * world * e2e_steps / (e2e_ms / 1e3)
+
+    # ---- CPU baseline (rank 0, bounded sample) ----------------------------------------
+    cpu = None
+    if rank == 0 and not args.no_cpu:
+        loops, kind = cpu_loops()
+        n_img = 32
+        cpu_step(loops, 1)
+        t = cpu_step(loops, n_img)
+        cpu = {"value": n_img / t, "unit": "img/s", "cores": 1, "kind": kind,
+               "sample": f"{n_img} images at each of the 4 stage shapes (fprop+dgrad+wgrad), fp32 NCHW, "
+                         f"{t:.1f} s on one host core of {os.cpu_count()}"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "img/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "stage-sweep: (56,96),(28,192),(14,384),(7,768) x batch 128 per GPU, K=31, "
+                                   "stride 1, NHWC, 8 orientations round-robin; fprop+dgrad+wgrad per shape",
+                       "l2": "inputs rotate over sets totalling >4x L2, so every launch reads from HBM",
+                       "parallelism": f"dp{world} (batch-sharded; weight-gradient all-reduce when >1)"},
+            "roofline": roof, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": n_launch, "clocks": clocks, "kernels": kernels,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

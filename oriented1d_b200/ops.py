@@ -13,6 +13,9 @@ import torch
 from . import _lib
 from ._lib import lib, check
 
+# kernels launched by one call of each entry point (used by the benchmark's launch count)
+KERNELS_PER_CALL = {"fprop": 1, "dgrad": 1, "wgrad": 2, "transpose": 1}
+
 _DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
 
 
