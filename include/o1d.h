@@ -55,6 +55,18 @@ const char *o1d_strerror(int status);
 /* Text of the last CUDA failure seen by the calling thread ("" if none). */
 const char *o1d_last_error(void);
 
+/* Kernel routing, for tests and A/B timing: 0 = automatic (tiled kernels where they apply,
+ * general kernels otherwise), 1 = general kernels only.  Process-wide.  (No counterpart in
+ * the reference, which picks general vs specialised kernels with the SPECIALIZED
+ * environment variable at import time, models/convnext.py:16-23.) */
+int o1d_set_route(int route);
+
+/* Reads the device-side failure flag of the current device into *flag_out (0 = healthy,
+ * 1 = a kernel gave up waiting for a TMA transfer and its output is invalid).  This call
+ * SYNCHRONISES the device; it is a diagnostic, not part of the hot path.  (The reference
+ * checks no launch or device errors at all, kernels.h:529,542,555.) */
+int o1d_device_status(int *flag_out);
+
 /* Rasterised tap offsets of C channels, computed on the host exactly as the reference's
  * CPU loops do (kernels.cpp:37,43-44).  theta_host: C floats (radians, fp32);
  * dh, dw: C*K int8 each.  Requires K odd, K <= 255. */

@@ -21,6 +21,8 @@ SIGNATURES = {
     "o1d_abi_version": (_c_int, []),
     "o1d_strerror": (ctypes.c_char_p, [_c_int]),
     "o1d_last_error": (ctypes.c_char_p, []),
+    "o1d_set_route": (_c_int, [_c_int]),
+    "o1d_device_status": (_c_int, [ctypes.POINTER(_c_int)]),
     "o1d_offsets": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p]),
     "o1d_plan_bytes": (_c_size_t, [_c_int, _c_int]),
     "o1d_plan_build": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p]),
@@ -43,13 +45,14 @@ class O1dError(RuntimeError):
 
 def _load() -> ctypes.CDLL:
     path = _build.LIB
-    if not os.path.exists(path):
+    if _build.stale():
         try:
             _build.build()
         except Exception as e:  # no CPU path exists: fail loudly
-            raise RuntimeError(
-                f"libo1d.so is missing and could not be built ({e}); "
-                "run `python -m oriented1d_b200.build`") from e
+            if not os.path.exists(path):
+                raise RuntimeError(
+                    f"libo1d.so is missing and could not be built ({e}); "
+                    "run `python -m oriented1d_b200.build`") from e
     lib = ctypes.CDLL(path)
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)          # AttributeError if the library lacks a symbol

@@ -18,7 +18,7 @@ LIB = os.path.join(HERE, "libo1d.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-O3", "-std=c++17", "-lineinfo",
+    "-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
     "-Xcompiler", "-fPIC", "-shared",
 ]
 
@@ -34,12 +34,25 @@ def sources() -> list[str]:
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
+def source_digest() -> str:
+    """Hash of everything the library is compiled from (file names and contents)."""
+    import hashlib
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    deps = sorted(glob.glob(os.path.join(CSRC, "*"))) + [os.path.join(HERE, "..", "include", "o1d.h")]
+    for d in deps:
+        h.update(os.path.basename(d).encode())
+        with open(d, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
 def stale() -> bool:
-    if not os.path.exists(LIB):
+    """True when libo1d.so is missing or was built from other sources (content hash kept
+    beside the library; file times are not used because copies do not preserve them)."""
+    if not os.path.exists(LIB) or not os.path.exists(LIB + ".digest"):
         return True
-    t = os.path.getmtime(LIB)
-    deps = glob.glob(os.path.join(CSRC, "*")) + [os.path.join(HERE, "..", "include", "o1d.h")]
-    return any(os.path.getmtime(d) > t for d in deps)
+    with open(LIB + ".digest") as f:
+        return f.read().strip() != source_digest()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -50,6 +63,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         cmd.insert(1, "-Xptxas=-v")
         print(" ".join(cmd))
     subprocess.run(cmd, check=True)
+    with open(LIB + ".digest", "w") as f:
+        f.write(source_digest())
     return LIB
 
 

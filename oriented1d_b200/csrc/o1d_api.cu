@@ -9,6 +9,7 @@
 
 #include "o1d_common.cuh"
 #include "o1d_generic.cuh"
+#include "o1d_tiled_host.cuh"
 #include "o1d_transpose.cuh"
 
 using namespace o1d;
@@ -16,6 +17,7 @@ using namespace o1d;
 namespace {
 
 thread_local char g_err[256] = "";
+int g_force_generic = 0;   // o1d_set_route(): 1 = skip the tiled kernels (testing aid)
 
 int cuda_fail(cudaError_t e, const char *what) {
     snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
@@ -140,6 +142,34 @@ int launch_generic_wgrad(const void *dy, const void *x, const PlanHeader &ph, co
     return O1D_OK;
 }
 
+constexpr int kNotTiled = -1;
+
+// Forward / stride-1 input gradient through the tiled kernels; kNotTiled when they do not apply.
+int try_tiled(const void *x, const float *w, const float *bias, const PlanHeader &ph, const void *plan_host,
+              const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride, int layout, int dtype,
+              int add_identity, int flip, cudaStream_t st, const DeviceInfo &d) {
+    if (g_force_generic) return kNotTiled;
+    const int esize = dtype == O1D_F32 ? 4 : 2;
+    TiledConfig cfg;
+    if (!tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, &cfg))
+        return kNotTiled;
+    if (((uintptr_t)y & 15) != 0) return kNotTiled;
+    CUtensorMap map;
+    if (!make_nhwc_tensor_map(&map, x, N, H, W, C, esize, cfg.p.CC, cfg.p.BR)) return kNotTiled;
+    cfg.p.flip = flip;
+    cfg.p.add_identity = add_identity;
+    PlanView pv = plan_view(plan_dev, ph);
+    cudaError_t e;
+    if (dtype == O1D_F32)
+        e = cfg.p.R == 8 ? launch_tiled_fprop<float, 8>(cfg, map, w, bias, pv, (float *)y, st)
+                         : launch_tiled_fprop<float, 7>(cfg, map, w, bias, pv, (float *)y, st);
+    else
+        e = cfg.p.R == 8 ? launch_tiled_fprop<__nv_bfloat16, 8>(cfg, map, w, bias, pv, (__nv_bfloat16 *)y, st)
+                         : launch_tiled_fprop<__nv_bfloat16, 7>(cfg, map, w, bias, pv, (__nv_bfloat16 *)y, st);
+    if (e != cudaSuccess) return cuda_fail(e, "tiled fprop launch");
+    return O1D_OK;
+}
+
 #define O1D_DISPATCH(fn, ...)                                                                    \
     (dtype == O1D_F32                                                                            \
          ? (layout == O1D_NHWC ? fn<float, O1D_NHWC>(__VA_ARGS__) : fn<float, O1D_NCHW>(__VA_ARGS__)) \
@@ -166,6 +196,18 @@ const char *o1d_strerror(int status) {
 
 const char *o1d_last_error(void) { return g_err; }
 
+int o1d_set_route(int route) {
+    if (route != 0 && route != 1) return O1D_ERR_INVALID;
+    g_force_generic = route;
+    return O1D_OK;
+}
+
+int o1d_device_status(int *flag_out) {
+    if (!flag_out) return O1D_ERR_INVALID;
+    O1D_CUDA(cudaMemcpyFromSymbol(flag_out, g_o1d_device_error, sizeof(int)));
+    return O1D_OK;
+}
+
 int o1d_offsets(const float *theta_host, int C, int K, int8_t *dh, int8_t *dw) {
     if (!theta_host || !dh || !dw || C <= 0 || K <= 0 || (K & 1) == 0 || K > 255) return O1D_ERR_INVALID;
     for (int c = 0; c < C; c++) raster(theta_host[c], K, dh + (size_t)c * K, dw + (size_t)c * K);
@@ -175,7 +217,8 @@ int o1d_offsets(const float *theta_host, int C, int K, int8_t *dh, int8_t *dw) {
 // Worst case: every channel its own class.
 size_t o1d_plan_bytes(int C, int K) {
     if (C <= 0 || K <= 0) return 0;
-    return sizeof(PlanHeader) + align16((uint32_t)C * 2) + align16((uint32_t)C * K * 2) + align16((uint32_t)C);
+    return sizeof(PlanHeader) + align16((uint32_t)C * 2) + align16((uint32_t)C * K * 2) + align16((uint32_t)C) +
+           align16(4 * sizeof(KindComp));
 }
 
 int o1d_plan_build(const float *theta_host, int C, int K, void *plan_host) {
@@ -212,25 +255,48 @@ int o1d_plan_build(const float *theta_host, int C, int K, void *plan_host) {
     h.cls_off = sizeof(PlanHeader);
     h.taps_off = h.cls_off + align16((uint32_t)C * 2);
     h.canon_off = h.taps_off + align16((uint32_t)ncls * K * 2);
-    h.total_bytes = h.canon_off + align16((uint32_t)ncls);
+    h.comps_off = h.canon_off + align16((uint32_t)ncls);
+    h.total_bytes = h.comps_off + align16(4 * sizeof(KindComp));
     char *b = static_cast<char *>(plan_host);
     memset(b, 0, o1d_plan_bytes(C, K));
     memcpy(b + h.cls_off, cls.data(), (size_t)C * 2);
     memcpy(b + h.taps_off, tables.data(), tables.size());
-    // canonical orientation of each class: the line of angle i*pi/8 rounded to fp32
+    // canonical orientation of each class: its taps equal the centre of a built-in table
     int all_canon = 1;
+    std::vector<int8_t> canon_of(ncls, -1);
     for (int i = 0; i < ncls; i++) {
         int8_t canon = -1;
-        for (int o = 0; o < 8 && canon < 0; o++) {
-            raster((float)(o * M_PI / 8.0), K, dh.data(), dw.data());
+        for (int o = 0; o < 8 && canon < 0 && K <= kMaxTaps; o++) {
             bool same = true;
-            for (int k = 0; k < K && same; k++)
-                same = tables[(size_t)i * 2 * K + 2 * k] == dh[k] && tables[(size_t)i * 2 * K + 2 * k + 1] == dw[k];
+            for (int k = 0; k < K && same; k++) {
+                const int kk = k - K / 2 + kHalf;
+                same = tables[(size_t)i * 2 * K + 2 * k] == kCanonDh[o][kk] &&
+                       tables[(size_t)i * 2 * K + 2 * k + 1] == kCanonDw[o][kk];
+            }
             if (same) canon = (int8_t)o;
         }
         b[h.canon_off + i] = canon;
+        canon_of[i] = canon;
         if (canon < 0) all_canon = 0;
     }
+    // distinct (axis, slant, diagonal) compositions of aligned chunks of 8/16/32/64 channels
+    KindComp comps[4];
+    for (int ci = 0; ci < 4; ci++) {
+        KindComp &kc = comps[ci];
+        memset(&kc, 0, sizeof(kc));
+        const int CC = kChunkWidths[ci];
+        if (!all_canon || C % CC != 0) { kc.n = -1; continue; }
+        for (int c0 = 0; c0 < C && kc.n >= 0; c0 += CC) {
+            uint8_t tri[3] = {0, 0, 0};
+            for (int c = c0; c < c0 + CC; c++) tri[canon_kind(canon_of[cls[c]])]++;
+            bool seen = false;
+            for (int t = 0; t < kc.n && !seen; t++) seen = memcmp(kc.tri[t], tri, 3) == 0;
+            if (seen) continue;
+            if (kc.n == kMaxComps) { kc.n = -1; break; }
+            memcpy(kc.tri[kc.n++], tri, 3);
+        }
+    }
+    memcpy(b + h.comps_off, comps, sizeof(comps));
     h.all_canon = all_canon;
     memcpy(b, &h, sizeof(h));
     return O1D_OK;
@@ -253,6 +319,9 @@ int o1d_fprop(const void *x, const float *w, const float *bias, const void *plan
     DeviceInfo d;
     if ((rc = device_info(&d))) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    rc = try_tiled(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
+                   /*flip=*/0, st, d);
+    if (rc != kNotTiled) return rc;
     return O1D_DISPATCH(launch_generic_fprop, x, w, bias, ph, plan_dev, y, N, H, W, C, K, stride,
                         add_identity, st, d);
 }
@@ -267,6 +336,11 @@ int o1d_dgrad(const void *dy, const float *w, const void *plan_host, const void 
     DeviceInfo d;
     if ((rc = device_info(&d))) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    // stride 1: dx = fprop(dy) with the taps mirrored, i.e. (the lines being odd-symmetric)
+    // with the weights read in reverse order
+    rc = try_tiled(dy, w, nullptr, ph, plan_host, plan_dev, dx, N, H, W, C, K, stride, layout, dtype,
+                   add_identity, /*flip=*/1, st, d);
+    if (rc != kNotTiled) return rc;
     return O1D_DISPATCH(launch_generic_dgrad, dy, w, ph, plan_dev, dx, N, H, W, C, K, stride,
                         add_identity, st, d);
 }

@@ -12,13 +12,24 @@ namespace o1d {
 // ---------------------------------------------------------------------------------
 // Plan blob.  The same bytes live on the host and on the device.
 //   [PlanHeader (64 B)] [cls: C x uint16, padded to 16 B] [taps: ncls x K x (dh,dw) int8,
-//   padded to 16 B] [canon: ncls x int8, padded to 16 B]
+//   padded to 16 B] [canon: ncls x int8, padded to 16 B] [comps: 4 x KindComp]
 // cls[c]    orientation class of channel c
 // taps      rasterised offsets of each class, exactly the reference's
 //           (int)(-sinf(theta)*j), (int)(cosf(theta)*j)  (kernels.cpp:43-44)
 // canon[i]  0..7 when class i's line equals the built-in table of the i*22.5 degree
 //           orientation (those have compile-time specialised kernels), else -1
+// comps[i]  for chunk width kChunkWidths[i]: the distinct (axis, slant, diagonal) channel
+//           counts a chunk of that many consecutive channels can have (tiled kernels size
+//           their thread groups from it); n = -1 when C is not a multiple of the width or
+//           there are more than kMaxComps distinct triples
 // ---------------------------------------------------------------------------------
+constexpr int kChunkWidths[4] = {8, 16, 32, 64};
+constexpr int kMaxComps = 16;
+struct KindComp {
+    int32_t n;
+    uint8_t tri[kMaxComps][3];
+};
+
 constexpr uint32_t kPlanMagic = 0x4f314450u;  // "O1DP"
 
 struct PlanHeader {
@@ -27,7 +38,8 @@ struct PlanHeader {
     int32_t max_dh, max_dw;   // largest |dh|, |dw| over all classes
     int32_t all_canon;        // 1 when every class has canon >= 0
     uint32_t cls_off, taps_off, canon_off, total_bytes;
-    uint32_t reserved[5];
+    uint32_t comps_off;
+    uint32_t reserved[4];
 };
 static_assert(sizeof(PlanHeader) == 64, "plan header is 64 bytes");
 

@@ -1,0 +1,427 @@
+// Tiled kernels for the common case: stride 1, K <= 31, every channel on one of the eight
+// canonical lines, NHWC.  One persistent CTA per SM walks work items (image n, chunk of CC
+// channels):
+//
+//   1. TMA (cp.async.bulk.tensor, 4-D box CC x W x BR x 1 over the NHWC tensor) streams the
+//      item's row bands into a ring of staging buffers; the producer runs NSTG bands ahead,
+//      across item boundaries, so HBM reads overlap the arithmetic of the previous item.
+//   2. "restage": each band is re-indexed into one fp32 plane per channel in (line, position)
+//      coordinates (o1d_lines.cuh) with zero gaps between lines, so that every canonical
+//      line becomes one of three base shapes and no tap needs a bounds test.
+//   3. compute: a thread owns a segment of R consecutive outputs along the line direction,
+//      loads each needed input once into a register window and reuses it for all taps of
+//      that line row (1 shared-memory load per ~3-7 FMAs instead of 1 per FMA).  Warps are
+//      uniform in base shape, so there is no divergence and offsets are immediates.
+//   4. outputs go through a small planar staging buffer and leave as 128-bit NHWC stores,
+//      with bias added on the way.
+//
+// The reference kernels (models/dwoconv1d_specialized/kernels/kernels.h:201-291) give each
+// block one (n, c) plane band, re-read the halo rows per band (up to 15x read
+// amplification at 56x56) and redo sincosf + float->int + four compares per tap.
+#pragma once
+
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "o1d_common.cuh"
+#include "o1d_lines.cuh"
+
+namespace o1d {
+
+constexpr int kTiledThreads = 512;
+constexpr int kMaxStages = 8;
+constexpr int kMaxCC = 64;
+constexpr int kZeroFloats = 64;              // block of zeros a missing line is redirected to
+constexpr uint32_t kSpinLimit = 1u << 22;    // mbarrier polls before giving up
+
+// Device-side failure flag (a TMA wait that ran out of polls).  Read with o1d_device_status().
+__device__ int g_o1d_device_error = 0;
+
+struct FastDiv {   // q = n / d for n*d < 2^32
+    uint32_t mul, d;
+    __host__ __device__ static FastDiv make(uint32_t d_) { return FastDiv{(uint32_t)(0x100000000ull / d_) + 1u, d_}; }
+    __device__ __forceinline__ uint32_t div(uint32_t n) const { return d == 1 ? n : __umulhi(n, mul); }
+};
+
+struct TiledParams {
+    int N, H, W, C, K;
+    int CC, nchunks, total_items;
+    int R, BR, NB, NSTG;
+    int pitch_n, pitch_t;         // line pitch of non-transposed / transposed planes (floats)
+    int plane_stride;             // floats between channel planes
+    int out_pitch_n, out_pitch_t, out_plane_stride;
+    int nseg_line, nseg_diag;     // segments per channel per band
+    int flip, add_identity;
+    int rezero;                   // planes must be cleared per item (H != W)
+    // shared memory layout, in floats from the start of dynamic smem
+    int off_planar, off_zero, off_out, off_wts, off_misc;
+    int off_stage_bytes, stage_bytes, stage_stride, off_bar_bytes;
+    int zero_floats_total;        // floats to clear at kernel start (planar + zero block)
+    FastDiv div_gv, div_w, div_nseg_line, div_nseg_diag, div_br, div_wline, div_wdiag, div_chunks, div_nb;
+};
+
+template <int I, int N, typename F>
+__device__ __forceinline__ void static_for(F &&f) {
+    if constexpr (I < N) {
+        f(std::integral_constant<int, I>{});
+        static_for<I + 1, N>(f);
+    }
+}
+
+// ---- mbarrier / TMA primitives ------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and raises the device flag) if the data never arrives.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(&g_o1d_device_error, 1);
+    return false;
+}
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1,
+                                            int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+// ---- segment evaluation --------------------------------------------------------------
+// AXIS / SLANT: R outputs at (line, pos0 .. pos0+R-1).  `sm` is the float view of shared
+// memory, `base` the index of (line 0, position 0) of the channel plane.
+template <int KIND, int JH, int R>
+__device__ __forceinline__ void seg_line(const float *__restrict__ sm, int base, int pitch, int nlines,
+                                         int zero_idx, int line, int pos0, const float (&w)[kMaxTaps],
+                                         float (&acc)[R]) {
+    using P = LP<KIND, JH>;
+    static_for<0, P::p.nrows>([&](auto ri) {
+        constexpr int r = decltype(ri)::value;
+        constexpr int d = P::p.row_d[r], lo = P::p.row_lo[r], hi = P::p.row_hi[r];
+        constexpr int WN = hi - lo + R;
+        const int l = line + d;
+        const int src = ((unsigned)l < (unsigned)nlines) ? base + l * pitch + pos0 + lo : zero_idx;
+        float win[WN];
+#pragma unroll
+        for (int i = 0; i < WN; i++) win[i] = sm[src + i];
+        static_for<0, P::p.ntaps>([&](auto ti) {
+            constexpr int t = decltype(ti)::value;
+            if constexpr (P::p.tap_row[t] == r) {
+                constexpr int off = P::p.tap_dp[t] - lo, k = P::p.tap_k[t];
+#pragma unroll
+                for (int o = 0; o < R; o++) acc[o] = fmaf(w[k], win[off + o], acc[o]);
+            }
+        });
+    });
+}
+
+// DIAG: outputs r = 0..R-1 at (ltop - r, pos0 + r); tap m reads (ltop - (r+m), pos0 + (r+m)).
+template <int JH, int R>
+__device__ __forceinline__ void seg_diag(const float *__restrict__ sm, int base, int pitch, int nlines,
+                                         int zero_idx, int ltop, int pos0, const float (&w)[kMaxTaps],
+                                         float (&acc)[R]) {
+    using P = LP<KIND_DIAG, JH>;
+    constexpr int lo = P::p.row_lo[0], hi = P::p.row_hi[0];
+    constexpr int WN = hi - lo + R;
+    float win[WN];
+    const int step = 1 - pitch;
+    const int origin = base + ltop * pitch + pos0;
+#pragma unroll
+    for (int i = 0; i < WN; i++) {
+        const int t = lo + i;
+        const int l = ltop - t;
+        win[i] = sm[((unsigned)l < (unsigned)nlines) ? origin + t * step : zero_idx];
+    }
+    static_for<0, P::p.ntaps>([&](auto ti) {
+        constexpr int t = decltype(ti)::value;
+        constexpr int off = P::p.tap_dp[t] - lo, k = P::p.tap_k[t];
+#pragma unroll
+        for (int o = 0; o < R; o++) acc[o] = fmaf(w[k], win[off + o], acc[o]);
+    });
+}
+
+// Sum colliding taps into the first of their group (the reference adds the products of
+// all taps that land on the same pixel; merging the weights first is the same sum).
+template <int KIND, int JH>
+__device__ __forceinline__ void merge_weights(float (&w)[kMaxTaps]) {
+    using P = LP<KIND, JH>;
+    static_for<0, kMaxTaps>([&](auto ki) {
+        constexpr int k = decltype(ki)::value;
+        constexpr int into = P::p.merge_into[k];
+        if constexpr (into >= 0 && into != k) w[into] += w[k];
+    });
+}
+
+// Elements of T per 16-byte vector, and the unpack / pack helpers.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    __device__ static void unpack(const uint4 &v, float (&f)[4]) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    }
+    __device__ static uint4 pack(const float (&f)[4]) {
+        return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+    }
+};
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ static void unpack(const uint4 &v, float (&f)[8]) {
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            f[2 * i] = __uint_as_float(u[i] << 16);
+            f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+        }
+    }
+    __device__ static uint4 pack(const float (&f)[8]) {
+        uint32_t u[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            u[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(u[0], u[1], u[2], u[3]);
+    }
+};
+
+// ---------------------------------------------------------------------------------
+// Forward (and, with flipped weights, stride-1 input gradient), NHWC.
+// ---------------------------------------------------------------------------------
+template <typename T, int R, int JH>
+__global__ void __launch_bounds__(kTiledThreads, 1)
+tiled_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restrict__ wgt,
+                        const float *__restrict__ bias, const uint16_t *__restrict__ cls,
+                        const int8_t *__restrict__ canon, T *__restrict__ y, const TiledParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float *sm = reinterpret_cast<float *>(smem_raw);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + p.off_bar_bytes);
+    float *wts = sm + p.off_wts;                               // [CC][32]
+    int *misc = reinterpret_cast<int *>(sm + p.off_misc);
+    // misc layout: [0..2] channels per kind, [4..4+CC) sorted channel list (by kind),
+    // [4+CC ..) per-channel int4 maps for restage, then for the store phase, then bias
+    int *ch_sorted = misc + 4;
+    int4 *map_in = reinterpret_cast<int4 *>(misc + 4 + kMaxCC);
+    int4 *map_out = map_in + kMaxCC;
+    float *bias_s = reinterpret_cast<float *>(map_out + kMaxCC);
+    int *err_s = misc + 3;
+
+    constexpr int VE = Vec16<T>::N;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int GV = p.CC / VE;
+
+    for (int i = tid; i < p.zero_floats_total; i += nt) sm[p.off_planar + i] = 0.f;
+    if (tid == 0) {
+        for (int s = 0; s < p.NSTG; s++) mbar_init(&full[s], 1);
+        *err_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int my_items = (p.total_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int total_bands = my_items * p.NB;
+
+    auto issue = [&](int gb) {   // producer: one elected thread
+        const int it = p.div_nb.div(gb), b = gb - it * p.NB;
+        const int item = blockIdx.x + it * gridDim.x;
+        const int n = p.div_chunks.div(item), chunk = item - n * p.nchunks;
+        const int s = gb % p.NSTG;
+        mbar_expect_tx(&full[s], p.stage_bytes);
+        tma_load_4d(smem_raw + p.off_stage_bytes + (size_t)s * p.stage_stride, &tmap, &full[s], chunk * p.CC, 0,
+                    b * p.BR, n);
+    };
+    if (tid == 0)
+        for (int gb = 0; gb < p.NSTG && gb < total_bands; gb++) issue(gb);
+
+    for (int it = 0; it < my_items; it++) {
+        const int item = blockIdx.x + it * gridDim.x;
+        const int n = p.div_chunks.div(item), chunk = item - n * p.nchunks;
+        const int c0 = chunk * p.CC;
+
+        // ---- per-item channel tables (warp 0) and weights (all threads) ----------------
+        if (tid < 32) {
+            int cnt_before = 0;
+            int counts[3];
+            for (int kind = 0; kind < 3; kind++) {
+                int cnt = 0;
+                for (int base = 0; base < p.CC; base += 32) {
+                    const int i = base + tid;
+                    const int o = (i < p.CC) ? canon[cls[c0 + i]] : -1;
+                    const bool mine = o >= 0 && canon_kind(o) == kind;
+                    const unsigned m = __ballot_sync(0xffffffffu, mine);
+                    if (mine) ch_sorted[cnt_before + cnt + __popc(m & ((1u << tid) - 1))] = i;
+                    cnt += __popc(m);
+                }
+                counts[kind] = cnt;
+                cnt_before += cnt;
+            }
+            if (tid < 3) misc[tid] = counts[tid];
+        }
+        for (int i = tid; i < p.CC; i += nt) {
+            const int o = canon[cls[c0 + i]];
+            const int mode = canon_mode(o);
+            const int pbase = p.off_planar + 32 + i * p.plane_stride;
+            const int obase = i * p.out_plane_stride;
+            // storage index = a*h + b*w + c
+            int4 mi, mo;
+            if (mode & MODE_T) {
+                mi = make_int4((mode & MODE_FP) ? -1 : 1, p.pitch_t, pbase + ((mode & MODE_FP) ? p.H - 1 : 0), mode);
+                mo = make_int4((mode & MODE_FP) ? -1 : 1, p.out_pitch_t, obase + ((mode & MODE_FP) ? p.BR - 1 : 0), mode);
+            } else {
+                mi = make_int4(p.pitch_n, (mode & MODE_FP) ? -1 : 1, pbase + ((mode & MODE_FP) ? p.W - 1 : 0), mode);
+                mo = make_int4(p.out_pitch_n, (mode & MODE_FP) ? -1 : 1, obase + ((mode & MODE_FP) ? p.W - 1 : 0), mode);
+            }
+            map_in[i] = mi;
+            map_out[i] = mo;
+            bias_s[i] = bias ? __ldg(bias + c0 + i) : 0.f;
+        }
+        {
+            const int pad = p.K / 2;
+            for (int e = tid; e < p.CC * 32; e += nt) {
+                const int i = e >> 5, k = e & 31;
+                float v = 0.f;
+                if (k < kMaxTaps) {
+                    const int o = canon[cls[c0 + i]];
+                    int kk = k - kHalf + pad;                      // tap of the K-long kernel
+                    if (kk >= 0 && kk < p.K) {
+                        const bool rev = ((canon_mode(o) & MODE_REV) != 0) != (p.flip != 0);
+                        if (rev) kk = p.K - 1 - kk;
+                        v = __ldg(wgt + (size_t)(c0 + i) * p.K + kk);
+                        if (p.add_identity && kk == pad) v += 1.f;
+                    }
+                }
+                wts[e] = v;
+            }
+        }
+        if (p.rezero) {
+            for (int i = tid; i < p.CC * p.plane_stride; i += nt) sm[p.off_planar + 32 + i] = 0.f;
+        }
+        __syncthreads();
+
+        // ---- restage: staging bands -> planes -------------------------------------------
+        {
+            const int vecs = p.BR * p.W * GV;
+            for (int b = 0; b < p.NB; b++) {
+                const int gb = it * p.NB + b, s = gb % p.NSTG;
+                if (*err_s == 0 && !mbar_wait(&full[s], (gb / p.NSTG) & 1)) *err_s = 1;
+                const uint4 *stage = reinterpret_cast<const uint4 *>(smem_raw + p.off_stage_bytes + (size_t)s * p.stage_stride);
+                for (int v = tid; v < vecs; v += nt) {
+                    const int pix = p.div_gv.div(v), g = v - pix * GV;
+                    const int rl = p.div_w.div(pix), col = pix - rl * p.W;
+                    const int h = b * p.BR + rl;
+                    float f[VE];
+                    Vec16<T>::unpack(stage[v], f);
+#pragma unroll
+                    for (int j = 0; j < VE; j++) {
+                        const int4 m = map_in[g * VE + j];
+                        sm[m.x * h + m.y * col + m.z] = f[j];
+                    }
+                }
+                __syncthreads();
+                if (tid == 0 && gb + p.NSTG < total_bands) issue(gb + p.NSTG);
+            }
+        }
+
+        // ---- compute -----------------------------------------------------------------
+        // thread -> (kind, channel, segment); groups of equal kind start on warp boundaries
+        const int nA = misc[0], nS = misc[1], nD = misc[2];
+        const int slotsA = (nA * p.nseg_line + 31) & ~31, slotsS = (nS * p.nseg_line + 31) & ~31;
+        int kind = -1, ch = 0, seg = 0;
+        {
+            int idx = tid;
+            if (idx < slotsA) {
+                const int j = p.div_nseg_line.div(idx);
+                if (j < nA) { kind = KIND_AXIS; ch = ch_sorted[j]; seg = idx - j * p.nseg_line; }
+            } else if ((idx -= slotsA) < slotsS) {
+                const int j = p.div_nseg_line.div(idx);
+                if (j < nS) { kind = KIND_SLANT; ch = ch_sorted[nA + j]; seg = idx - j * p.nseg_line; }
+            } else {
+                idx -= slotsS;
+                const int j = p.div_nseg_diag.div(idx);
+                if (j < nD) { kind = KIND_DIAG; ch = ch_sorted[nA + nS + j]; seg = idx - j * p.nseg_diag; }
+            }
+        }
+        float w[kMaxTaps];
+#pragma unroll
+        for (int k = 0; k < kMaxTaps; k++) w[k] = wts[ch * 32 + k];
+        if (kind == KIND_AXIS) merge_weights<KIND_AXIS, JH>(w);
+        else if (kind == KIND_SLANT) merge_weights<KIND_SLANT, JH>(w);
+        else if (kind == KIND_DIAG) merge_weights<KIND_DIAG, JH>(w);
+
+        const int4 mi = map_in[ch], mo = map_out[ch];
+        const bool transposed = (mi.w & MODE_T) != 0, fp = (mi.w & MODE_FP) != 0;
+        const int pbase = p.off_planar + 32 + ch * p.plane_stride;
+        const int pitch = transposed ? p.pitch_t : p.pitch_n;
+        const int nlines = transposed ? p.W : p.H;
+        float *outb = sm + p.off_out;
+
+        for (int b = 0; b < p.NB; b++) {
+            float *ob = outb + (b & 1) * (p.CC * p.out_plane_stride) + ch * p.out_plane_stride;
+            if (kind == KIND_AXIS || kind == KIND_SLANT) {
+                int line, pos0, oidx;
+                if (!transposed) {                       // lines are image rows
+                    const int sg = p.div_br.div(seg), rl = seg - sg * p.BR;
+                    line = b * p.BR + rl; pos0 = sg * R;
+                    oidx = rl * p.out_pitch_n + pos0;
+                } else {                                 // lines are image columns
+                    const int sub = p.div_wline.div(seg), l = seg - sub * p.W;
+                    const int band0 = fp ? p.H - (b + 1) * p.BR : b * p.BR;
+                    line = l; pos0 = band0 + sub * R;
+                    oidx = l * p.out_pitch_t + sub * R;
+                }
+                float acc[R];
+#pragma unroll
+                for (int o = 0; o < R; o++) acc[o] = 0.f;
+                if (kind == KIND_AXIS) seg_line<KIND_AXIS, JH, R>(sm, pbase, pitch, nlines, p.off_zero, line, pos0, w, acc);
+                else seg_line<KIND_SLANT, JH, R>(sm, pbase, pitch, nlines, p.off_zero, line, pos0, w, acc);
+#pragma unroll
+                for (int o = 0; o < R; o++) ob[oidx + o] = acc[o];
+            } else if (kind == KIND_DIAG) {
+                const int wd = p.W + R - 1;
+                const int sub = p.div_wdiag.div(seg), qi = seg - sub * wd;
+                const int pos0 = qi - (R - 1);
+                const int ltop_local = sub * R + R - 1;
+                float acc[R];
+#pragma unroll
+                for (int o = 0; o < R; o++) acc[o] = 0.f;
+                seg_diag<JH, R>(sm, pbase, p.pitch_n, p.H, p.off_zero, b * p.BR + ltop_local, pos0, w, acc);
+#pragma unroll
+                for (int o = 0; o < R; o++)
+                    if ((unsigned)(pos0 + o) < (unsigned)p.W) ob[(ltop_local - o) * p.out_pitch_n + pos0 + o] = acc[o];
+            }
+            __syncthreads();
+            // ---- store band b: planar staging -> NHWC, 16 bytes per thread -------------------
+            {
+                const float *src = outb + (b & 1) * (p.CC * p.out_plane_stride);
+                const int vecs = p.BR * p.W * GV;
+                T *ybase = y + (((size_t)n * p.H + (size_t)b * p.BR) * p.W) * p.C + c0;
+                for (int v = tid; v < vecs; v += nt) {
+                    const int pix = p.div_gv.div(v), g = v - pix * GV;
+                    const int rl = p.div_w.div(pix), col = pix - rl * p.W;
+                    float f[VE];
+#pragma unroll
+                    for (int j = 0; j < VE; j++) {
+                        const int4 m = map_out[g * VE + j];
+                        f[j] = src[m.x * rl + m.y * col + m.z] + bias_s[g * VE + j];
+                    }
+                    *reinterpret_cast<uint4 *>(ybase + (size_t)pix * p.C + g * VE) = Vec16<T>::pack(f);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace o1d

@@ -1,0 +1,152 @@
+// Host side of the tiled kernels: applicability test, tile/chunk selection, shared-memory
+// layout, TMA descriptor, launch.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "o1d_tiled.cuh"
+
+namespace o1d {
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup, so that the
+// library does not link against libcuda and loads on machines without a driver.
+inline PFN_encodeTiled encode_tiled_fn() {
+    static PFN_encodeTiled fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (PFN_encodeTiled)p;
+    }
+    return fn;
+}
+
+struct TiledConfig {
+    TiledParams p;
+    int smem_bytes;
+    int grid;
+    int stage_stride;
+    double util;
+};
+
+inline int round32(int v) { return (v + 31) & ~31; }
+inline int make_odd(int v) { return v | 1; }
+
+// Picks R, BR (band rows), CC (chunk channels) and the stage count; returns false when the
+// tiled kernels do not apply and the general kernels must be used.
+inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, int H, int W, int C, int K,
+                            int stride, int layout, int esize, int smem_limit, int sms, TiledConfig *out) {
+    if (stride != 1 || layout != O1D_NHWC || K > kMaxTaps || !ph.all_canon || ph.comps_off == 0) return false;
+    if (H > 256 || W > 256 || (C * esize) % 16 != 0) return false;
+    int R = 0;
+    if (H % 8 == 0 && W % 8 == 0) R = 8;
+    else if (H % 7 == 0 && W % 7 == 0) R = 7;
+    else return false;
+    const int VE = 16 / esize;
+    const KindComp *comps = reinterpret_cast<const KindComp *>(static_cast<const char *>(plan_host) + ph.comps_off);
+    const int G = (R == 8) ? 17 : 16;
+    const int pitch_n = make_odd(W + G), pitch_t = make_odd(H + G);
+    const int PLS = (H * pitch_n > W * pitch_t) ? H * pitch_n : W * pitch_t;
+
+    bool found = false;
+    TiledConfig best{};
+    for (int ci = 0; ci < 4; ci++) {
+        const int CC = kChunkWidths[ci];
+        if (CC % VE != 0 || C % CC != 0 || comps[ci].n <= 0) continue;
+        for (int BR = R; BR <= H; BR += R) {
+            if (H % BR != 0) continue;
+            const int nseg_line = BR * (W / R), nseg_diag = (W + R - 1) * (BR / R);
+            int worst = 0;
+            double active = 0;
+            for (int t = 0; t < comps[ci].n; t++) {
+                const int a = comps[ci].tri[t][0], s = comps[ci].tri[t][1], d = comps[ci].tri[t][2];
+                const int slots = round32(a * nseg_line) + round32(s * nseg_line) + round32(d * nseg_diag);
+                if (slots > worst) worst = slots;
+                active += (double)((a + s) * nseg_line + d * nseg_diag) / comps[ci].n;
+            }
+            if (worst > kTiledThreads) continue;
+            const int out_pitch_n = make_odd(W), out_pitch_t = make_odd(BR);
+            const int OPS = (BR * out_pitch_n > W * out_pitch_t) ? BR * out_pitch_n : W * out_pitch_t;
+            TiledParams p{};
+            p.off_planar = 0;
+            const int planar_floats = 32 + CC * PLS;
+            p.off_zero = planar_floats;
+            p.zero_floats_total = planar_floats + kZeroFloats;
+            p.off_out = p.zero_floats_total;
+            p.off_wts = p.off_out + 2 * CC * OPS;
+            p.off_misc = p.off_wts + CC * 32;
+            const int misc_ints = 4 + kMaxCC + 2 * kMaxCC * 4 + kMaxCC;
+            int bytes = (p.off_misc + misc_ints) * 4;
+            bytes = (bytes + 127) & ~127;
+            p.off_stage_bytes = bytes;
+            p.stage_bytes = BR * W * CC * esize;
+            const int stage_stride = (p.stage_bytes + 127) & ~127;
+            const int NB = H / BR;
+            int room = smem_limit - bytes - 8 * kMaxStages - 128;
+            int nstg = room / stage_stride;
+            if (nstg > kMaxStages) nstg = kMaxStages;
+            if (nstg < 2 && !(nstg == 1 && NB == 1)) continue;
+            // Rank: thread utilisation first; among equals prefer fewer, larger bands.
+            const double util = active / kTiledThreads;
+            const bool better = !found || util > best.util + 1e-9 ||
+                                (util > best.util - 1e-9 && BR * CC > best.p.BR * best.p.CC);
+            if (!better) continue;
+            p.N = N; p.H = H; p.W = W; p.C = C; p.K = K;
+            p.CC = CC; p.nchunks = C / CC; p.total_items = N * p.nchunks;
+            p.R = R; p.BR = BR; p.NB = NB; p.NSTG = nstg;
+            p.pitch_n = pitch_n; p.pitch_t = pitch_t; p.plane_stride = PLS;
+            p.out_pitch_n = out_pitch_n; p.out_pitch_t = out_pitch_t; p.out_plane_stride = OPS;
+            p.nseg_line = nseg_line; p.nseg_diag = nseg_diag;
+            p.rezero = (H != W);
+            p.stage_stride = stage_stride;
+            p.off_bar_bytes = p.off_stage_bytes + nstg * stage_stride;
+            p.div_gv = FastDiv::make(CC / VE); p.div_w = FastDiv::make(W);
+            p.div_nseg_line = FastDiv::make(nseg_line); p.div_nseg_diag = FastDiv::make(nseg_diag);
+            p.div_br = FastDiv::make(BR); p.div_wline = FastDiv::make(W); p.div_wdiag = FastDiv::make(W + R - 1);
+            p.div_chunks = FastDiv::make(p.nchunks); p.div_nb = FastDiv::make(NB);
+            best.p = p;
+            best.smem_bytes = p.off_bar_bytes + 8 * kMaxStages;
+            best.stage_stride = stage_stride;
+            best.grid = p.total_items < sms ? p.total_items : sms;
+            best.util = util;
+            found = true;
+        }
+    }
+    if (found) *out = best;
+    return found;
+}
+
+// 4-D tensor map over an NHWC tensor: dims (C, W, H, N), box (CC, W, BR, 1).
+inline bool make_nhwc_tensor_map(CUtensorMap *map, const void *base, int N, int H, int W, int C, int esize,
+                                 int CC, int BR) {
+    PFN_encodeTiled enc = encode_tiled_fn();
+    if (!enc || ((uintptr_t)base & 15)) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)W * C * esize, (cuuint64_t)H * W * C * esize};
+    cuuint32_t box[4] = {(cuuint32_t)CC, (cuuint32_t)W, (cuuint32_t)BR, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                     const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <typename T, int R>
+cudaError_t launch_tiled_fprop(const TiledConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
+                               const PlanView &pv, T *y, cudaStream_t st) {
+    auto kern = tiled_fprop_nhwc_kernel<T, R, kHalf>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
+    if (e != cudaSuccess) return e;
+    kern<<<cfg.grid, kTiledThreads, cfg.smem_bytes, st>>>(map, w, bias, pv.cls, pv.canon, y, cfg.p);
+    return cudaGetLastError();
+}
+
+}  // namespace o1d

@@ -156,3 +156,18 @@ def nchw_to_nhwc(x):
     """[N,C,H,W] -> [N,H,W,C], contiguous (reference: kernels.cu:63-68)."""
     N, C, H, W = x.shape
     return _transpose(x, N, C, H * W, (N, H, W, C))
+
+
+def set_route(general_only: bool) -> None:
+    """Testing aid: True routes every call to the general kernels, False restores the
+    automatic choice (tiled kernels where they apply)."""
+    check(lib.o1d_set_route(1 if general_only else 0), "o1d_set_route")
+
+
+def device_status(device=None) -> int:
+    """Device-side failure flag (0 = healthy).  Synchronises the device."""
+    import ctypes
+    flag = ctypes.c_int(0)
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        check(lib.o1d_device_status(ctypes.byref(flag)), "o1d_device_status")
+    return flag.value

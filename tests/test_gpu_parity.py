@@ -219,7 +219,7 @@ def test_module_arbitrary_size_and_bf16_theta(oracle):
     y = m(_to_dev(x, True))
     assert tuple(y.shape) == (1, 13, 20, C)
     ry = O.forward_safe(oracle, x, w, th, None, 2, False, False)
-    assert rel_err(_to_nchw(y, True), ry) <= TOL_FPROP
+    assert rel_err(_to_nchw(y.detach(), True), ry) <= TOL_FPROP
     # bf16 module: theta is rounded by .bfloat16(), the plan must not be
     mb = o1d.DepthwiseOrientedConv1d(8, 8, 31, groups=8, padding=15, angle=[float(a) for a in angle_list("rr", 8)]
                                      ).to(DEV).bfloat16()
@@ -228,7 +228,7 @@ def test_module_arbitrary_size_and_bf16_theta(oracle):
     with torch.no_grad():
         mb.weight.copy_(torch.arange(1, 32).float().repeat(8, 1).reshape(8, 1, 1, 31))
         mb.bias.zero_()
-    yi = mb(torch.from_numpy(xi).to(DEV).bfloat16()).float().cpu().numpy()
+    yi = mb(torch.from_numpy(xi).to(DEV).bfloat16()).detach().float().cpu().numpy()
     dh, dw = oracle.offsets(angle_list("rr", 8), 31)
     for c in range(8):
         expect = np.zeros((33, 33), np.float32)
@@ -265,3 +265,47 @@ def test_full_size_properties(hw, C):
     # the batch is independent per image: a 2-image slice reproduces its part bit for bit
     ys = o1d.fprop(x1[5:7].contiguous(), w, None, plan, 1, True)
     assert torch.equal(ys, y1[5:7])
+
+
+@pytest.mark.parametrize("hw,C,mode", [(56, 96, "rr"), (56, 96, "model"), (28, 192, "rr"), (28, 192, "model+"),
+                                        (14, 384, "rr"), (14, 384, "model"), (7, 768, "rr"), (7, 768, "model+"),
+                                        (32, 64, "model"), (16, 24, "rr")])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_tiled_route_equals_general_route(hw, C, mode, dtype):
+    """The tiled kernels (TMA-staged planes, register windows) against the general kernels
+    on identical device inputs, forward and input gradient, with bias / identity tap."""
+    N, K = 5, 31
+    g = torch.Generator(device="cpu").manual_seed(hw * C)
+    x = torch.randn((N, hw, hw, C), generator=g).to(DEV).to(dtype)
+    w = (0.02 * torch.randn((C, 1, 1, K), generator=g)).to(DEV)
+    bias = torch.randn((C,), generator=g).to(DEV)
+    plan = o1d.Plan(angle_list(mode, C), K)
+    try:
+        o1d.ops.set_route(True)
+        y_ref = o1d.fprop(x, w, bias, plan, 1, True, True).float()
+        dx_ref = o1d.dgrad(x, w, plan, hw, hw, 1, True, False).float()
+    finally:
+        o1d.ops.set_route(False)
+    y = o1d.fprop(x, w, bias, plan, 1, True, True).float()
+    dx = o1d.dgrad(x, w, plan, hw, hw, 1, True, False).float()
+    assert o1d.ops.device_status() == 0
+    if dtype == torch.float32:
+        assert float((y - y_ref).abs().max()) <= 1e-5 * float(y_ref.abs().max())
+        assert float((dx - dx_ref).abs().max()) <= 1e-5 * float(dx_ref.abs().max())
+    else:   # both round an fp32 sum to bf16: at most one bf16 ulp apart
+        assert float(((y - y_ref).abs() / y_ref.abs().clamp_min(1e-2)).max()) <= 2 ** -7
+        assert float(((dx - dx_ref).abs() / dx_ref.abs().clamp_min(1e-2)).max()) <= 2 ** -7
+
+
+@pytest.mark.parametrize("K", [7, 13, 15, 27])
+def test_tiled_short_kernels(oracle, K):
+    """K < 31 uses the centre of the 31-tap line."""
+    N, C, hw = 2, 32, 28
+    x, w, dy = make_inputs(K, N, C, hw, hw, K)
+    th = angle_list("model+", C)
+    plan = o1d.Plan(th, K)
+    wd = torch.from_numpy(w).to(DEV)
+    y = o1d.fprop(_to_dev(x, True), wd, None, plan, 1, True)
+    dx = o1d.dgrad(_to_dev(dy, True), wd, plan, hw, hw, 1, True)
+    assert rel_err(_to_nchw(y, True), oracle.fprop(x, w, th, 1)) <= TOL_FPROP
+    assert rel_err(_to_nchw(dx, True), oracle.dgrad(dy, w, th, 1)) <= TOL_DGRAD
