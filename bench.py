@@ -357,6 +357,51 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_case(args):
+    """One kernel of the sweep on its own, a few launches: the command profiled with ncu.
+    Case names are the keys of the `kernels` table, e.g. fprop_f32_56x56x96."""
+    import torch
+
+    import oriented1d_b200 as o1d
+
+    op, tag, shape = args.case.split("_")
+    hw, _, C = (int(v) for v in shape.split("x"))
+    dtype = torch.float32 if tag == "f32" else torch.bfloat16
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    n = args.batch
+    plan = o1d.Plan(round_robin_angles(C) if args.angles == "rr" else block_angles(C), K)
+    w = (0.02 * torch.randn((C, 1, 1, K), generator=g)).to(dev)
+    sets = [(torch.randn((n, hw, hw, C), generator=g).to(dev).to(dtype),
+             torch.randn((n, hw, hw, C), generator=g).to(dev).to(dtype)) for _ in range(2)]
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for i in range(args.reps):
+        x, dy = sets[i % 2]
+        e0.record()
+        if op == "fprop":
+            o1d.fprop(x, w, None, plan, 1, True)
+        elif op == "dgrad":
+            o1d.dgrad(dy, w, plan, hw, hw, 1, True)
+        else:
+            o1d.wgrad(dy, x, plan, 1, True, True)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    es = 4 if dtype == torch.float32 else 2
+    print(json.dumps({"case": args.case, "batch": n, "us": times, "alg_bytes": algorithmic_bytes(hw, C, es, n),
+                      "device_status": o1d.ops.device_status()}))
+
+
+def block_angles(C, n=8):
+    """The models' assignment: blocks of ~C/n consecutive channels share an angle
+    (reference: models/convnext.py:60-65)."""
+    import numpy as np
+    return np.array([((n * (c + 1) - 1) // C) * np.pi / n for c in range(C)], dtype=np.float64).astype(np.float32)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -364,8 +409,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--case", default=None, help="run one kernel case alone, e.g. fprop_f32_56x56x96")
+    ap.add_argument("--batch", type=int, default=64, help="batch for --case")
+    ap.add_argument("--reps", type=int, default=3, help="launches for --case")
+    ap.add_argument("--angles", default="rr", choices=["rr", "block"], help="channel->orientation map for --case")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -143,6 +143,7 @@ int launch_generic_wgrad(const void *dy, const void *x, const PlanHeader &ph, co
 }
 
 constexpr int kNotTiled = -1;
+constexpr int kMaxTiledCtas = 256;   // upper bound on SMs (grid of the persistent kernels)
 
 // Forward / stride-1 input gradient through the tiled kernels; kNotTiled when they do not apply.
 int try_tiled(const void *x, const float *w, const float *bias, const PlanHeader &ph, const void *plan_host,
@@ -151,7 +152,7 @@ int try_tiled(const void *x, const float *w, const float *bias, const PlanHeader
     if (g_force_generic) return kNotTiled;
     const int esize = dtype == O1D_F32 ? 4 : 2;
     TiledConfig cfg;
-    if (!tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, &cfg))
+    if (!tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, OP_FPROP, &cfg))
         return kNotTiled;
     if (((uintptr_t)y & 15) != 0) return kNotTiled;
     CUtensorMap map;
@@ -161,12 +162,49 @@ int try_tiled(const void *x, const float *w, const float *bias, const PlanHeader
     PlanView pv = plan_view(plan_dev, ph);
     cudaError_t e;
     if (dtype == O1D_F32)
-        e = cfg.p.R == 8 ? launch_tiled_fprop<float, 8>(cfg, map, w, bias, pv, (float *)y, st)
-                         : launch_tiled_fprop<float, 7>(cfg, map, w, bias, pv, (float *)y, st);
+        e = cfg.p.R == 8 ? launch_tiled<float, 8, OP_FPROP>(cfg, map, w, bias, pv, (float *)y, nullptr, st)
+                         : launch_tiled<float, 7, OP_FPROP>(cfg, map, w, bias, pv, (float *)y, nullptr, st);
     else
-        e = cfg.p.R == 8 ? launch_tiled_fprop<__nv_bfloat16, 8>(cfg, map, w, bias, pv, (__nv_bfloat16 *)y, st)
-                         : launch_tiled_fprop<__nv_bfloat16, 7>(cfg, map, w, bias, pv, (__nv_bfloat16 *)y, st);
+        e = cfg.p.R == 8
+                ? launch_tiled<__nv_bfloat16, 8, OP_FPROP>(cfg, map, w, bias, pv, (__nv_bfloat16 *)y, nullptr, st)
+                : launch_tiled<__nv_bfloat16, 7, OP_FPROP>(cfg, map, w, bias, pv, (__nv_bfloat16 *)y, nullptr, st);
     if (e != cudaSuccess) return cuda_fail(e, "tiled fprop launch");
+    return O1D_OK;
+}
+
+// Weight gradient through the tiled kernels.  `cfg_only`: just report the workspace size.
+int try_tiled_wgrad(const void *dy, const void *x, const PlanHeader &ph, const void *plan_host,
+                    const void *plan_dev, float *dw, float *db, void *workspace, size_t workspace_bytes, int N,
+                    int H, int W, int C, int K, int stride, int layout, int dtype, cudaStream_t st,
+                    const DeviceInfo &d, size_t *need_bytes) {
+    if (g_force_generic) return kNotTiled;
+    const int esize = dtype == O1D_F32 ? 4 : 2;
+    TiledConfig cfg;
+    if (!tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, OP_WGRAD, &cfg))
+        return kNotTiled;
+    const size_t need = tiled_wgrad_partial_bytes(cfg);
+    if (need_bytes) { *need_bytes = need; return O1D_OK; }
+    if (((uintptr_t)dy & 15) != 0 || ((uintptr_t)workspace & 15) != 0) return kNotTiled;
+    if (workspace_bytes < need) return O1D_ERR_WORKSPACE;
+    CUtensorMap map;
+    if (!make_nhwc_tensor_map(&map, x, N, H, W, C, esize, cfg.p.CC, cfg.p.BR)) return kNotTiled;
+    PlanView pv = plan_view(plan_dev, ph);
+    float *partial = (float *)workspace;
+    cudaError_t e;
+    if (dtype == O1D_F32)
+        e = cfg.p.R == 8 ? launch_tiled<float, 8, OP_WGRAD>(cfg, map, nullptr, nullptr, pv, (float *)dy, partial, st)
+                         : launch_tiled<float, 7, OP_WGRAD>(cfg, map, nullptr, nullptr, pv, (float *)dy, partial, st);
+    else
+        e = cfg.p.R == 8 ? launch_tiled<__nv_bfloat16, 8, OP_WGRAD>(cfg, map, nullptr, nullptr, pv,
+                                                                     (__nv_bfloat16 *)dy, partial, st)
+                         : launch_tiled<__nv_bfloat16, 7, OP_WGRAD>(cfg, map, nullptr, nullptr, pv,
+                                                                     (__nv_bfloat16 *)dy, partial, st);
+    if (e != cudaSuccess) return cuda_fail(e, "tiled wgrad launch");
+    constexpr MergeTables mt = make_merge_tables<kHalf>();
+    const int tot = C * (K + 1);
+    tiled_wgrad_final_kernel<<<ceil_div(tot, 128), 128, 0, st>>>(partial, pv.cls, pv.canon, dw, db, C, K, cfg.p.CC, N,
+                                                                 cfg.p.total_items, cfg.grid, cfg.p.max_visits, mt);
+    O1D_CUDA(cudaGetLastError());
     return O1D_OK;
 }
 
@@ -348,7 +386,11 @@ int o1d_dgrad(const void *dy, const float *w, const void *plan_host, const void 
 size_t o1d_wgrad_workspace_bytes(int N, int H, int W, int C, int K, int stride, int layout, int dtype) {
     if (bad_common(N, H, W, C, K, stride, layout, dtype)) return 0;
     const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
-    return (size_t)generic_wgrad_slices(N, P, Q, C, layout) * C * (K + 1) * sizeof(float);
+    // Large enough for either route: the general kernels' slices, and (an upper bound that
+    // needs no plan) one partial per tiled CTA and chunk visit.
+    const size_t general = (size_t)generic_wgrad_slices(N, P, Q, C, layout) * C * (K + 1) * sizeof(float);
+    const size_t tiled = (size_t)kMaxTiledCtas * 4 * kMaxCC * kPartialStride * sizeof(float);
+    return general > tiled ? general : tiled;
 }
 
 int o1d_wgrad(const void *dy, const void *x, const void *plan_host, const void *plan_dev, float *dw,
@@ -361,6 +403,11 @@ int o1d_wgrad(const void *dy, const void *x, const void *plan_host, const void *
     if (!workspace || workspace_bytes < o1d_wgrad_workspace_bytes(N, H, W, C, K, stride, layout, dtype))
         return O1D_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
+    DeviceInfo d;
+    if ((rc = device_info(&d))) return rc;
+    rc = try_tiled_wgrad(dy, x, ph, plan_host, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K, stride,
+                         layout, dtype, st, d, nullptr);
+    if (rc != kNotTiled && rc != O1D_ERR_WORKSPACE) return rc;
     return O1D_DISPATCH(launch_generic_wgrad, dy, x, ph, plan_dev, dw, db, (float *)workspace, N, H, W,
                         C, K, stride, st);
 }

@@ -12,12 +12,19 @@
 //      loads each needed input once into a register window and reuses it for all taps of
 //      that line row (1 shared-memory load per ~3-7 FMAs instead of 1 per FMA).  Warps are
 //      uniform in base shape, so there is no divergence and offsets are immediates.
-//   4. outputs go through a small planar staging buffer and leave as 128-bit NHWC stores,
-//      with bias added on the way.
+//   4. forward: outputs go through a small planar staging buffer and leave as 128-bit NHWC
+//      stores, with bias added on the way.
+//      weight gradient: the same staging buffer is filled the other way round (dy band,
+//      128-bit NHWC loads), each thread multiplies its register window with its R dy values
+//      into one accumulator per tap and keeps accumulating over bands and images; when the
+//      CTA moves to another channel chunk the accumulators are reduced across threads in a
+//      fixed order and written as one partial per (CTA, chunk); a second kernel adds the
+//      partials in CTA order.  No atomics anywhere: results are bit-reproducible.
 //
-// The reference kernels (models/dwoconv1d_specialized/kernels/kernels.h:201-291) give each
-// block one (n, c) plane band, re-read the halo rows per band (up to 15x read
-// amplification at 56x56) and redo sincosf + float->int + four compares per tap.
+// The reference kernels (models/dwoconv1d_specialized/kernels/kernels.h:201-291, :388-509)
+// give each block one (n, c) plane band, re-read the halo rows per band (up to 15x read
+// amplification at 56x56), redo sincosf + float->int + four compares per tap, and finish
+// the weight gradient with 31 fp32 atomicAdd per block.
 #pragma once
 
 #include <cuda.h>
@@ -34,6 +41,10 @@ constexpr int kMaxStages = 8;
 constexpr int kMaxCC = 64;
 constexpr int kZeroFloats = 64;              // block of zeros a missing line is redirected to
 constexpr uint32_t kSpinLimit = 1u << 22;    // mbarrier polls before giving up
+constexpr int kPartialStride = 32;           // floats per channel in a weight-gradient partial:
+                                             // 31 stored taps + the bias-gradient sum
+
+enum : int { OP_FPROP = 0, OP_WGRAD = 1 };
 
 // Device-side failure flag (a TMA wait that ran out of polls).  Read with o1d_device_status().
 __device__ int g_o1d_device_error = 0;
@@ -54,11 +65,13 @@ struct TiledParams {
     int nseg_line, nseg_diag;     // segments per channel per band
     int flip, add_identity;
     int rezero;                   // planes must be cleared per item (H != W)
+    int step_rows, step_cols;     // pixel advance of one thread per loop trip in restage/store
+    int max_visits;               // weight gradient: partial slots per CTA
     // shared memory layout, in floats from the start of dynamic smem
     int off_planar, off_zero, off_out, off_wts, off_misc;
     int off_stage_bytes, stage_bytes, stage_stride, off_bar_bytes;
     int zero_floats_total;        // floats to clear at kernel start (planar + zero block)
-    FastDiv div_gv, div_w, div_nseg_line, div_nseg_diag, div_br, div_wline, div_wdiag, div_chunks, div_nb;
+    FastDiv div_gv, div_w, div_nseg_line, div_nseg_diag, div_br, div_wline, div_wdiag, div_chunks, div_nb, div_n;
 };
 
 template <int I, int N, typename F>
@@ -102,17 +115,20 @@ __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, u
 // ---- segment evaluation --------------------------------------------------------------
 // AXIS / SLANT: R outputs at (line, pos0 .. pos0+R-1).  `sm` is the float view of shared
 // memory, `base` the index of (line 0, position 0) of the channel plane.
-template <int KIND, int JH, int R>
+//   forward:          acc[o]  += w[k] * x(line+dl_k, pos0+o+dp_k)
+//   weight gradient:  acc[k]  += sum_o x(line+dl_k, pos0+o+dp_k) * g[o]
+template <int OP, int KIND, int JH, int R>
 __device__ __forceinline__ void seg_line(const float *__restrict__ sm, int base, int pitch, int nlines,
-                                         int zero_idx, int line, int pos0, const float (&w)[kMaxTaps],
-                                         float (&acc)[R]) {
+                                         int zero_idx, int line, int pos0,
+                                         const float (&w)[OP == OP_FPROP ? kMaxTaps : R],
+                                         float (&acc)[OP == OP_FPROP ? R : kMaxTaps]) {
     using P = LP<KIND, JH>;
+    const int at0 = base + line * pitch + pos0;
     static_for<0, P::p.nrows>([&](auto ri) {
         constexpr int r = decltype(ri)::value;
         constexpr int d = P::p.row_d[r], lo = P::p.row_lo[r], hi = P::p.row_hi[r];
         constexpr int WN = hi - lo + R;
-        const int l = line + d;
-        const int src = ((unsigned)l < (unsigned)nlines) ? base + l * pitch + pos0 + lo : zero_idx;
+        const int src = ((unsigned)(line + d) < (unsigned)nlines) ? at0 + d * pitch + lo : zero_idx;
         float win[WN];
 #pragma unroll
         for (int i = 0; i < WN; i++) win[i] = sm[src + i];
@@ -120,18 +136,26 @@ __device__ __forceinline__ void seg_line(const float *__restrict__ sm, int base,
             constexpr int t = decltype(ti)::value;
             if constexpr (P::p.tap_row[t] == r) {
                 constexpr int off = P::p.tap_dp[t] - lo, k = P::p.tap_k[t];
+                if constexpr (OP == OP_FPROP) {
 #pragma unroll
-                for (int o = 0; o < R; o++) acc[o] = fmaf(w[k], win[off + o], acc[o]);
+                    for (int o = 0; o < R; o++) acc[o] = fmaf(w[k], win[off + o], acc[o]);
+                } else {
+                    float s = acc[k];
+#pragma unroll
+                    for (int o = 0; o < R; o++) s = fmaf(win[off + o], w[o], s);
+                    acc[k] = s;
+                }
             }
         });
     });
 }
 
 // DIAG: outputs r = 0..R-1 at (ltop - r, pos0 + r); tap m reads (ltop - (r+m), pos0 + (r+m)).
-template <int JH, int R>
+template <int OP, int JH, int R>
 __device__ __forceinline__ void seg_diag(const float *__restrict__ sm, int base, int pitch, int nlines,
-                                         int zero_idx, int ltop, int pos0, const float (&w)[kMaxTaps],
-                                         float (&acc)[R]) {
+                                         int zero_idx, int ltop, int pos0,
+                                         const float (&w)[OP == OP_FPROP ? kMaxTaps : R],
+                                         float (&acc)[OP == OP_FPROP ? R : kMaxTaps]) {
     using P = LP<KIND_DIAG, JH>;
     constexpr int lo = P::p.row_lo[0], hi = P::p.row_hi[0];
     constexpr int WN = hi - lo + R;
@@ -141,14 +165,20 @@ __device__ __forceinline__ void seg_diag(const float *__restrict__ sm, int base,
 #pragma unroll
     for (int i = 0; i < WN; i++) {
         const int t = lo + i;
-        const int l = ltop - t;
-        win[i] = sm[((unsigned)l < (unsigned)nlines) ? origin + t * step : zero_idx];
+        win[i] = sm[((unsigned)(ltop - t) < (unsigned)nlines) ? origin + t * step : zero_idx];
     }
     static_for<0, P::p.ntaps>([&](auto ti) {
         constexpr int t = decltype(ti)::value;
         constexpr int off = P::p.tap_dp[t] - lo, k = P::p.tap_k[t];
+        if constexpr (OP == OP_FPROP) {
 #pragma unroll
-        for (int o = 0; o < R; o++) acc[o] = fmaf(w[k], win[off + o], acc[o]);
+            for (int o = 0; o < R; o++) acc[o] = fmaf(w[k], win[off + o], acc[o]);
+        } else {
+            float s = acc[k];
+#pragma unroll
+            for (int o = 0; o < R; o++) s = fmaf(win[off + o], w[o], s);
+            acc[k] = s;
+        }
     });
 }
 
@@ -162,6 +192,18 @@ __device__ __forceinline__ void merge_weights(float (&w)[kMaxTaps]) {
         constexpr int into = P::p.merge_into[k];
         if constexpr (into >= 0 && into != k) w[into] += w[k];
     });
+}
+
+// merge_into tables of the three base lines as kernel-parameter data (second-level reduce).
+struct MergeTables { int8_t t[3][32]; };
+template <int JH> constexpr MergeTables make_merge_tables() {
+    MergeTables m{};
+    for (int kind = 0; kind < 3; kind++) {
+        LinePlan p = make_line_plan(kind, JH);
+        for (int k = 0; k < kMaxTaps; k++) m.t[kind][k] = (int8_t)p.merge_into[k];
+        m.t[kind][31] = -1;
+    }
+    return m;
 }
 
 // Elements of T per 16-byte vector, and the unpack / pack helpers.
@@ -196,28 +238,39 @@ template <> struct Vec16<__nv_bfloat16> {
     }
 };
 
+// Item range of a CTA in the weight gradient: contiguous in chunk-major order, so that a
+// CTA stays on one channel chunk for many images and seldom flushes its accumulators.
+__host__ __device__ inline int wgrad_item_lo(int cta, int ctas, int total) {
+    return (int)(((long long)cta * total) / ctas);
+}
+
 // ---------------------------------------------------------------------------------
-// Forward (and, with flipped weights, stride-1 input gradient), NHWC.
+// OP_FPROP: y = conv(x) (+bias); with flip=1 the weights are read in reverse order, which
+//           for stride 1 is the input gradient.  `io` is y.
+// OP_WGRAD: partial[(cta, visit)][CC][32] = per-chunk sums of x (*) dy; `io` is dy.
 // ---------------------------------------------------------------------------------
-template <typename T, int R, int JH>
+template <typename T, int R, int JH, int OP>
 __global__ void __launch_bounds__(kTiledThreads, 1)
-tiled_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restrict__ wgt,
-                        const float *__restrict__ bias, const uint16_t *__restrict__ cls,
-                        const int8_t *__restrict__ canon, T *__restrict__ y, const TiledParams p) {
+tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restrict__ wgt,
+                  const float *__restrict__ bias, const uint16_t *__restrict__ cls,
+                  const int8_t *__restrict__ canon, T *__restrict__ io, float *__restrict__ partial,
+                  const TiledParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float *sm = reinterpret_cast<float *>(smem_raw);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + p.off_bar_bytes);
     float *wts = sm + p.off_wts;                               // [CC][32]
     int *misc = reinterpret_cast<int *>(sm + p.off_misc);
-    // misc layout: [0..2] channels per kind, [4..4+CC) sorted channel list (by kind),
-    // [4+CC ..) per-channel int4 maps for restage, then for the store phase, then bias
+    // misc layout: [0..2] channels per kind, [3] error flag, [4..4+CC) channels sorted by kind,
+    // then per-channel int4 index maps for the planes and for the band buffer, then bias
     int *ch_sorted = misc + 4;
     int4 *map_in = reinterpret_cast<int4 *>(misc + 4 + kMaxCC);
     int4 *map_out = map_in + kMaxCC;
     float *bias_s = reinterpret_cast<float *>(map_out + kMaxCC);
+    int2 *ch_range = reinterpret_cast<int2 *>(bias_s + kMaxCC);   // threads [x, x+y) work on channel i
     int *err_s = misc + 3;
 
     constexpr int VE = Vec16<T>::N;
+    constexpr int NACC = (OP == OP_FPROP) ? R : kMaxTaps;
     const int tid = threadIdx.x, nt = blockDim.x;
     const int GV = p.CC / VE;
 
@@ -230,13 +283,30 @@ tiled_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *_
     }
     __syncthreads();
 
-    const int my_items = (p.total_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    // ---- item sequence of this CTA ------------------------------------------------------
+    int my_items, item_base;
+    if (OP == OP_FPROP) {
+        my_items = (p.total_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+        item_base = blockIdx.x;
+    } else {
+        item_base = wgrad_item_lo(blockIdx.x, gridDim.x, p.total_items);
+        my_items = wgrad_item_lo(blockIdx.x + 1, gridDim.x, p.total_items) - item_base;
+    }
+    auto item_of = [&](int it, int &n, int &chunk) {
+        if (OP == OP_FPROP) {           // image-major: neighbouring CTAs share DRAM pages
+            const int item = item_base + it * gridDim.x;
+            n = p.div_chunks.div(item); chunk = item - n * p.nchunks;
+        } else {                        // chunk-major
+            const int item = item_base + it;
+            chunk = p.div_n.div(item); n = item - chunk * p.N;
+        }
+    };
     const int total_bands = my_items * p.NB;
 
     auto issue = [&](int gb) {   // producer: one elected thread
         const int it = p.div_nb.div(gb), b = gb - it * p.NB;
-        const int item = blockIdx.x + it * gridDim.x;
-        const int n = p.div_chunks.div(item), chunk = item - n * p.nchunks;
+        int n, chunk;
+        item_of(it, n, chunk);
         const int s = gb % p.NSTG;
         mbar_expect_tx(&full[s], p.stage_bytes);
         tma_load_4d(smem_raw + p.off_stage_bytes + (size_t)s * p.stage_stride, &tmap, &full[s], chunk * p.CC, 0,
@@ -245,64 +315,120 @@ tiled_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *_
     if (tid == 0)
         for (int gb = 0; gb < p.NSTG && gb < total_bands; gb++) issue(gb);
 
-    for (int it = 0; it < my_items; it++) {
-        const int item = blockIdx.x + it * gridDim.x;
-        const int n = p.div_chunks.div(item), chunk = item - n * p.nchunks;
-        const int c0 = chunk * p.CC;
+    // fixed per-thread walk over the (pixel, 16-byte vector) pairs of one band
+    const int g_vec = tid % GV;
+    const int pix_first = tid / GV;
+    const int rl_first = p.div_w.div(pix_first), col_first = pix_first - rl_first * p.W;
+    const int band_pixels = p.BR * p.W;
 
-        // ---- per-item channel tables (warp 0) and weights (all threads) ----------------
-        if (tid < 32) {
-            int cnt_before = 0;
-            int counts[3];
-            for (int kind = 0; kind < 3; kind++) {
-                int cnt = 0;
-                for (int base = 0; base < p.CC; base += 32) {
-                    const int i = base + tid;
-                    const int o = (i < p.CC) ? canon[cls[c0 + i]] : -1;
-                    const bool mine = o >= 0 && canon_kind(o) == kind;
-                    const unsigned m = __ballot_sync(0xffffffffu, mine);
-                    if (mine) ch_sorted[cnt_before + cnt + __popc(m & ((1u << tid) - 1))] = i;
-                    cnt += __popc(m);
+    float acc_w[OP == OP_WGRAD ? kMaxTaps : 1];
+    float acc_db = 0.f;
+    if (OP == OP_WGRAD) {
+#pragma unroll
+        for (int k = 0; k < (OP == OP_WGRAD ? kMaxTaps : 1); k++) acc_w[k] = 0.f;
+    }
+    int cur_chunk = -1, visit = -1;
+    bool have_next_band = false;        // weight gradient: dy band 0 of this item is already staged
+    int kind = -1, ch = 0, seg = 0;
+    int group_n = 0;                    // threads working on my channel
+
+    // Cross-thread reduction of the weight-gradient accumulators of the current chunk, in
+    // thread order (fixed), a few taps per pass through the idle band buffers.
+    auto flush = [&]() {
+        float *red = sm + p.off_out;
+        const int cap = (2 * p.CC * p.out_plane_stride) / nt;   // taps per pass (host ensures >= 1)
+        float *dst = partial + ((size_t)blockIdx.x * p.max_visits + visit) * p.CC * kPartialStride;
+        for (int k0 = 0; k0 < kPartialStride; k0 += cap) {
+            __syncthreads();
+#pragma unroll
+            for (int k = 0; k < kPartialStride; k++)
+                if (k >= k0 && k < k0 + cap) {
+                    float v = 0.f;
+                    if (kind >= 0) v = (k < kMaxTaps) ? acc_w[k < kMaxTaps ? k : 0] : acc_db;
+                    red[(k - k0) * nt + tid] = v;
                 }
-                counts[kind] = cnt;
-                cnt_before += cnt;
+            __syncthreads();
+            const int ntap = (kPartialStride - k0 < cap) ? kPartialStride - k0 : cap;
+            for (int e = tid; e < p.CC * ntap; e += nt) {
+                const int i = e / ntap, kk = e - i * ntap;
+                const int2 rg = ch_range[i];
+                float sum = 0.f;
+                for (int t = 0; t < rg.y; t++) sum += red[kk * nt + rg.x + t];
+                dst[i * kPartialStride + k0 + kk] = sum;
             }
-            if (tid < 3) misc[tid] = counts[tid];
         }
-        for (int i = tid; i < p.CC; i += nt) {
-            const int o = canon[cls[c0 + i]];
-            const int mode = canon_mode(o);
-            const int pbase = p.off_planar + 32 + i * p.plane_stride;
-            const int obase = i * p.out_plane_stride;
-            // storage index = a*h + b*w + c
-            int4 mi, mo;
-            if (mode & MODE_T) {
-                mi = make_int4((mode & MODE_FP) ? -1 : 1, p.pitch_t, pbase + ((mode & MODE_FP) ? p.H - 1 : 0), mode);
-                mo = make_int4((mode & MODE_FP) ? -1 : 1, p.out_pitch_t, obase + ((mode & MODE_FP) ? p.BR - 1 : 0), mode);
-            } else {
-                mi = make_int4(p.pitch_n, (mode & MODE_FP) ? -1 : 1, pbase + ((mode & MODE_FP) ? p.W - 1 : 0), mode);
-                mo = make_int4(p.out_pitch_n, (mode & MODE_FP) ? -1 : 1, obase + ((mode & MODE_FP) ? p.W - 1 : 0), mode);
-            }
-            map_in[i] = mi;
-            map_out[i] = mo;
-            bias_s[i] = bias ? __ldg(bias + c0 + i) : 0.f;
+        __syncthreads();
+    };
+
+    for (int it = 0; it < my_items; it++) {
+        int n, chunk;
+        item_of(it, n, chunk);
+        const int c0 = chunk * p.CC;
+        const bool new_chunk = (chunk != cur_chunk);
+
+        if (OP == OP_WGRAD && new_chunk && cur_chunk >= 0) {
+            flush();
+#pragma unroll
+            for (int k = 0; k < (OP == OP_WGRAD ? kMaxTaps : 1); k++) acc_w[k] = 0.f;
+            acc_db = 0.f;
         }
-        {
-            const int pad = p.K / 2;
-            for (int e = tid; e < p.CC * 32; e += nt) {
-                const int i = e >> 5, k = e & 31;
-                float v = 0.f;
-                if (k < kMaxTaps) {
-                    const int o = canon[cls[c0 + i]];
-                    int kk = k - kHalf + pad;                      // tap of the K-long kernel
-                    if (kk >= 0 && kk < p.K) {
-                        const bool rev = ((canon_mode(o) & MODE_REV) != 0) != (p.flip != 0);
-                        if (rev) kk = p.K - 1 - kk;
-                        v = __ldg(wgt + (size_t)(c0 + i) * p.K + kk);
-                        if (p.add_identity && kk == pad) v += 1.f;
+
+        // ---- per-chunk channel tables --------------------------------------------------
+        if (OP == OP_FPROP || new_chunk) {
+            if (tid < 32) {
+                int cnt_before = 0;
+                int counts[3];
+#pragma unroll
+                for (int kd = 0; kd < 3; kd++) {
+                    int cnt = 0;
+                    for (int base = 0; base < p.CC; base += 32) {
+                        const int i = base + tid;
+                        const int o = (i < p.CC) ? canon[cls[c0 + i]] : -1;
+                        const bool mine = o >= 0 && canon_kind(o) == kd;
+                        const unsigned m = __ballot_sync(0xffffffffu, mine);
+                        if (mine) ch_sorted[cnt_before + cnt + __popc(m & ((1u << tid) - 1))] = i;
+                        cnt += __popc(m);
                     }
+                    counts[kd] = cnt;
+                    cnt_before += cnt;
                 }
-                wts[e] = v;
+#pragma unroll
+                for (int kd = 0; kd < 3; kd++) if (tid == kd) misc[kd] = counts[kd];
+            }
+            for (int i = tid; i < p.CC; i += nt) {
+                const int o = canon[cls[c0 + i]];
+                const int mode = canon_mode(o);
+                const int pbase = p.off_planar + 32 + i * p.plane_stride;
+                const int obase = i * p.out_plane_stride;
+                int4 mi, mo;   // storage index = x*h + y*w + z
+                if (mode & MODE_T) {
+                    mi = make_int4((mode & MODE_FP) ? -1 : 1, p.pitch_t, pbase + ((mode & MODE_FP) ? p.H - 1 : 0), mode);
+                    mo = make_int4((mode & MODE_FP) ? -1 : 1, p.out_pitch_t, obase + ((mode & MODE_FP) ? p.BR - 1 : 0), mode);
+                } else {
+                    mi = make_int4(p.pitch_n, (mode & MODE_FP) ? -1 : 1, pbase + ((mode & MODE_FP) ? p.W - 1 : 0), mode);
+                    mo = make_int4(p.out_pitch_n, (mode & MODE_FP) ? -1 : 1, obase + ((mode & MODE_FP) ? p.W - 1 : 0), mode);
+                }
+                map_in[i] = mi;
+                map_out[i] = mo;
+                bias_s[i] = (OP == OP_FPROP && bias) ? __ldg(bias + c0 + i) : 0.f;
+            }
+            if (OP == OP_FPROP) {
+                const int pad = p.K / 2;
+                for (int e = tid; e < p.CC * 32; e += nt) {
+                    const int i = e >> 5, k = e & 31;
+                    float v = 0.f;
+                    if (k < kMaxTaps) {
+                        const int o = canon[cls[c0 + i]];
+                        int kk = k - kHalf + pad;                      // tap of the K-long kernel
+                        if (kk >= 0 && kk < p.K) {
+                            const bool rev = ((canon_mode(o) & MODE_REV) != 0) != (p.flip != 0);
+                            if (rev) kk = p.K - 1 - kk;
+                            v = __ldg(wgt + (size_t)(c0 + i) * p.K + kk);
+                            if (p.add_identity && kk == pad) v += 1.f;
+                        }
+                    }
+                    wts[e] = v;
+                }
             }
         }
         if (p.rezero) {
@@ -310,24 +436,45 @@ tiled_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *_
         }
         __syncthreads();
 
+        // ---- thread -> (kind, channel, segment); groups of equal kind start on warp boundaries
+        if (OP == OP_FPROP || new_chunk) {
+            const int nA = misc[0], nS = misc[1], nD = misc[2];
+            const int slotsA = (nA * p.nseg_line + 31) & ~31, slotsS = (nS * p.nseg_line + 31) & ~31;
+            kind = -1; ch = 0; seg = 0;
+            int idx = tid;
+            if (idx < slotsA) {
+                const int j = p.div_nseg_line.div(idx);
+                if (j < nA) { kind = KIND_AXIS; ch = ch_sorted[j]; seg = idx - j * p.nseg_line; group_n = p.nseg_line; }
+            } else if ((idx -= slotsA) < slotsS) {
+                const int j = p.div_nseg_line.div(idx);
+                if (j < nS) { kind = KIND_SLANT; ch = ch_sorted[nA + j]; seg = idx - j * p.nseg_line; group_n = p.nseg_line; }
+            } else {
+                idx -= slotsS;
+                const int j = p.div_nseg_diag.div(idx);
+                if (j < nD) { kind = KIND_DIAG; ch = ch_sorted[nA + nS + j]; seg = idx - j * p.nseg_diag; group_n = p.nseg_diag; }
+            }
+            if (kind >= 0 && seg == 0) ch_range[ch] = make_int2(tid, group_n);
+            if (OP == OP_WGRAD) { cur_chunk = chunk; visit++; }
+        }
+
         // ---- restage: staging bands -> planes -------------------------------------------
         {
-            const int vecs = p.BR * p.W * GV;
+            int4 m[VE];
+#pragma unroll
+            for (int j = 0; j < VE; j++) m[j] = map_in[g_vec * VE + j];
             for (int b = 0; b < p.NB; b++) {
                 const int gb = it * p.NB + b, s = gb % p.NSTG;
                 if (*err_s == 0 && !mbar_wait(&full[s], (gb / p.NSTG) & 1)) *err_s = 1;
                 const uint4 *stage = reinterpret_cast<const uint4 *>(smem_raw + p.off_stage_bytes + (size_t)s * p.stage_stride);
-                for (int v = tid; v < vecs; v += nt) {
-                    const int pix = p.div_gv.div(v), g = v - pix * GV;
-                    const int rl = p.div_w.div(pix), col = pix - rl * p.W;
+                int rl = rl_first, col = col_first;
+                for (int pix = pix_first; pix < band_pixels; pix += nt / GV) {
                     const int h = b * p.BR + rl;
                     float f[VE];
-                    Vec16<T>::unpack(stage[v], f);
+                    Vec16<T>::unpack(stage[pix * GV + g_vec], f);
 #pragma unroll
-                    for (int j = 0; j < VE; j++) {
-                        const int4 m = map_in[g * VE + j];
-                        sm[m.x * h + m.y * col + m.z] = f[j];
-                    }
+                    for (int j = 0; j < VE; j++) sm[m[j].x * h + m[j].y * col + m[j].z] = f[j];
+                    rl += p.step_rows; col += p.step_cols;
+                    if (col >= p.W) { col -= p.W; rl++; }
                 }
                 __syncthreads();
                 if (tid == 0 && gb + p.NSTG < total_bands) issue(gb + p.NSTG);
@@ -335,40 +482,77 @@ tiled_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *_
         }
 
         // ---- compute -----------------------------------------------------------------
-        // thread -> (kind, channel, segment); groups of equal kind start on warp boundaries
-        const int nA = misc[0], nS = misc[1], nD = misc[2];
-        const int slotsA = (nA * p.nseg_line + 31) & ~31, slotsS = (nS * p.nseg_line + 31) & ~31;
-        int kind = -1, ch = 0, seg = 0;
-        {
-            int idx = tid;
-            if (idx < slotsA) {
-                const int j = p.div_nseg_line.div(idx);
-                if (j < nA) { kind = KIND_AXIS; ch = ch_sorted[j]; seg = idx - j * p.nseg_line; }
-            } else if ((idx -= slotsA) < slotsS) {
-                const int j = p.div_nseg_line.div(idx);
-                if (j < nS) { kind = KIND_SLANT; ch = ch_sorted[nA + j]; seg = idx - j * p.nseg_line; }
-            } else {
-                idx -= slotsS;
-                const int j = p.div_nseg_diag.div(idx);
-                if (j < nD) { kind = KIND_DIAG; ch = ch_sorted[nA + nS + j]; seg = idx - j * p.nseg_diag; }
-            }
-        }
         float w[kMaxTaps];
+        if (OP == OP_FPROP) {
 #pragma unroll
-        for (int k = 0; k < kMaxTaps; k++) w[k] = wts[ch * 32 + k];
-        if (kind == KIND_AXIS) merge_weights<KIND_AXIS, JH>(w);
-        else if (kind == KIND_SLANT) merge_weights<KIND_SLANT, JH>(w);
-        else if (kind == KIND_DIAG) merge_weights<KIND_DIAG, JH>(w);
+            for (int k = 0; k < kMaxTaps; k++) w[k] = wts[ch * 32 + k];
+            if (kind == KIND_AXIS) merge_weights<KIND_AXIS, JH>(w);
+            else if (kind == KIND_SLANT) merge_weights<KIND_SLANT, JH>(w);
+            else if (kind == KIND_DIAG) merge_weights<KIND_DIAG, JH>(w);
+        }
 
-        const int4 mi = map_in[ch], mo = map_out[ch];
+        const int4 mi = map_in[ch];
         const bool transposed = (mi.w & MODE_T) != 0, fp = (mi.w & MODE_FP) != 0;
         const int pbase = p.off_planar + 32 + ch * p.plane_stride;
         const int pitch = transposed ? p.pitch_t : p.pitch_n;
         const int nlines = transposed ? p.W : p.H;
         float *outb = sm + p.off_out;
 
+        // band buffer <-> global: per-thread constants
+        int4 mo[VE];
+        float bs[VE];
+#pragma unroll
+        for (int j = 0; j < VE; j++) { mo[j] = map_out[g_vec * VE + j]; bs[j] = bias_s[g_vec * VE + j]; }
+        T *gbase = io + ((size_t)n * p.H * p.W) * p.C + c0 + g_vec * VE;
+        const int band_floats = p.CC * p.out_plane_stride;
+        const int pix_step = nt / GV;
+
+        // Weight gradient: a dy band travels global -> registers (128-bit NHWC loads, issued
+        // before the arithmetic of the previous band) -> band buffer (after it).
+        constexpr int kPre = 2;                       // vectors per thread kept in registers
+        uint4 pre[kPre];
+        auto dy_fetch = [&](const T *src_band) {      // first kPre vectors of this thread
+#pragma unroll
+            for (int u = 0; u < kPre; u++) {
+                const int pix = pix_first + u * pix_step;
+                if (pix < band_pixels) pre[u] = __ldg(reinterpret_cast<const uint4 *>(src_band + (size_t)pix * p.C));
+            }
+        };
+        auto dy_commit = [&](const T *src_band, float *dstb) {
+            int rl = rl_first, col = col_first, u = 0;
+            for (int pix = pix_first; pix < band_pixels; pix += pix_step, u++) {
+                uint4 v;
+                if (u < kPre) v = (u == 0) ? pre[0] : pre[kPre - 1];
+                else v = __ldg(reinterpret_cast<const uint4 *>(src_band + (size_t)pix * p.C));
+                float f[VE];
+                Vec16<T>::unpack(v, f);
+#pragma unroll
+                for (int j = 0; j < VE; j++) dstb[mo[j].x * rl + mo[j].y * col + mo[j].z] = f[j];
+                rl += p.step_rows; col += p.step_cols;
+                if (col >= p.W) { col -= p.W; rl++; }
+            }
+        };
+        if (OP == OP_WGRAD && !have_next_band) {       // first band of the item, not prefetched
+            dy_fetch(gbase);
+            dy_commit(gbase, outb + ((it * p.NB) & 1) * band_floats);
+            __syncthreads();
+        }
+        have_next_band = false;
+
         for (int b = 0; b < p.NB; b++) {
-            float *ob = outb + (b & 1) * (p.CC * p.out_plane_stride) + ch * p.out_plane_stride;
+            const int gbi = it * p.NB + b;             // global band index: selects the buffer
+            float *ob = outb + (gbi & 1) * band_floats + ch * p.out_plane_stride;
+            const T *next_src = nullptr;
+            if (OP == OP_WGRAD) {
+                if (b + 1 < p.NB) {
+                    next_src = gbase + (size_t)(b + 1) * band_pixels * p.C;
+                } else if (it + 1 < my_items) {
+                    int n2, chunk2;
+                    item_of(it + 1, n2, chunk2);
+                    if (chunk2 == chunk) next_src = io + ((size_t)n2 * p.H * p.W) * p.C + c0 + g_vec * VE;
+                }
+                if (next_src) dy_fetch(next_src);
+            }
             if (kind == KIND_AXIS || kind == KIND_SLANT) {
                 int line, pos0, oidx;
                 if (!transposed) {                       // lines are image rows
@@ -381,47 +565,96 @@ tiled_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *_
                     line = l; pos0 = band0 + sub * R;
                     oidx = l * p.out_pitch_t + sub * R;
                 }
-                float acc[R];
+                if constexpr (OP == OP_FPROP) {
+                    float acc[R];
 #pragma unroll
-                for (int o = 0; o < R; o++) acc[o] = 0.f;
-                if (kind == KIND_AXIS) seg_line<KIND_AXIS, JH, R>(sm, pbase, pitch, nlines, p.off_zero, line, pos0, w, acc);
-                else seg_line<KIND_SLANT, JH, R>(sm, pbase, pitch, nlines, p.off_zero, line, pos0, w, acc);
+                    for (int o = 0; o < R; o++) acc[o] = 0.f;
+                    if (kind == KIND_AXIS) seg_line<OP_FPROP, KIND_AXIS, JH, R>(sm, pbase, pitch, nlines, p.off_zero, line, pos0, w, acc);
+                    else seg_line<OP_FPROP, KIND_SLANT, JH, R>(sm, pbase, pitch, nlines, p.off_zero, line, pos0, w, acc);
 #pragma unroll
-                for (int o = 0; o < R; o++) ob[oidx + o] = acc[o];
+                    for (int o = 0; o < R; o++) ob[oidx + o] = acc[o];
+                } else {
+                    float g[R];
+#pragma unroll
+                    for (int o = 0; o < R; o++) { g[o] = ob[oidx + o]; acc_db += g[o]; }
+                    if (kind == KIND_AXIS) seg_line<OP_WGRAD, KIND_AXIS, JH, R>(sm, pbase, pitch, nlines, p.off_zero, line, pos0, g, acc_w);
+                    else seg_line<OP_WGRAD, KIND_SLANT, JH, R>(sm, pbase, pitch, nlines, p.off_zero, line, pos0, g, acc_w);
+                }
             } else if (kind == KIND_DIAG) {
                 const int wd = p.W + R - 1;
                 const int sub = p.div_wdiag.div(seg), qi = seg - sub * wd;
                 const int pos0 = qi - (R - 1);
                 const int ltop_local = sub * R + R - 1;
-                float acc[R];
+                if constexpr (OP == OP_FPROP) {
+                    float acc[R];
 #pragma unroll
-                for (int o = 0; o < R; o++) acc[o] = 0.f;
-                seg_diag<JH, R>(sm, pbase, p.pitch_n, p.H, p.off_zero, b * p.BR + ltop_local, pos0, w, acc);
+                    for (int o = 0; o < R; o++) acc[o] = 0.f;
+                    seg_diag<OP_FPROP, JH, R>(sm, pbase, p.pitch_n, p.H, p.off_zero, b * p.BR + ltop_local, pos0, w, acc);
 #pragma unroll
-                for (int o = 0; o < R; o++)
-                    if ((unsigned)(pos0 + o) < (unsigned)p.W) ob[(ltop_local - o) * p.out_pitch_n + pos0 + o] = acc[o];
+                    for (int o = 0; o < R; o++)
+                        if ((unsigned)(pos0 + o) < (unsigned)p.W) ob[(ltop_local - o) * p.out_pitch_n + pos0 + o] = acc[o];
+                } else {
+                    float g[R];
+#pragma unroll
+                    for (int o = 0; o < R; o++) {
+                        g[o] = ((unsigned)(pos0 + o) < (unsigned)p.W) ? ob[(ltop_local - o) * p.out_pitch_n + pos0 + o] : 0.f;
+                        acc_db += g[o];
+                    }
+                    seg_diag<OP_WGRAD, JH, R>(sm, pbase, p.pitch_n, p.H, p.off_zero, b * p.BR + ltop_local, pos0, g, acc_w);
+                }
+            }
+            if (OP == OP_WGRAD && next_src) {
+                // the other buffer was last read one band ago, before the previous barrier
+                dy_commit(next_src, outb + ((gbi + 1) & 1) * band_floats);
+                if (b + 1 == p.NB) have_next_band = true;
             }
             __syncthreads();
-            // ---- store band b: planar staging -> NHWC, 16 bytes per thread -------------------
-            {
-                const float *src = outb + (b & 1) * (p.CC * p.out_plane_stride);
-                const int vecs = p.BR * p.W * GV;
-                T *ybase = y + (((size_t)n * p.H + (size_t)b * p.BR) * p.W) * p.C + c0;
-                for (int v = tid; v < vecs; v += nt) {
-                    const int pix = p.div_gv.div(v), g = v - pix * GV;
-                    const int rl = p.div_w.div(pix), col = pix - rl * p.W;
+            if (OP == OP_FPROP) {
+                // ---- store band b: band buffer -> NHWC, 16 bytes per thread ---------------------
+                const float *src = outb + (gbi & 1) * band_floats;
+                int rl = rl_first, col = col_first;
+                for (int pix = pix_first; pix < band_pixels; pix += pix_step) {
                     float f[VE];
 #pragma unroll
-                    for (int j = 0; j < VE; j++) {
-                        const int4 m = map_out[g * VE + j];
-                        f[j] = src[m.x * rl + m.y * col + m.z] + bias_s[g * VE + j];
-                    }
-                    *reinterpret_cast<uint4 *>(ybase + (size_t)pix * p.C + g * VE) = Vec16<T>::pack(f);
+                    for (int j = 0; j < VE; j++) f[j] = src[mo[j].x * rl + mo[j].y * col + mo[j].z] + bs[j];
+                    *reinterpret_cast<uint4 *>(gbase + ((size_t)b * band_pixels + pix) * p.C) = Vec16<T>::pack(f);
+                    rl += p.step_rows; col += p.step_cols;
+                    if (col >= p.W) { col -= p.W; rl++; }
                 }
             }
         }
-        __syncthreads();
     }
+    if (OP == OP_WGRAD && cur_chunk >= 0) flush();
+}
+
+// Second level of the weight gradient: dw[c][k] = sum over the CTAs that visited c's chunk,
+// in CTA order, of their partial for the stored tap that original tap k maps to.
+__global__ void tiled_wgrad_final_kernel(const float *__restrict__ partial, const uint16_t *__restrict__ cls,
+                                         const int8_t *__restrict__ canon, float *__restrict__ dw,
+                                         float *__restrict__ db, int C, int K, int CC, int N, int total_items,
+                                         int ctas, int max_visits, const MergeTables mt) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= C * (K + 1)) return;
+    const int c = idx / (K + 1), k = idx % (K + 1);
+    if (k == K && db == nullptr) return;
+    const int chunk = c / CC, i = c % CC;
+    int slot;
+    if (k == K) {
+        slot = kMaxTaps;                                   // bias-gradient sum
+    } else {
+        const int o = canon[cls[c]];
+        const int kk = (canon_mode(o) & MODE_REV) ? K - 1 - k : k;
+        slot = mt.t[canon_kind(o)][kk + kHalf - K / 2];
+    }
+    const int item_lo = chunk * N, item_hi = item_lo + N;
+    float sum = 0.f;
+    for (int b = 0; b < ctas; b++) {
+        const int lo = wgrad_item_lo(b, ctas, total_items), hi = wgrad_item_lo(b + 1, ctas, total_items);
+        if (hi <= item_lo || lo >= item_hi || hi == lo) continue;
+        const int v = chunk - lo / N;
+        sum += partial[(((size_t)b * max_visits + v) * CC + i) * kPartialStride + slot];
+    }
+    if (k == K) db[c] = sum; else dw[(size_t)c * K + k] = sum;
 }
 
 }  // namespace o1d

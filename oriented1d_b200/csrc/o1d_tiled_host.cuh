@@ -37,12 +37,22 @@ struct TiledConfig {
 };
 
 inline int round32(int v) { return (v + 31) & ~31; }
+// Smallest stride >= v with stride*VE congruent to 32/GV modulo 32 (GV = CC/VE vectors per
+// pixel): the GV channel groups of one pixel then start 32/GV banks apart.
+inline int skew_stride(int v, int CC, int VE) {
+    const int GV = CC / VE;
+    if (GV <= 1 || GV > 32) return v;
+    const int want = 32 / GV;
+    for (int s = v; s < v + 64; s++)
+        if ((s * VE) % 32 == want % 32) return s;
+    return v;
+}
 inline int make_odd(int v) { return v | 1; }
 
 // Picks R, BR (band rows), CC (chunk channels) and the stage count; returns false when the
 // tiled kernels do not apply and the general kernels must be used.
 inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, int H, int W, int C, int K,
-                            int stride, int layout, int esize, int smem_limit, int sms, TiledConfig *out) {
+                            int stride, int layout, int esize, int smem_limit, int sms, int op, TiledConfig *out) {
     if (stride != 1 || layout != O1D_NHWC || K > kMaxTaps || !ph.all_canon || ph.comps_off == 0) return false;
     if (H > 256 || W > 256 || (C * esize) % 16 != 0) return false;
     int R = 0;
@@ -53,7 +63,7 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
     const KindComp *comps = reinterpret_cast<const KindComp *>(static_cast<const char *>(plan_host) + ph.comps_off);
     const int G = (R == 8) ? 17 : 16;
     const int pitch_n = make_odd(W + G), pitch_t = make_odd(H + G);
-    const int PLS = (H * pitch_n > W * pitch_t) ? H * pitch_n : W * pitch_t;
+    const int PLS0 = (H * pitch_n > W * pitch_t) ? H * pitch_n : W * pitch_t;
 
     bool found = false;
     TiledConfig best{};
@@ -73,7 +83,11 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             }
             if (worst > kTiledThreads) continue;
             const int out_pitch_n = make_odd(W), out_pitch_t = make_odd(BR);
-            const int OPS = (BR * out_pitch_n > W * out_pitch_t) ? BR * out_pitch_n : W * out_pitch_t;
+            // Plane strides are padded so that the channel groups a warp touches together in
+            // the restage / store loops (VE channels apart) fall into different banks.
+            const int PLS = skew_stride(PLS0, CC, VE);
+            const int OPS = skew_stride((BR * out_pitch_n > W * out_pitch_t) ? BR * out_pitch_n : W * out_pitch_t, CC, VE);
+            if (op == OP_WGRAD && (2 * CC * OPS) / kTiledThreads < 1) continue;
             TiledParams p{};
             p.off_planar = 0;
             const int planar_floats = 32 + CC * PLS;
@@ -82,7 +96,7 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             p.off_out = p.zero_floats_total;
             p.off_wts = p.off_out + 2 * CC * OPS;
             p.off_misc = p.off_wts + CC * 32;
-            const int misc_ints = 4 + kMaxCC + 2 * kMaxCC * 4 + kMaxCC;
+            const int misc_ints = 4 + kMaxCC + 2 * kMaxCC * 4 + kMaxCC + 2 * kMaxCC;
             int bytes = (p.off_misc + misc_ints) * 4;
             bytes = (bytes + 127) & ~127;
             p.off_stage_bytes = bytes;
@@ -110,7 +124,9 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             p.div_gv = FastDiv::make(CC / VE); p.div_w = FastDiv::make(W);
             p.div_nseg_line = FastDiv::make(nseg_line); p.div_nseg_diag = FastDiv::make(nseg_diag);
             p.div_br = FastDiv::make(BR); p.div_wline = FastDiv::make(W); p.div_wdiag = FastDiv::make(W + R - 1);
-            p.div_chunks = FastDiv::make(p.nchunks); p.div_nb = FastDiv::make(NB);
+            p.div_chunks = FastDiv::make(p.nchunks); p.div_nb = FastDiv::make(NB); p.div_n = FastDiv::make(N);
+            const int pix_step = kTiledThreads / (CC / VE);
+            p.step_rows = pix_step / W; p.step_cols = pix_step % W;
             best.p = p;
             best.smem_bytes = p.off_bar_bytes + 8 * kMaxStages;
             best.stage_stride = stage_stride;
@@ -119,7 +135,21 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             found = true;
         }
     }
-    if (found) *out = best;
+    if (found) {
+        if (op == OP_WGRAD) {   // contiguous item ranges; partial slots = chunks a CTA can touch
+            int mv = 1;
+            for (int b = 0; b < best.grid; b++) {
+                const int lo = wgrad_item_lo(b, best.grid, best.p.total_items);
+                const int hi = wgrad_item_lo(b + 1, best.grid, best.p.total_items);
+                if (hi > lo) {
+                    const int v = (hi - 1) / N - lo / N + 1;
+                    if (v > mv) mv = v;
+                }
+            }
+            best.p.max_visits = mv;
+        }
+        *out = best;
+    }
     return found;
 }
 
@@ -139,14 +169,18 @@ inline bool make_nhwc_tensor_map(CUtensorMap *map, const void *base, int N, int 
     return r == CUDA_SUCCESS;
 }
 
-template <typename T, int R>
-cudaError_t launch_tiled_fprop(const TiledConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
-                               const PlanView &pv, T *y, cudaStream_t st) {
-    auto kern = tiled_fprop_nhwc_kernel<T, R, kHalf>;
+template <typename T, int R, int OP>
+cudaError_t launch_tiled(const TiledConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
+                         const PlanView &pv, T *io, float *partial, cudaStream_t st) {
+    auto kern = tiled_nhwc_kernel<T, R, kHalf, OP>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
     if (e != cudaSuccess) return e;
-    kern<<<cfg.grid, kTiledThreads, cfg.smem_bytes, st>>>(map, w, bias, pv.cls, pv.canon, y, cfg.p);
+    kern<<<cfg.grid, kTiledThreads, cfg.smem_bytes, st>>>(map, w, bias, pv.cls, pv.canon, io, partial, cfg.p);
     return cudaGetLastError();
+}
+
+inline size_t tiled_wgrad_partial_bytes(const TiledConfig &cfg) {
+    return (size_t)cfg.grid * cfg.p.max_visits * cfg.p.CC * kPartialStride * sizeof(float);
 }
 
 }  // namespace o1d

@@ -277,6 +277,7 @@ def test_tiled_route_equals_general_route(hw, C, mode, dtype):
     N, K = 5, 31
     g = torch.Generator(device="cpu").manual_seed(hw * C)
     x = torch.randn((N, hw, hw, C), generator=g).to(DEV).to(dtype)
+    dy = torch.randn((N, hw, hw, C), generator=g).to(DEV).to(dtype)
     w = (0.02 * torch.randn((C, 1, 1, K), generator=g)).to(DEV)
     bias = torch.randn((C,), generator=g).to(DEV)
     plan = o1d.Plan(angle_list(mode, C), K)
@@ -284,11 +285,17 @@ def test_tiled_route_equals_general_route(hw, C, mode, dtype):
         o1d.ops.set_route(True)
         y_ref = o1d.fprop(x, w, bias, plan, 1, True, True).float()
         dx_ref = o1d.dgrad(x, w, plan, hw, hw, 1, True, False).float()
+        dw_ref, db_ref = o1d.wgrad(dy, x, plan, 1, True, True)
     finally:
         o1d.ops.set_route(False)
     y = o1d.fprop(x, w, bias, plan, 1, True, True).float()
     dx = o1d.dgrad(x, w, plan, hw, hw, 1, True, False).float()
+    dw, db = o1d.wgrad(dy, x, plan, 1, True, True)
+    dw2, db2 = o1d.wgrad(dy, x, plan, 1, True, True)
     assert o1d.ops.device_status() == 0
+    assert torch.equal(dw, dw2) and torch.equal(db, db2)          # deterministic
+    assert float((dw - dw_ref).abs().max()) <= 1e-4 * float(dw_ref.abs().max())
+    assert float((db - db_ref).abs().max()) <= 1e-4 * float(db_ref.abs().max())
     if dtype == torch.float32:
         assert float((y - y_ref).abs().max()) <= 1e-5 * float(y_ref.abs().max())
         assert float((dx - dx_ref).abs().max()) <= 1e-5 * float(dx_ref.abs().max())
@@ -307,5 +314,7 @@ def test_tiled_short_kernels(oracle, K):
     wd = torch.from_numpy(w).to(DEV)
     y = o1d.fprop(_to_dev(x, True), wd, None, plan, 1, True)
     dx = o1d.dgrad(_to_dev(dy, True), wd, plan, hw, hw, 1, True)
+    dw, _ = o1d.wgrad(_to_dev(dy, True), _to_dev(x, True), plan, 1, True)
     assert rel_err(_to_nchw(y, True), oracle.fprop(x, w, th, 1)) <= TOL_FPROP
     assert rel_err(_to_nchw(dx, True), oracle.dgrad(dy, w, th, 1)) <= TOL_DGRAD
+    assert rel_err(dw.cpu().numpy(), oracle.wgrad_f64(dy, x, th, K, 1)) <= TOL_WGRAD
