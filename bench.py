@@ -222,21 +222,35 @@ def run_ours(args):
             flat = torch.cat(grads)
             dist.all_reduce(flat)
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, graph_cycle=0):
+        """Device time of `steps` calls of fn (CUDA events on the launching stream, barrier and
+        synchronize on both sides, max over ranks).  With graph_cycle > 0 the calls are captured
+        once into a CUDA graph of `graph_cycle` consecutive calls (one full rotation of the input
+        sets) and replayed, so that host launch latency does not sit between kernels."""
         for _ in range(warmup):
             fn()
+        torch.cuda.synchronize()
+        runner, per = fn, 1
+        if graph_cycle > 0:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(graph_cycle):
+                    fn()
+            graph.replay()                      # one untimed replay
+            runner, per = graph.replay, graph_cycle
+        reps = max(1, -(-steps // per))
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
-            fn()
+        for _ in range(reps):
+            runner()
         e1.record()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-        ms = e0.elapsed_time(e1)
+        ms = e0.elapsed_time(e1) * steps / (reps * per)     # normalised to `steps` calls
         if world > 1:
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -247,8 +261,12 @@ def run_ours(args):
     with ClockSampler(local) as clk:
         launches["n"] = 0
         warm = max(args.warmup, 3)
-        ms = timed(lambda: step(layers32), args.steps, warm)
-        n_launch = launches["n"] * args.steps // (args.steps + warm)
+        cycle = max(L.nsets for L in layers32) if (world == 1 and not args.no_graph) else 0
+        launches["n"] = 0
+        step(layers32)
+        per_step = launches["n"]
+        ms = timed(lambda: step(layers32), args.steps, warm, graph_cycle=cycle)
+        n_launch = per_step * args.steps
         time.sleep(0.25)
     clocks = clk.summary()
     value = BATCH * world * args.steps / (ms / 1e3)
@@ -256,7 +274,7 @@ def run_ours(args):
     # ---- per-kernel timings (rank 0 only, after the headline) -------------------------
     kernels, roof = {}, None
     if rank == 0:
-        reps = 20
+        reps = 40
         for dtype, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
             layers = layers32 if dtype == torch.float32 else [Layer(hw, C, dtype) for hw, C in STAGES]
             for L in layers:
@@ -276,7 +294,7 @@ def run_ours(args):
                     o1d.wgrad(dy, x, L.plan, 1, True, True)
 
                 for name, fn in (("fprop", f_fprop), ("dgrad", f_dgrad), ("wgrad", f_wgrad)):
-                    t_ms = timed(fn, reps, 3) / reps
+                    t_ms = timed(fn, reps, 3, graph_cycle=0 if args.no_graph else L.nsets) / reps
                     gbs = ab / (t_ms * 1e-3) / 1e9
                     kernels[f"{name}_{tag}_{L.hw}x{L.hw}x{L.C}"] = {
                         "us": round(t_ms * 1e3, 2), "alg_bytes": ab, "gbs": round(gbs, 1),
@@ -346,6 +364,7 @@ def run_ours(args):
             "config": {"workload": "stage-sweep: (56,96),(28,192),(14,384),(7,768) x batch 128 per GPU, K=31, "
                                    "stride 1, NHWC, 8 orientations round-robin; fprop+dgrad+wgrad per shape",
                        "l2": "inputs rotate over sets totalling >4x L2, so every launch reads from HBM",
+                       "launch": "eager" if (args.no_graph or world > 1) else "CUDA graph of one full input rotation, replayed",
                        "parallelism": f"dp{world} (batch-sharded; weight-gradient all-reduce when >1)"},
             "roofline": roof, "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -409,6 +428,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graphs")
     ap.add_argument("--case", default=None, help="run one kernel case alone, e.g. fprop_f32_56x56x96")
     ap.add_argument("--batch", type=int, default=64, help="batch for --case")
     ap.add_argument("--reps", type=int, default=3, help="launches for --case")
