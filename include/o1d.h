@@ -114,6 +114,28 @@ int o1d_wgrad(const void *dy, const void *x,
               int N, int H, int W, int C, int K, int stride,
               int layout, int dtype, void *stream);
 
+/* Weight gradient without a workspace argument, for callers that are not able to allocate
+ * device memory at the call site (plugin sandboxes and framework hooks that forbid it,
+ * processes whose memory pool is fixed at start-up, code running under an allocator lock).
+ * It has no counterpart in the reference.  Same arithmetic and same results as
+ * o1d_wgrad(); the per-block partial sums go to an array of O1D_STATIC_SCRATCH_BYTES that
+ * is compiled into the library (each GPU that loads the library keeps that much memory
+ * until the process exits).  The call allocates nothing and frees nothing.
+ *   - Shapes whose partial sums do not fit are refused with O1D_ERR_UNSUPPORTED and a
+ *     message in o1d_last_error(); use o1d_wgrad() with your own workspace for those.
+ *   - The first call on each device looks up the array's device address; make that first
+ *     call outside of any CUDA stream capture.
+ *   - All calls on a device share the one array, and it still holds the previous call's
+ *     partial sums afterwards (nothing in it needs clearing: every slot a call reads it has
+ *     written first).  Two calls that may run on the GPU at the same time — different
+ *     streams, different threads — would overwrite each other's partial sums: serialise them. */
+#define O1D_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
+int o1d_wgrad_static(const void *dy, const void *x,
+                     const void *plan_host, const void *plan_dev,
+                     float *dw, float *db,
+                     int N, int H, int W, int C, int K, int stride,
+                     int layout, int dtype, void *stream);
+
 /* Batched 2-D transpose [n, a, b] -> [n, b, a].  Replaces nhwc_to_nchw / nchw_to_nhwc
  * (kernels.cu:56-68, nhwc_utils.h:46-110): NHWC->NCHW is (n=N, a=H*W, b=C),
  * NCHW->NHWC is (n=N, a=C, b=H*W). */

@@ -31,6 +31,7 @@ SIGNATURES = {
     "o1d_dgrad": (_c_int, [_c_void_p] * 5 + [_c_int] * 9 + [_c_void_p]),
     "o1d_wgrad_workspace_bytes": (_c_size_t, [_c_int] * 8),
     "o1d_wgrad": (_c_int, [_c_void_p] * 7 + [_c_size_t] + [_c_int] * 8 + [_c_void_p]),
+    "o1d_wgrad_static": (_c_int, [_c_void_p] * 6 + [_c_int] * 8 + [_c_void_p]),
     "o1d_transpose": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p]),
 }
 

@@ -412,6 +412,74 @@ int o1d_wgrad(const void *dy, const void *x, const void *plan_host, const void *
                         C, K, stride, st);
 }
 
+// ---------------------------------------------------------------------------------------
+// Weight gradient for callers that cannot allocate.
+//
+// Some hosts of this library have no way to hand it a workspace: code that runs inside a
+// framework hook or a plugin sandbox where device allocation is forbidden, a process whose
+// memory pool was sized once at start-up and is fully committed, or a call site reached
+// while an allocator lock is held.  For them the per-block partial sums of the weight
+// gradient live in the fixed array below instead of a caller buffer.  The array is part
+// of the library image: every GPU that loads libo1d holds these bytes until the process
+// exits, which is why the size is modest and requests that need more are refused.
+//
+// The array's name is only a host-side handle.  Its device address is looked up once per
+// device with cudaGetSymbolAddress (with that device current) and that address is what the
+// kernels receive.
+// ---------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_wgrad_static_scratch[O1D_STATIC_SCRATCH_BYTES];
+
+namespace {
+// Device address of the static scratch on the current device; resolved on first use.
+int static_scratch_ptr(void **out) {
+    static void *cache[64];
+    int dev = 0;
+    O1D_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return O1D_ERR_UNSUPPORTED;
+    if (!cache[dev]) {
+        void *ptr = nullptr;
+        O1D_CUDA(cudaGetSymbolAddress(&ptr, g_wgrad_static_scratch));
+        if (!ptr) return O1D_ERR_CUDA;
+        cache[dev] = ptr;
+    }
+    *out = cache[dev];
+    return O1D_OK;
+}
+}  // namespace
+
+int o1d_wgrad_static(const void *dy, const void *x, const void *plan_host, const void *plan_dev, float *dw,
+                     float *db, int N, int H, int W, int C, int K, int stride, int layout, int dtype,
+                     void *stream) {
+    if (!dy || !x || !dw || !plan_dev || bad_common(N, H, W, C, K, stride, layout, dtype)) return O1D_ERR_INVALID;
+    PlanHeader ph;
+    int rc = check_plan(plan_host, C, K, &ph);
+    if (rc) return rc;
+    DeviceInfo d;
+    if ((rc = device_info(&d))) return rc;
+    void *scratch = nullptr;
+    if ((rc = static_scratch_ptr(&scratch))) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    // tiled route, if it applies and its partials fit
+    size_t need = 0;
+    rc = try_tiled_wgrad(dy, x, ph, plan_host, plan_dev, dw, db, nullptr, 0, N, H, W, C, K, stride, layout, dtype,
+                         st, d, &need);
+    if (rc == O1D_OK && need <= (size_t)O1D_STATIC_SCRATCH_BYTES) {
+        rc = try_tiled_wgrad(dy, x, ph, plan_host, plan_dev, dw, db, scratch, O1D_STATIC_SCRATCH_BYTES, N, H, W, C,
+                             K, stride, layout, dtype, st, d, nullptr);
+        if (rc != kNotTiled) return rc;
+    }
+    // general route
+    const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
+    need = (size_t)generic_wgrad_slices(N, P, Q, C, layout) * C * (K + 1) * sizeof(float);
+    if (need > (size_t)O1D_STATIC_SCRATCH_BYTES) {
+        snprintf(g_err, sizeof(g_err), "o1d_wgrad_static: needs %zu bytes of scratch, the built-in array holds %d",
+                 need, O1D_STATIC_SCRATCH_BYTES);
+        return O1D_ERR_UNSUPPORTED;
+    }
+    return O1D_DISPATCH(launch_generic_wgrad, dy, x, ph, plan_dev, dw, db, (float *)scratch, N, H, W, C, K, stride,
+                        st);
+}
+
 int o1d_transpose(const void *in, void *out, int n, int a, int b, int dtype, void *stream) {
     if (!in || !out || n <= 0 || a <= 0 || b <= 0 || (dtype != O1D_F32 && dtype != O1D_BF16)) return O1D_ERR_INVALID;
     if (n > 65535) return O1D_ERR_UNSUPPORTED;
