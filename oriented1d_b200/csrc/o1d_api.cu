@@ -160,14 +160,7 @@ int try_tiled(const void *x, const float *w, const float *bias, const PlanHeader
     cfg.p.flip = flip;
     cfg.p.add_identity = add_identity;
     PlanView pv = plan_view(plan_dev, ph);
-    cudaError_t e;
-    if (dtype == O1D_F32)
-        e = cfg.p.R == 8 ? launch_tiled<float, 8, OP_FPROP>(cfg, map, w, bias, pv, (float *)y, nullptr, st)
-                         : launch_tiled<float, 7, OP_FPROP>(cfg, map, w, bias, pv, (float *)y, nullptr, st);
-    else
-        e = cfg.p.R == 8
-                ? launch_tiled<__nv_bfloat16, 8, OP_FPROP>(cfg, map, w, bias, pv, (__nv_bfloat16 *)y, nullptr, st)
-                : launch_tiled<__nv_bfloat16, 7, OP_FPROP>(cfg, map, w, bias, pv, (__nv_bfloat16 *)y, nullptr, st);
+    cudaError_t e = launch_tiled<OP_FPROP>(cfg, dtype, map, w, bias, pv, y, nullptr, st);
     if (e != cudaSuccess) return cuda_fail(e, "tiled fprop launch");
     return O1D_OK;
 }
@@ -190,19 +183,11 @@ int try_tiled_wgrad(const void *dy, const void *x, const PlanHeader &ph, const v
     if (!make_nhwc_tensor_map(&map, x, N, H, W, C, esize, cfg.p.CC, cfg.p.BR)) return kNotTiled;
     PlanView pv = plan_view(plan_dev, ph);
     float *partial = (float *)workspace;
-    cudaError_t e;
-    if (dtype == O1D_F32)
-        e = cfg.p.R == 8 ? launch_tiled<float, 8, OP_WGRAD>(cfg, map, nullptr, nullptr, pv, (float *)dy, partial, st)
-                         : launch_tiled<float, 7, OP_WGRAD>(cfg, map, nullptr, nullptr, pv, (float *)dy, partial, st);
-    else
-        e = cfg.p.R == 8 ? launch_tiled<__nv_bfloat16, 8, OP_WGRAD>(cfg, map, nullptr, nullptr, pv,
-                                                                     (__nv_bfloat16 *)dy, partial, st)
-                         : launch_tiled<__nv_bfloat16, 7, OP_WGRAD>(cfg, map, nullptr, nullptr, pv,
-                                                                     (__nv_bfloat16 *)dy, partial, st);
+    cudaError_t e = launch_tiled<OP_WGRAD>(cfg, dtype, map, nullptr, nullptr, pv, const_cast<void *>(dy), partial, st);
     if (e != cudaSuccess) return cuda_fail(e, "tiled wgrad launch");
-    constexpr MergeTables mt = make_merge_tables<kHalf>();
+    const MergeTables mt = merge_tables_for(cfg.jh);
     const int tot = C * (K + 1);
-    tiled_wgrad_final_kernel<<<ceil_div(tot, 128), 128, 0, st>>>(partial, pv.cls, pv.canon, dw, db, C, K, cfg.p.CC, N,
+    tiled_wgrad_final_kernel<<<ceil_div(tot, 128), 128, 0, st>>>(partial, pv.chan, dw, db, C, K, cfg.p.CC, N,
                                                                  cfg.p.total_items, cfg.grid, cfg.p.max_visits, mt);
     O1D_CUDA(cudaGetLastError());
     return O1D_OK;
@@ -256,7 +241,7 @@ int o1d_offsets(const float *theta_host, int C, int K, int8_t *dh, int8_t *dw) {
 size_t o1d_plan_bytes(int C, int K) {
     if (C <= 0 || K <= 0) return 0;
     return sizeof(PlanHeader) + align16((uint32_t)C * 2) + align16((uint32_t)C * K * 2) + align16((uint32_t)C) +
-           align16(4 * sizeof(KindComp));
+           align16(4 * sizeof(KindComp)) + align16((uint32_t)C);
 }
 
 int o1d_plan_build(const float *theta_host, int C, int K, void *plan_host) {
@@ -294,7 +279,8 @@ int o1d_plan_build(const float *theta_host, int C, int K, void *plan_host) {
     h.taps_off = h.cls_off + align16((uint32_t)C * 2);
     h.canon_off = h.taps_off + align16((uint32_t)ncls * K * 2);
     h.comps_off = h.canon_off + align16((uint32_t)ncls);
-    h.total_bytes = h.comps_off + align16(4 * sizeof(KindComp));
+    h.chan_off = h.comps_off + align16(4 * sizeof(KindComp));
+    h.total_bytes = h.chan_off + align16((uint32_t)C);
     char *b = static_cast<char *>(plan_host);
     memset(b, 0, o1d_plan_bytes(C, K));
     memcpy(b + h.cls_off, cls.data(), (size_t)C * 2);
@@ -335,6 +321,7 @@ int o1d_plan_build(const float *theta_host, int C, int K, void *plan_host) {
         }
     }
     memcpy(b + h.comps_off, comps, sizeof(comps));
+    for (int c = 0; c < C; c++) b[h.chan_off + c] = canon_of[cls[c]];
     h.all_canon = all_canon;
     memcpy(b, &h, sizeof(h));
     return O1D_OK;

@@ -13,11 +13,13 @@ namespace o1d {
 // Plan blob.  The same bytes live on the host and on the device.
 //   [PlanHeader (64 B)] [cls: C x uint16, padded to 16 B] [taps: ncls x K x (dh,dw) int8,
 //   padded to 16 B] [canon: ncls x int8, padded to 16 B] [comps: 4 x KindComp]
+//   [chan: C x int8, padded to 16 B]
 // cls[c]    orientation class of channel c
 // taps      rasterised offsets of each class, exactly the reference's
 //           (int)(-sinf(theta)*j), (int)(cosf(theta)*j)  (kernels.cpp:43-44)
 // canon[i]  0..7 when class i's line equals the built-in table of the i*22.5 degree
 //           orientation (those have compile-time specialised kernels), else -1
+// chan[c]   canon[cls[c]]: the canonical id of channel c in one lookup
 // comps[i]  for chunk width kChunkWidths[i]: the distinct (axis, slant, diagonal) channel
 //           counts a chunk of that many consecutive channels can have (tiled kernels size
 //           their thread groups from it); n = -1 when C is not a multiple of the width or
@@ -38,8 +40,8 @@ struct PlanHeader {
     int32_t max_dh, max_dw;   // largest |dh|, |dw| over all classes
     int32_t all_canon;        // 1 when every class has canon >= 0
     uint32_t cls_off, taps_off, canon_off, total_bytes;
-    uint32_t comps_off;
-    uint32_t reserved[4];
+    uint32_t comps_off, chan_off;
+    uint32_t reserved[3];
 };
 static_assert(sizeof(PlanHeader) == 64, "plan header is 64 bytes");
 
@@ -49,6 +51,7 @@ struct PlanView {   // pointers into one blob (host or device)
     const uint16_t *cls;
     const int8_t *taps;   // [ncls][K][2]
     const int8_t *canon;
+    const int8_t *chan;   // [C] canonical id per channel
     int ncls;
 };
 
@@ -56,7 +59,8 @@ inline PlanView plan_view(const void *blob, const PlanHeader &h) {
     const char *b = static_cast<const char *>(blob);
     return PlanView{reinterpret_cast<const uint16_t *>(b + h.cls_off),
                     reinterpret_cast<const int8_t *>(b + h.taps_off),
-                    reinterpret_cast<const int8_t *>(b + h.canon_off), h.ncls};
+                    reinterpret_cast<const int8_t *>(b + h.canon_off),
+                    reinterpret_cast<const int8_t *>(b + h.chan_off), h.ncls};
 }
 
 // ---------------------------------------------------------------------------------

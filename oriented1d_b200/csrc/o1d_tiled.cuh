@@ -252,9 +252,8 @@ __host__ __device__ inline int wgrad_item_lo(int cta, int ctas, int total) {
 template <typename T, int R, int JH, int OP>
 __global__ void __launch_bounds__(kTiledThreads, 1)
 tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restrict__ wgt,
-                  const float *__restrict__ bias, const uint16_t *__restrict__ cls,
-                  const int8_t *__restrict__ canon, T *__restrict__ io, float *__restrict__ partial,
-                  const TiledParams p) {
+                  const float *__restrict__ bias, const int8_t *__restrict__ chan,
+                  T *__restrict__ io, float *__restrict__ partial, const TiledParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float *sm = reinterpret_cast<float *>(smem_raw);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + p.off_bar_bytes);
@@ -374,7 +373,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
         }
 
         // ---- per-chunk channel tables --------------------------------------------------
-        if (OP == OP_FPROP || new_chunk) {
+        if (new_chunk) {
             if (tid < 32) {
                 int cnt_before = 0;
                 int counts[3];
@@ -383,7 +382,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                     int cnt = 0;
                     for (int base = 0; base < p.CC; base += 32) {
                         const int i = base + tid;
-                        const int o = (i < p.CC) ? canon[cls[c0 + i]] : -1;
+                        const int o = (i < p.CC) ? chan[c0 + i] : -1;
                         const bool mine = o >= 0 && canon_kind(o) == kd;
                         const unsigned m = __ballot_sync(0xffffffffu, mine);
                         if (mine) ch_sorted[cnt_before + cnt + __popc(m & ((1u << tid) - 1))] = i;
@@ -396,7 +395,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 for (int kd = 0; kd < 3; kd++) if (tid == kd) misc[kd] = counts[kd];
             }
             for (int i = tid; i < p.CC; i += nt) {
-                const int o = canon[cls[c0 + i]];
+                const int o = chan[c0 + i];
                 const int mode = canon_mode(o);
                 const int pbase = p.off_planar + 32 + i * p.plane_stride;
                 const int obase = i * p.out_plane_stride;
@@ -418,7 +417,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                     const int i = e >> 5, k = e & 31;
                     float v = 0.f;
                     if (k < kMaxTaps) {
-                        const int o = canon[cls[c0 + i]];
+                        const int o = chan[c0 + i];
                         int kk = k - kHalf + pad;                      // tap of the K-long kernel
                         if (kk >= 0 && kk < p.K) {
                             const bool rev = ((canon_mode(o) & MODE_REV) != 0) != (p.flip != 0);
@@ -434,10 +433,10 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
         if (p.rezero) {
             for (int i = tid; i < p.CC * p.plane_stride; i += nt) sm[p.off_planar + 32 + i] = 0.f;
         }
-        __syncthreads();
+        if (new_chunk || p.rezero) __syncthreads();
 
         // ---- thread -> (kind, channel, segment); groups of equal kind start on warp boundaries
-        if (OP == OP_FPROP || new_chunk) {
+        if (new_chunk) {
             const int nA = misc[0], nS = misc[1], nD = misc[2];
             const int slotsA = (nA * p.nseg_line + 31) & ~31, slotsS = (nS * p.nseg_line + 31) & ~31;
             kind = -1; ch = 0; seg = 0;
@@ -454,7 +453,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 if (j < nD) { kind = KIND_DIAG; ch = ch_sorted[nA + nS + j]; seg = idx - j * p.nseg_diag; group_n = p.nseg_diag; }
             }
             if (kind >= 0 && seg == 0) ch_range[ch] = make_int2(tid, group_n);
-            if (OP == OP_WGRAD) { cur_chunk = chunk; visit++; }
+            cur_chunk = chunk; visit++;
         }
 
         // ---- restage: staging bands -> planes -------------------------------------------
@@ -629,8 +628,8 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
 
 // Second level of the weight gradient: dw[c][k] = sum over the CTAs that visited c's chunk,
 // in CTA order, of their partial for the stored tap that original tap k maps to.
-__global__ void tiled_wgrad_final_kernel(const float *__restrict__ partial, const uint16_t *__restrict__ cls,
-                                         const int8_t *__restrict__ canon, float *__restrict__ dw,
+__global__ void tiled_wgrad_final_kernel(const float *__restrict__ partial, const int8_t *__restrict__ chan,
+                                         float *__restrict__ dw,
                                          float *__restrict__ db, int C, int K, int CC, int N, int total_items,
                                          int ctas, int max_visits, const MergeTables mt) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -642,13 +641,14 @@ __global__ void tiled_wgrad_final_kernel(const float *__restrict__ partial, cons
     if (k == K) {
         slot = kMaxTaps;                                   // bias-gradient sum
     } else {
-        const int o = canon[cls[c]];
+        const int o = chan[c];
         const int kk = (canon_mode(o) & MODE_REV) ? K - 1 - k : k;
         slot = mt.t[canon_kind(o)][kk + kHalf - K / 2];
     }
     const int item_lo = chunk * N, item_hi = item_lo + N;
     float sum = 0.f;
-    for (int b = 0; b < ctas; b++) {
+    // slot < 0: the tap cannot reach inside an image of this size; its gradient is exactly 0
+    for (int b = 0; b < ctas && slot >= 0; b++) {
         const int lo = wgrad_item_lo(b, ctas, total_items), hi = wgrad_item_lo(b + 1, ctas, total_items);
         if (hi <= item_lo || lo >= item_hi || hi == lo) continue;
         const int v = chunk - lo / N;

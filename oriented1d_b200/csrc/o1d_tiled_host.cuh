@@ -33,8 +33,23 @@ struct TiledConfig {
     int smem_bytes;
     int grid;
     int stage_stride;
+    int jh;          // taps |j| <= jh are evaluated (instantiated: 7, 9, 15)
     double util;
 };
+
+// Largest |j| whose tap can land inside an image of extent S x S for at least one base line,
+// capped by the kernel length; rounded up to an instantiated value.
+inline int tiled_tap_reach(int H, int W, int K) {
+    const int S = H > W ? H : W;
+    int need = 0;
+    for (int j = kHalf; j >= 1 && !need; j--)
+        for (int b = 0; b < 3; b++) {
+            const int dh = kCanonDh[b][kHalf + j], dw = kCanonDw[b][kHalf + j];
+            if ((dh < 0 ? -dh : dh) < S && (dw < 0 ? -dw : dw) < S) need = j;
+        }
+    if (need > K / 2) need = K / 2;
+    return need <= 7 ? 7 : need <= 9 ? 9 : kHalf;
+}
 
 inline int round32(int v) { return (v + 31) & ~31; }
 // Smallest stride >= v with stride*VE congruent to 32/GV modulo 32 (GV = CC/VE vectors per
@@ -131,6 +146,13 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             best.smem_bytes = p.off_bar_bytes + 8 * kMaxStages;
             best.stage_stride = stage_stride;
             best.grid = p.total_items < sms ? p.total_items : sms;
+            if (op == OP_FPROP && p.nchunks <= best.grid) {
+                // A grid that is a multiple of the chunk count keeps every CTA on one chunk, so
+                // its channel tables and weights are built once; worth giving up to 15% of the SMs.
+                const int g = (best.grid / p.nchunks) * p.nchunks;
+                if (g * 100 >= best.grid * 85) best.grid = g;
+            }
+            best.jh = tiled_tap_reach(H, W, K);
             best.util = util;
             found = true;
         }
@@ -169,14 +191,43 @@ inline bool make_nhwc_tensor_map(CUtensorMap *map, const void *base, int N, int 
     return r == CUDA_SUCCESS;
 }
 
-template <typename T, int R, int OP>
-cudaError_t launch_tiled(const TiledConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
-                         const PlanView &pv, T *io, float *partial, cudaStream_t st) {
-    auto kern = tiled_nhwc_kernel<T, R, kHalf, OP>;
+template <typename T, int R, int JH, int OP>
+cudaError_t launch_tiled_one(const TiledConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
+                             const PlanView &pv, void *io, float *partial, cudaStream_t st) {
+    auto kern = tiled_nhwc_kernel<T, R, JH, OP>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
     if (e != cudaSuccess) return e;
-    kern<<<cfg.grid, kTiledThreads, cfg.smem_bytes, st>>>(map, w, bias, pv.cls, pv.canon, io, partial, cfg.p);
+    kern<<<cfg.grid, kTiledThreads, cfg.smem_bytes, st>>>(map, w, bias, pv.chan, (T *)io, partial, cfg.p);
     return cudaGetLastError();
+}
+
+template <typename T, int R, int OP>
+cudaError_t launch_tiled_jh(const TiledConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
+                            const PlanView &pv, void *io, float *partial, cudaStream_t st) {
+    switch (cfg.jh) {
+        case 7: return launch_tiled_one<T, R, 7, OP>(cfg, map, w, bias, pv, io, partial, st);
+        case 9: return launch_tiled_one<T, R, 9, OP>(cfg, map, w, bias, pv, io, partial, st);
+        default: return launch_tiled_one<T, R, kHalf, OP>(cfg, map, w, bias, pv, io, partial, st);
+    }
+}
+
+// Dispatch over (element type, segment length, tap reach) for one operation.
+template <int OP>
+cudaError_t launch_tiled(const TiledConfig &cfg, int dtype, const CUtensorMap &map, const float *w,
+                         const float *bias, const PlanView &pv, void *io, float *partial, cudaStream_t st) {
+    if (dtype == O1D_F32)
+        return cfg.p.R == 8 ? launch_tiled_jh<float, 8, OP>(cfg, map, w, bias, pv, io, partial, st)
+                            : launch_tiled_jh<float, 7, OP>(cfg, map, w, bias, pv, io, partial, st);
+    return cfg.p.R == 8 ? launch_tiled_jh<__nv_bfloat16, 8, OP>(cfg, map, w, bias, pv, io, partial, st)
+                        : launch_tiled_jh<__nv_bfloat16, 7, OP>(cfg, map, w, bias, pv, io, partial, st);
+}
+
+inline MergeTables merge_tables_for(int jh) {
+    switch (jh) {
+        case 7: { constexpr MergeTables m = make_merge_tables<7>(); return m; }
+        case 9: { constexpr MergeTables m = make_merge_tables<9>(); return m; }
+        default: { constexpr MergeTables m = make_merge_tables<kHalf>(); return m; }
+    }
 }
 
 inline size_t tiled_wgrad_partial_bytes(const TiledConfig &cfg) {
