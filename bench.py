@@ -178,6 +178,7 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG", "WARN")     # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     peak, peak_src = measured_peak()
@@ -222,11 +223,13 @@ def run_ours(args):
             flat = torch.cat(grads)
             dist.all_reduce(flat)
 
-    def timed(fn, steps, warmup, graph_cycle=0):
+    def timed(fn, steps, warmup, graph_cycle=0, all_ranks=True):
         """Device time of `steps` calls of fn (CUDA events on the launching stream, barrier and
         synchronize on both sides, max over ranks).  With graph_cycle > 0 the calls are captured
         once into a CUDA graph of `graph_cycle` consecutive calls (one full rotation of the input
-        sets) and replayed, so that host launch latency does not sit between kernels."""
+        sets) and replayed, so that host launch latency does not sit between kernels.
+        all_ranks=False: a measurement only this rank takes (no barrier, no max-reduce)."""
+        multi = all_ranks and world > 1
         for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
@@ -239,7 +242,7 @@ def run_ours(args):
             graph.replay()                      # one untimed replay
             runner, per = graph.replay, graph_cycle
         reps = max(1, -(-steps // per))
-        if world > 1:
+        if multi:
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -248,10 +251,10 @@ def run_ours(args):
             runner()
         e1.record()
         torch.cuda.synchronize()
-        if world > 1:
+        if multi:
             dist.barrier()
         ms = e0.elapsed_time(e1) * steps / (reps * per)     # normalised to `steps` calls
-        if world > 1:
+        if multi:
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
@@ -294,7 +297,7 @@ def run_ours(args):
                     o1d.wgrad(dy, x, L.plan, 1, True, True)
 
                 for name, fn in (("fprop", f_fprop), ("dgrad", f_dgrad), ("wgrad", f_wgrad)):
-                    t_ms = timed(fn, reps, 3, graph_cycle=0 if args.no_graph else L.nsets) / reps
+                    t_ms = timed(fn, reps, 3, graph_cycle=0 if args.no_graph else L.nsets, all_ranks=False) / reps
                     gbs = ab / (t_ms * 1e-3) / 1e9
                     kernels[f"{name}_{tag}_{L.hw}x{L.hw}x{L.C}"] = {
                         "us": round(t_ms * 1e3, 2), "alg_bytes": ab, "gbs": round(gbs, 1),
