@@ -96,6 +96,7 @@ struct LinePlan {
     int tap_row[kMaxTaps], tap_dp[kMaxTaps], tap_k[kMaxTaps];   // tap_k: first k of the group
     int merge_into[kMaxTaps];     // for each k: the tap_k it is summed into, or -1 (unused)
     int span;                     // max over rows of hi-lo+1
+    int max_d;                    // max |row_d|
 };
 
 constexpr LinePlan make_line_plan(int kind, int JH) {
@@ -124,7 +125,11 @@ constexpr LinePlan make_line_plan(int kind, int JH) {
         p.ntaps++;
     }
     for (int r = 0; r < p.nrows; r++)
+    {
         if (p.row_hi[r] - p.row_lo[r] + 1 > p.span) p.span = p.row_hi[r] - p.row_lo[r] + 1;
+        const int ad = p.row_d[r] < 0 ? -p.row_d[r] : p.row_d[r];
+        if (ad > p.max_d) p.max_d = ad;
+    }
     return p;
 }
 

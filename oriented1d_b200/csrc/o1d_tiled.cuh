@@ -114,21 +114,22 @@ __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, u
 
 // ---- segment evaluation --------------------------------------------------------------
 // AXIS / SLANT: R outputs at (line, pos0 .. pos0+R-1).  `sm` is the float view of shared
-// memory, `base` the index of (line 0, position 0) of the channel plane.
+// memory, `at0` the index of (line, pos0) in the channel plane.  CHECK = false when every
+// line the segment touches is known to exist (no redirect to the zero block).
 //   forward:          acc[o]  += w[k] * x(line+dl_k, pos0+o+dp_k)
 //   weight gradient:  acc[k]  += sum_o x(line+dl_k, pos0+o+dp_k) * g[o]
-template <int OP, int KIND, int JH, int R>
-__device__ __forceinline__ void seg_line(const float *__restrict__ sm, int base, int pitch, int nlines,
-                                         int zero_idx, int line, int pos0,
+template <int OP, int KIND, int JH, int R, bool CHECK>
+__device__ __forceinline__ void seg_line(const float *__restrict__ sm, int at0, int pitch, int nlines,
+                                         int zero_idx, int line,
                                          const float (&w)[OP == OP_FPROP ? kMaxTaps : R],
                                          float (&acc)[OP == OP_FPROP ? R : kMaxTaps]) {
     using P = LP<KIND, JH>;
-    const int at0 = base + line * pitch + pos0;
     static_for<0, P::p.nrows>([&](auto ri) {
         constexpr int r = decltype(ri)::value;
         constexpr int d = P::p.row_d[r], lo = P::p.row_lo[r], hi = P::p.row_hi[r];
         constexpr int WN = hi - lo + R;
-        const int src = ((unsigned)(line + d) < (unsigned)nlines) ? at0 + d * pitch + lo : zero_idx;
+        int src = at0 + d * pitch + lo;
+        if (CHECK && d != 0) src = ((unsigned)(line + d) < (unsigned)nlines) ? src : zero_idx;
         float win[WN];
 #pragma unroll
         for (int i = 0; i < WN; i++) win[i] = sm[src + i];
@@ -151,9 +152,10 @@ __device__ __forceinline__ void seg_line(const float *__restrict__ sm, int base,
 }
 
 // DIAG: outputs r = 0..R-1 at (ltop - r, pos0 + r); tap m reads (ltop - (r+m), pos0 + (r+m)).
-template <int OP, int JH, int R>
-__device__ __forceinline__ void seg_diag(const float *__restrict__ sm, int base, int pitch, int nlines,
-                                         int zero_idx, int ltop, int pos0,
+// `origin` is the index of (ltop, pos0).
+template <int OP, int JH, int R, bool CHECK>
+__device__ __forceinline__ void seg_diag(const float *__restrict__ sm, int origin, int pitch, int nlines,
+                                         int zero_idx, int ltop,
                                          const float (&w)[OP == OP_FPROP ? kMaxTaps : R],
                                          float (&acc)[OP == OP_FPROP ? R : kMaxTaps]) {
     using P = LP<KIND_DIAG, JH>;
@@ -161,11 +163,12 @@ __device__ __forceinline__ void seg_diag(const float *__restrict__ sm, int base,
     constexpr int WN = hi - lo + R;
     float win[WN];
     const int step = 1 - pitch;
-    const int origin = base + ltop * pitch + pos0;
 #pragma unroll
     for (int i = 0; i < WN; i++) {
         const int t = lo + i;
-        win[i] = sm[((unsigned)(ltop - t) < (unsigned)nlines) ? origin + t * step : zero_idx];
+        int src = origin + t * step;
+        if (CHECK) src = ((unsigned)(ltop - t) < (unsigned)nlines) ? src : zero_idx;
+        win[i] = sm[src];
     }
     static_for<0, P::p.ntaps>([&](auto ti) {
         constexpr int t = decltype(ti)::value;
@@ -269,13 +272,14 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
     int *err_s = misc + 3;
 
     constexpr int VE = Vec16<T>::N;
-    constexpr int NACC = (OP == OP_FPROP) ? R : kMaxTaps;
     const int tid = threadIdx.x, nt = blockDim.x;
-    const int GV = p.CC / VE;
+    // hot parameters in registers
+    const int CC = p.CC, GV = CC / VE, W = p.W, H = p.H, BR = p.BR, NB = p.NB, NSTG = p.NSTG;
+    const int C = p.C;
 
     for (int i = tid; i < p.zero_floats_total; i += nt) sm[p.off_planar + i] = 0.f;
     if (tid == 0) {
-        for (int s = 0; s < p.NSTG; s++) mbar_init(&full[s], 1);
+        for (int s = 0; s < NSTG; s++) mbar_init(&full[s], 1);
         *err_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -300,55 +304,67 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
             chunk = p.div_n.div(item); n = item - chunk * p.N;
         }
     };
-    const int total_bands = my_items * p.NB;
+    const int total_bands = my_items * NB;
 
     auto issue = [&](int gb) {   // producer: one elected thread
-        const int it = p.div_nb.div(gb), b = gb - it * p.NB;
+        const int it = p.div_nb.div(gb), b = gb - it * NB;
         int n, chunk;
         item_of(it, n, chunk);
-        const int s = gb % p.NSTG;
+        const int s = gb % NSTG;
         mbar_expect_tx(&full[s], p.stage_bytes);
-        tma_load_4d(smem_raw + p.off_stage_bytes + (size_t)s * p.stage_stride, &tmap, &full[s], chunk * p.CC, 0,
-                    b * p.BR, n);
+        tma_load_4d(smem_raw + p.off_stage_bytes + (size_t)s * p.stage_stride, &tmap, &full[s], chunk * CC, 0,
+                    b * BR, n);
     };
     if (tid == 0)
-        for (int gb = 0; gb < p.NSTG && gb < total_bands; gb++) issue(gb);
+        for (int gb = 0; gb < NSTG && gb < total_bands; gb++) issue(gb);
 
     // fixed per-thread walk over the (pixel, 16-byte vector) pairs of one band
     const int g_vec = tid % GV;
     const int pix_first = tid / GV;
-    const int rl_first = p.div_w.div(pix_first), col_first = pix_first - rl_first * p.W;
-    const int band_pixels = p.BR * p.W;
+    const int pix_step = nt / GV;
+    const int rl_first = p.div_w.div(pix_first), col_first = pix_first - rl_first * W;
+    const int band_pixels = BR * W;
+    const int band_floats = CC * p.out_plane_stride;
+    float *const outb = sm + p.off_out;
 
-    float acc_w[OP == OP_WGRAD ? kMaxTaps : 1];
+    constexpr int NACC = (OP == OP_WGRAD) ? kMaxTaps : 1;
+    float acc_w[NACC];
     float acc_db = 0.f;
-    if (OP == OP_WGRAD) {
 #pragma unroll
-        for (int k = 0; k < (OP == OP_WGRAD ? kMaxTaps : 1); k++) acc_w[k] = 0.f;
-    }
+    for (int k = 0; k < NACC; k++) acc_w[k] = 0.f;
+
     int cur_chunk = -1, visit = -1;
     bool have_next_band = false;        // weight gradient: dy band 0 of this item is already staged
-    int kind = -1, ch = 0, seg = 0;
-    int group_n = 0;                    // threads working on my channel
+    int stage = 0;                      // staging slot and mbarrier parity of the next band to consume
+    uint32_t parity = 0;
+    int gb = 0;                         // bands consumed so far
+
+    // per-thread segment, set when the chunk changes
+    int kind = -1, ch = 0, seg = 0, group_n = 0;
+    int at_base = 0, at_step = 0;       // plane index of (line, pos0) at band 0, advance per band
+    int line0 = 0, line_step = 0;       // storage line of the segment at band 0, advance per band
+    int nlines = 0, pitch = 0;
+    int oidx = 0;                       // index of the segment's first output in a band buffer
+    int diag_pos0 = 0;
 
     // Cross-thread reduction of the weight-gradient accumulators of the current chunk, in
     // thread order (fixed), a few taps per pass through the idle band buffers.
     auto flush = [&]() {
-        float *red = sm + p.off_out;
-        const int cap = (2 * p.CC * p.out_plane_stride) / nt;   // taps per pass (host ensures >= 1)
-        float *dst = partial + ((size_t)blockIdx.x * p.max_visits + visit) * p.CC * kPartialStride;
+        float *red = outb;
+        const int cap = (2 * band_floats) / nt;   // taps per pass (host ensures >= 1)
+        float *dst = partial + ((size_t)blockIdx.x * p.max_visits + visit) * CC * kPartialStride;
         for (int k0 = 0; k0 < kPartialStride; k0 += cap) {
             __syncthreads();
 #pragma unroll
             for (int k = 0; k < kPartialStride; k++)
                 if (k >= k0 && k < k0 + cap) {
                     float v = 0.f;
-                    if (kind >= 0) v = (k < kMaxTaps) ? acc_w[k < kMaxTaps ? k : 0] : acc_db;
+                    if (kind >= 0) v = (k < kMaxTaps) ? acc_w[k < NACC ? k : 0] : acc_db;
                     red[(k - k0) * nt + tid] = v;
                 }
             __syncthreads();
             const int ntap = (kPartialStride - k0 < cap) ? kPartialStride - k0 : cap;
-            for (int e = tid; e < p.CC * ntap; e += nt) {
+            for (int e = tid; e < CC * ntap; e += nt) {
                 const int i = e / ntap, kk = e - i * ntap;
                 const int2 rg = ch_range[i];
                 float sum = 0.f;
@@ -362,13 +378,13 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
     for (int it = 0; it < my_items; it++) {
         int n, chunk;
         item_of(it, n, chunk);
-        const int c0 = chunk * p.CC;
+        const int c0 = chunk * CC;
         const bool new_chunk = (chunk != cur_chunk);
 
         if (OP == OP_WGRAD && new_chunk && cur_chunk >= 0) {
             flush();
 #pragma unroll
-            for (int k = 0; k < (OP == OP_WGRAD ? kMaxTaps : 1); k++) acc_w[k] = 0.f;
+            for (int k = 0; k < NACC; k++) acc_w[k] = 0.f;
             acc_db = 0.f;
         }
 
@@ -380,9 +396,9 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
 #pragma unroll
                 for (int kd = 0; kd < 3; kd++) {
                     int cnt = 0;
-                    for (int base = 0; base < p.CC; base += 32) {
+                    for (int base = 0; base < CC; base += 32) {
                         const int i = base + tid;
-                        const int o = (i < p.CC) ? chan[c0 + i] : -1;
+                        const int o = (i < CC) ? chan[c0 + i] : -1;
                         const bool mine = o >= 0 && canon_kind(o) == kd;
                         const unsigned m = __ballot_sync(0xffffffffu, mine);
                         if (mine) ch_sorted[cnt_before + cnt + __popc(m & ((1u << tid) - 1))] = i;
@@ -394,18 +410,18 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
 #pragma unroll
                 for (int kd = 0; kd < 3; kd++) if (tid == kd) misc[kd] = counts[kd];
             }
-            for (int i = tid; i < p.CC; i += nt) {
+            for (int i = tid; i < CC; i += nt) {
                 const int o = chan[c0 + i];
                 const int mode = canon_mode(o);
                 const int pbase = p.off_planar + 32 + i * p.plane_stride;
                 const int obase = i * p.out_plane_stride;
                 int4 mi, mo;   // storage index = x*h + y*w + z
                 if (mode & MODE_T) {
-                    mi = make_int4((mode & MODE_FP) ? -1 : 1, p.pitch_t, pbase + ((mode & MODE_FP) ? p.H - 1 : 0), mode);
-                    mo = make_int4((mode & MODE_FP) ? -1 : 1, p.out_pitch_t, obase + ((mode & MODE_FP) ? p.BR - 1 : 0), mode);
+                    mi = make_int4((mode & MODE_FP) ? -1 : 1, p.pitch_t, pbase + ((mode & MODE_FP) ? H - 1 : 0), mode);
+                    mo = make_int4((mode & MODE_FP) ? -1 : 1, p.out_pitch_t, obase + ((mode & MODE_FP) ? BR - 1 : 0), mode);
                 } else {
-                    mi = make_int4(p.pitch_n, (mode & MODE_FP) ? -1 : 1, pbase + ((mode & MODE_FP) ? p.W - 1 : 0), mode);
-                    mo = make_int4(p.out_pitch_n, (mode & MODE_FP) ? -1 : 1, obase + ((mode & MODE_FP) ? p.W - 1 : 0), mode);
+                    mi = make_int4(p.pitch_n, (mode & MODE_FP) ? -1 : 1, pbase + ((mode & MODE_FP) ? W - 1 : 0), mode);
+                    mo = make_int4(p.out_pitch_n, (mode & MODE_FP) ? -1 : 1, obase + ((mode & MODE_FP) ? W - 1 : 0), mode);
                 }
                 map_in[i] = mi;
                 map_out[i] = mo;
@@ -413,7 +429,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
             }
             if (OP == OP_FPROP) {
                 const int pad = p.K / 2;
-                for (int e = tid; e < p.CC * 32; e += nt) {
+                for (int e = tid; e < CC * 32; e += nt) {
                     const int i = e >> 5, k = e & 31;
                     float v = 0.f;
                     if (k < kMaxTaps) {
@@ -431,7 +447,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
             }
         }
         if (p.rezero) {
-            for (int i = tid; i < p.CC * p.plane_stride; i += nt) sm[p.off_planar + 32 + i] = 0.f;
+            for (int i = tid; i < CC * p.plane_stride; i += nt) sm[p.off_planar + 32 + i] = 0.f;
         }
         if (new_chunk || p.rezero) __syncthreads();
 
@@ -454,29 +470,75 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
             }
             if (kind >= 0 && seg == 0) ch_range[ch] = make_int2(tid, group_n);
             cur_chunk = chunk; visit++;
+
+            // geometry of the segment, hoisted out of the band loop
+            const int mode = map_in[ch].w;
+            const bool transposed = (mode & MODE_T) != 0, fp = (mode & MODE_FP) != 0;
+            const int pbase = p.off_planar + 32 + ch * p.plane_stride;
+            const int obase = ch * p.out_plane_stride;
+            if (kind == KIND_DIAG) {
+                const int wd = W + R - 1;
+                const int sub = p.div_wdiag.div(seg), qi = seg - sub * wd;
+                diag_pos0 = qi - (R - 1);
+                const int ltop_local = sub * R + R - 1;
+                pitch = p.pitch_n; nlines = H;
+                line0 = ltop_local; line_step = BR;
+                at_base = pbase + ltop_local * pitch + diag_pos0; at_step = BR * pitch;
+                oidx = obase + ltop_local * p.out_pitch_n + diag_pos0;
+            } else if (!transposed) {                    // lines are image rows
+                const int sg = p.div_br.div(seg), rl = seg - sg * BR;
+                pitch = p.pitch_n; nlines = H;
+                line0 = rl; line_step = BR;
+                at_base = pbase + rl * pitch + sg * R; at_step = BR * pitch;
+                oidx = obase + rl * p.out_pitch_n + sg * R;
+            } else {                                     // lines are image columns
+                // lines are dealt to threads rotated by 5, so that the first warp of a channel gets
+                // lines 5..36, all of whose neighbours within +-5 exist (no-check fast path)
+                const int sub = p.div_wline.div(seg);
+                int l = seg - sub * W + 5;
+                if (l >= W) l -= W;
+                pitch = p.pitch_t; nlines = W;
+                line0 = l; line_step = 0;
+                at_base = pbase + l * pitch + (fp ? H - BR : 0) + sub * R; at_step = fp ? -BR : BR;
+                oidx = obase + l * p.out_pitch_t + sub * R;
+            }
         }
 
         // ---- restage: staging bands -> planes -------------------------------------------
         {
-            int4 m[VE];
+            int ia[VE], dstep[VE], dwrap[VE], dband[VE];
 #pragma unroll
-            for (int j = 0; j < VE; j++) m[j] = map_in[g_vec * VE + j];
-            for (int b = 0; b < p.NB; b++) {
-                const int gb = it * p.NB + b, s = gb % p.NSTG;
-                if (*err_s == 0 && !mbar_wait(&full[s], (gb / p.NSTG) & 1)) *err_s = 1;
-                const uint4 *stage = reinterpret_cast<const uint4 *>(smem_raw + p.off_stage_bytes + (size_t)s * p.stage_stride);
-                int rl = rl_first, col = col_first;
-                for (int pix = pix_first; pix < band_pixels; pix += nt / GV) {
-                    const int h = b * p.BR + rl;
+            for (int j = 0; j < VE; j++) {
+                const int4 m = map_in[g_vec * VE + j];
+                ia[j] = m.x * rl_first + m.y * col_first + m.z;
+                dstep[j] = m.x * p.step_rows + m.y * p.step_cols;
+                dwrap[j] = m.x - m.y * W;
+                dband[j] = m.x * BR;
+            }
+            for (int b = 0; b < NB; b++) {
+                if (*err_s == 0 && !mbar_wait(&full[stage], parity)) *err_s = 1;
+                const uint4 *stg = reinterpret_cast<const uint4 *>(smem_raw + p.off_stage_bytes + (size_t)stage * p.stage_stride);
+                int idx[VE];
+#pragma unroll
+                for (int j = 0; j < VE; j++) idx[j] = ia[j];
+                int col = col_first;
+                for (int pix = pix_first; pix < band_pixels; pix += pix_step) {
                     float f[VE];
-                    Vec16<T>::unpack(stage[pix * GV + g_vec], f);
+                    Vec16<T>::unpack(stg[pix * GV + g_vec], f);
 #pragma unroll
-                    for (int j = 0; j < VE; j++) sm[m[j].x * h + m[j].y * col + m[j].z] = f[j];
-                    rl += p.step_rows; col += p.step_cols;
-                    if (col >= p.W) { col -= p.W; rl++; }
+                    for (int j = 0; j < VE; j++) sm[idx[j]] = f[j];
+                    col += p.step_cols;
+                    const bool wrap = col >= W;
+                    if (wrap) col -= W;
+#pragma unroll
+                    for (int j = 0; j < VE; j++) idx[j] += dstep[j] + (wrap ? dwrap[j] : 0);
                 }
+#pragma unroll
+                for (int j = 0; j < VE; j++) ia[j] += dband[j];
                 __syncthreads();
-                if (tid == 0 && gb + p.NSTG < total_bands) issue(gb + p.NSTG);
+                if (tid == 0 && gb + NSTG < total_bands) issue(gb + NSTG);
+                gb++;
+                if (++stage == NSTG) { stage = 0; parity ^= 1; }
             }
         }
 
@@ -490,21 +552,18 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
             else if (kind == KIND_DIAG) merge_weights<KIND_DIAG, JH>(w);
         }
 
-        const int4 mi = map_in[ch];
-        const bool transposed = (mi.w & MODE_T) != 0, fp = (mi.w & MODE_FP) != 0;
-        const int pbase = p.off_planar + 32 + ch * p.plane_stride;
-        const int pitch = transposed ? p.pitch_t : p.pitch_n;
-        const int nlines = transposed ? p.W : p.H;
-        float *outb = sm + p.off_out;
-
-        // band buffer <-> global: per-thread constants
-        int4 mo[VE];
+        // band buffer <-> global: per-thread constants (index walk as in restage)
+        int oa[VE], ostep[VE], owrap[VE];
         float bs[VE];
 #pragma unroll
-        for (int j = 0; j < VE; j++) { mo[j] = map_out[g_vec * VE + j]; bs[j] = bias_s[g_vec * VE + j]; }
-        T *gbase = io + ((size_t)n * p.H * p.W) * p.C + c0 + g_vec * VE;
-        const int band_floats = p.CC * p.out_plane_stride;
-        const int pix_step = nt / GV;
+        for (int j = 0; j < VE; j++) {
+            const int4 m = map_out[g_vec * VE + j];
+            oa[j] = m.x * rl_first + m.y * col_first + m.z;
+            ostep[j] = m.x * p.step_rows + m.y * p.step_cols;
+            owrap[j] = m.x - m.y * W;
+            bs[j] = bias_s[g_vec * VE + j];
+        }
+        T *gbase = io + ((size_t)n * H * W) * C + c0 + g_vec * VE;
 
         // Weight gradient: a dy band travels global -> registers (128-bit NHWC loads, issued
         // before the arithmetic of the previous band) -> band buffer (after it).
@@ -514,111 +573,140 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
 #pragma unroll
             for (int u = 0; u < kPre; u++) {
                 const int pix = pix_first + u * pix_step;
-                if (pix < band_pixels) pre[u] = __ldg(reinterpret_cast<const uint4 *>(src_band + (size_t)pix * p.C));
+                if (pix < band_pixels) pre[u] = __ldg(reinterpret_cast<const uint4 *>(src_band + (size_t)pix * C));
             }
         };
         auto dy_commit = [&](const T *src_band, float *dstb) {
-            int rl = rl_first, col = col_first, u = 0;
+            int idx[VE];
+#pragma unroll
+            for (int j = 0; j < VE; j++) idx[j] = oa[j];
+            int col = col_first, u = 0;
             for (int pix = pix_first; pix < band_pixels; pix += pix_step, u++) {
                 uint4 v;
                 if (u < kPre) v = (u == 0) ? pre[0] : pre[kPre - 1];
-                else v = __ldg(reinterpret_cast<const uint4 *>(src_band + (size_t)pix * p.C));
+                else v = __ldg(reinterpret_cast<const uint4 *>(src_band + (size_t)pix * C));
                 float f[VE];
                 Vec16<T>::unpack(v, f);
 #pragma unroll
-                for (int j = 0; j < VE; j++) dstb[mo[j].x * rl + mo[j].y * col + mo[j].z] = f[j];
-                rl += p.step_rows; col += p.step_cols;
-                if (col >= p.W) { col -= p.W; rl++; }
+                for (int j = 0; j < VE; j++) dstb[idx[j]] = f[j];
+                col += p.step_cols;
+                const bool wrap = col >= W;
+                if (wrap) col -= W;
+#pragma unroll
+                for (int j = 0; j < VE; j++) idx[j] += ostep[j] + (wrap ? owrap[j] : 0);
             }
         };
         if (OP == OP_WGRAD && !have_next_band) {       // first band of the item, not prefetched
             dy_fetch(gbase);
-            dy_commit(gbase, outb + ((it * p.NB) & 1) * band_floats);
+            dy_commit(gbase, outb + ((it * NB) & 1) * band_floats);
             __syncthreads();
         }
         have_next_band = false;
 
-        for (int b = 0; b < p.NB; b++) {
-            const int gbi = it * p.NB + b;             // global band index: selects the buffer
-            float *ob = outb + (gbi & 1) * band_floats + ch * p.out_plane_stride;
+        int at = at_base, line = line0;
+        for (int b = 0; b < NB; b++, at += at_step, line += line_step) {
+            const int gbi = it * NB + b;               // global band index: selects the buffer
+            float *ob = outb + (gbi & 1) * band_floats + oidx;
             const T *next_src = nullptr;
             if (OP == OP_WGRAD) {
-                if (b + 1 < p.NB) {
-                    next_src = gbase + (size_t)(b + 1) * band_pixels * p.C;
+                if (b + 1 < NB) {
+                    next_src = gbase + (size_t)(b + 1) * band_pixels * C;
                 } else if (it + 1 < my_items) {
                     int n2, chunk2;
                     item_of(it + 1, n2, chunk2);
-                    if (chunk2 == chunk) next_src = io + ((size_t)n2 * p.H * p.W) * p.C + c0 + g_vec * VE;
+                    if (chunk2 == chunk) next_src = io + ((size_t)n2 * H * W) * C + c0 + g_vec * VE;
                 }
                 if (next_src) dy_fetch(next_src);
             }
-            if (kind == KIND_AXIS || kind == KIND_SLANT) {
-                int line, pos0, oidx;
-                if (!transposed) {                       // lines are image rows
-                    const int sg = p.div_br.div(seg), rl = seg - sg * p.BR;
-                    line = b * p.BR + rl; pos0 = sg * R;
-                    oidx = rl * p.out_pitch_n + pos0;
-                } else {                                 // lines are image columns
-                    const int sub = p.div_wline.div(seg), l = seg - sub * p.W;
-                    const int band0 = fp ? p.H - (b + 1) * p.BR : b * p.BR;
-                    line = l; pos0 = band0 + sub * R;
-                    oidx = l * p.out_pitch_t + sub * R;
-                }
+            // Do all lines this warp's segments touch exist?  Voted by every lane (idle lanes
+            // included, they agree) so that the answer is warp-uniform.
+            bool lane_inside = true;
+            if (kind == KIND_SLANT) {
+                constexpr int MD = LP<KIND_SLANT, JH>::p.max_d;
+                lane_inside = line - MD >= 0 && line + MD < nlines;
+            } else if (kind == KIND_DIAG) {
+                using PD = LP<KIND_DIAG, JH>;
+                constexpr int TLO = PD::p.row_lo[0], THI = PD::p.row_hi[0] + R - 1;   // t range read
+                lane_inside = line - THI >= 0 && line - TLO < nlines;
+            }
+            const bool inside = __all_sync(0xffffffffu, lane_inside);
+            if (kind == KIND_AXIS) {
+                // a single line row (d = 0) and the segment's own line always exists: no checks
                 if constexpr (OP == OP_FPROP) {
                     float acc[R];
 #pragma unroll
                     for (int o = 0; o < R; o++) acc[o] = 0.f;
-                    if (kind == KIND_AXIS) seg_line<OP_FPROP, KIND_AXIS, JH, R>(sm, pbase, pitch, nlines, p.off_zero, line, pos0, w, acc);
-                    else seg_line<OP_FPROP, KIND_SLANT, JH, R>(sm, pbase, pitch, nlines, p.off_zero, line, pos0, w, acc);
+                    seg_line<OP_FPROP, KIND_AXIS, JH, R, false>(sm, at, pitch, nlines, p.off_zero, line, w, acc);
 #pragma unroll
-                    for (int o = 0; o < R; o++) ob[oidx + o] = acc[o];
+                    for (int o = 0; o < R; o++) ob[o] = acc[o];
                 } else {
                     float g[R];
 #pragma unroll
-                    for (int o = 0; o < R; o++) { g[o] = ob[oidx + o]; acc_db += g[o]; }
-                    if (kind == KIND_AXIS) seg_line<OP_WGRAD, KIND_AXIS, JH, R>(sm, pbase, pitch, nlines, p.off_zero, line, pos0, g, acc_w);
-                    else seg_line<OP_WGRAD, KIND_SLANT, JH, R>(sm, pbase, pitch, nlines, p.off_zero, line, pos0, g, acc_w);
+                    for (int o = 0; o < R; o++) { g[o] = ob[o]; acc_db += g[o]; }
+                    seg_line<OP_WGRAD, KIND_AXIS, JH, R, false>(sm, at, pitch, nlines, p.off_zero, line, g, acc_w);
                 }
-            } else if (kind == KIND_DIAG) {
-                const int wd = p.W + R - 1;
-                const int sub = p.div_wdiag.div(seg), qi = seg - sub * wd;
-                const int pos0 = qi - (R - 1);
-                const int ltop_local = sub * R + R - 1;
+            } else if (kind == KIND_SLANT) {
                 if constexpr (OP == OP_FPROP) {
                     float acc[R];
 #pragma unroll
                     for (int o = 0; o < R; o++) acc[o] = 0.f;
-                    seg_diag<OP_FPROP, JH, R>(sm, pbase, p.pitch_n, p.H, p.off_zero, b * p.BR + ltop_local, pos0, w, acc);
+                    if (inside) seg_line<OP_FPROP, KIND_SLANT, JH, R, false>(sm, at, pitch, nlines, p.off_zero, line, w, acc);
+                    else seg_line<OP_FPROP, KIND_SLANT, JH, R, true>(sm, at, pitch, nlines, p.off_zero, line, w, acc);
+#pragma unroll
+                    for (int o = 0; o < R; o++) ob[o] = acc[o];
+                } else {
+                    float g[R];
+#pragma unroll
+                    for (int o = 0; o < R; o++) { g[o] = ob[o]; acc_db += g[o]; }
+                    if (inside) seg_line<OP_WGRAD, KIND_SLANT, JH, R, false>(sm, at, pitch, nlines, p.off_zero, line, g, acc_w);
+                    else seg_line<OP_WGRAD, KIND_SLANT, JH, R, true>(sm, at, pitch, nlines, p.off_zero, line, g, acc_w);
+                }
+            } else if (kind == KIND_DIAG) {
+                const int odiag = 1 - p.out_pitch_n;
+                if constexpr (OP == OP_FPROP) {
+                    float acc[R];
+#pragma unroll
+                    for (int o = 0; o < R; o++) acc[o] = 0.f;
+                    if (inside) seg_diag<OP_FPROP, JH, R, false>(sm, at, pitch, nlines, p.off_zero, line, w, acc);
+                    else seg_diag<OP_FPROP, JH, R, true>(sm, at, pitch, nlines, p.off_zero, line, w, acc);
 #pragma unroll
                     for (int o = 0; o < R; o++)
-                        if ((unsigned)(pos0 + o) < (unsigned)p.W) ob[(ltop_local - o) * p.out_pitch_n + pos0 + o] = acc[o];
+                        if ((unsigned)(diag_pos0 + o) < (unsigned)W) ob[o * odiag] = acc[o];
                 } else {
                     float g[R];
 #pragma unroll
                     for (int o = 0; o < R; o++) {
-                        g[o] = ((unsigned)(pos0 + o) < (unsigned)p.W) ? ob[(ltop_local - o) * p.out_pitch_n + pos0 + o] : 0.f;
+                        g[o] = ((unsigned)(diag_pos0 + o) < (unsigned)W) ? ob[o * odiag] : 0.f;
                         acc_db += g[o];
                     }
-                    seg_diag<OP_WGRAD, JH, R>(sm, pbase, p.pitch_n, p.H, p.off_zero, b * p.BR + ltop_local, pos0, g, acc_w);
+                    if (inside) seg_diag<OP_WGRAD, JH, R, false>(sm, at, pitch, nlines, p.off_zero, line, g, acc_w);
+                    else seg_diag<OP_WGRAD, JH, R, true>(sm, at, pitch, nlines, p.off_zero, line, g, acc_w);
                 }
             }
             if (OP == OP_WGRAD && next_src) {
                 // the other buffer was last read one band ago, before the previous barrier
                 dy_commit(next_src, outb + ((gbi + 1) & 1) * band_floats);
-                if (b + 1 == p.NB) have_next_band = true;
+                if (b + 1 == NB) have_next_band = true;
             }
             __syncthreads();
             if (OP == OP_FPROP) {
                 // ---- store band b: band buffer -> NHWC, 16 bytes per thread ---------------------
                 const float *src = outb + (gbi & 1) * band_floats;
-                int rl = rl_first, col = col_first;
+                T *gdst = gbase + (size_t)b * band_pixels * C;
+                int idx[VE];
+#pragma unroll
+                for (int j = 0; j < VE; j++) idx[j] = oa[j];
+                int col = col_first;
                 for (int pix = pix_first; pix < band_pixels; pix += pix_step) {
                     float f[VE];
 #pragma unroll
-                    for (int j = 0; j < VE; j++) f[j] = src[mo[j].x * rl + mo[j].y * col + mo[j].z] + bs[j];
-                    *reinterpret_cast<uint4 *>(gbase + ((size_t)b * band_pixels + pix) * p.C) = Vec16<T>::pack(f);
-                    rl += p.step_rows; col += p.step_cols;
-                    if (col >= p.W) { col -= p.W; rl++; }
+                    for (int j = 0; j < VE; j++) f[j] = src[idx[j]] + bs[j];
+                    *reinterpret_cast<uint4 *>(gdst + (size_t)pix * C) = Vec16<T>::pack(f);
+                    col += p.step_cols;
+                    const bool wrap = col >= W;
+                    if (wrap) col -= W;
+#pragma unroll
+                    for (int j = 0; j < VE; j++) idx[j] += ostep[j] + (wrap ? owrap[j] : 0);
                 }
             }
         }
