@@ -451,9 +451,11 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
         }
         if (new_chunk || p.rezero) __syncthreads();
 
-        // ---- thread -> (kind, channel, segment); groups of equal kind start on warp boundaries
+        // ---- thread -> (kind, channel, segment), channels grouped by kind
         if (new_chunk) {
             const int nA = misc[0], nS = misc[1], nD = misc[2];
+            // groups start on warp boundaries: a warp of mixed kinds would run every path in turn
+            // and, being the slowest warp, hold up the band barrier
             const int slotsA = (nA * p.nseg_line + 31) & ~31, slotsS = (nS * p.nseg_line + 31) & ~31;
             kind = -1; ch = 0; seg = 0;
             int idx = tid;

@@ -32,6 +32,9 @@ struct TiledConfig {
     TiledParams p;
     int smem_bytes;
     int grid;
+    int threads;     // CTA size: 512, 256 or 128 (smaller CTAs co-reside and overlap their phases)
+    int ctas_per_sm;
+    double score;
     int stage_stride;
     int jh;          // taps |j| <= jh are evaluated (instantiated: 7, 9, 15)
     double util;
@@ -82,9 +85,10 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
 
     bool found = false;
     TiledConfig best{};
+    for (int NT = kTiledThreads; NT >= 128; NT /= 2)
     for (int ci = 0; ci < 4; ci++) {
         const int CC = kChunkWidths[ci];
-        if (CC % VE != 0 || C % CC != 0 || comps[ci].n <= 0) continue;
+        if (CC % VE != 0 || C % CC != 0 || comps[ci].n <= 0 || NT % (CC / VE) != 0) continue;
         for (int BR = R; BR <= H; BR += R) {
             if (H % BR != 0) continue;
             const int nseg_line = BR * (W / R), nseg_diag = (W + R - 1) * (BR / R);
@@ -96,13 +100,13 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
                 if (slots > worst) worst = slots;
                 active += (double)((a + s) * nseg_line + d * nseg_diag) / comps[ci].n;
             }
-            if (worst > kTiledThreads) continue;
+            if (worst > NT) continue;
             const int out_pitch_n = make_odd(W), out_pitch_t = make_odd(BR);
             // Plane strides are padded so that the channel groups a warp touches together in
             // the restage / store loops (VE channels apart) fall into different banks.
             const int PLS = skew_stride(PLS0, CC, VE);
             const int OPS = skew_stride((BR * out_pitch_n > W * out_pitch_t) ? BR * out_pitch_n : W * out_pitch_t, CC, VE);
-            if (op == OP_WGRAD && (2 * CC * OPS) / kTiledThreads < 1) continue;
+            if (op == OP_WGRAD && (2 * CC * OPS) / NT < 1) continue;
             TiledParams p{};
             p.off_planar = 0;
             const int planar_floats = 32 + CC * PLS;
@@ -120,12 +124,23 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             const int NB = H / BR;
             int room = smem_limit - bytes - 8 * kMaxStages - 128;
             int nstg = room / stage_stride;
+            const int nstg_cap = NB + 2 > 3 ? NB + 2 : 3;        // about one item of read-ahead
+            if (nstg > nstg_cap) nstg = nstg_cap;
             if (nstg > kMaxStages) nstg = kMaxStages;
             if (nstg < 2 && !(nstg == 1 && NB == 1)) continue;
-            // Rank: thread utilisation first; among equals prefer fewer, larger bands.
-            const double util = active / kTiledThreads;
-            const bool better = !found || util > best.util + 1e-9 ||
-                                (util > best.util - 1e-9 && BR * CC > best.p.BR * best.p.CC);
+            const int smem_total = bytes + nstg * stage_stride + 8 * kMaxStages;
+            // CTAs that fit one SM: 64K registers at 128 per thread, 228 KB of shared memory
+            // (1 KB reserved per CTA)
+            int ctas = kTiledThreads / NT;
+            const int by_smem = (228 * 1024) / (smem_total + 1024);
+            if (by_smem < ctas) ctas = by_smem;
+            if (ctas < 1) continue;
+            // Rank: lanes doing useful work per SM, with a bonus when two or more CTAs share an
+            // SM (their load / restage / compute / store phases overlap); then larger tiles.
+            const double util = active / NT;
+            const double score = util * (double)(ctas * NT) / kTiledThreads * (ctas >= 2 ? 1.25 : 1.0);
+            const bool better = !found || score > best.score + 1e-9 ||
+                                (score > best.score - 1e-9 && BR * CC > best.p.BR * best.p.CC);
             if (!better) continue;
             p.N = N; p.H = H; p.W = W; p.C = C; p.K = K;
             p.CC = CC; p.nchunks = C / CC; p.total_items = N * p.nchunks;
@@ -140,12 +155,13 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             p.div_nseg_line = FastDiv::make(nseg_line); p.div_nseg_diag = FastDiv::make(nseg_diag);
             p.div_br = FastDiv::make(BR); p.div_wline = FastDiv::make(W); p.div_wdiag = FastDiv::make(W + R - 1);
             p.div_chunks = FastDiv::make(p.nchunks); p.div_nb = FastDiv::make(NB); p.div_n = FastDiv::make(N);
-            const int pix_step = kTiledThreads / (CC / VE);
+            const int pix_step = NT / (CC / VE);
             p.step_rows = pix_step / W; p.step_cols = pix_step % W;
             best.p = p;
             best.smem_bytes = p.off_bar_bytes + 8 * kMaxStages;
             best.stage_stride = stage_stride;
-            best.grid = p.total_items < sms ? p.total_items : sms;
+            best.threads = NT; best.ctas_per_sm = ctas; best.score = score;
+            best.grid = p.total_items < sms * ctas ? p.total_items : sms * ctas;
             if (op == OP_FPROP && p.nchunks <= best.grid) {
                 // A grid that is a multiple of the chunk count keeps every CTA on one chunk, so
                 // its channel tables and weights are built once; worth giving up to 15% of the SMs.
@@ -197,7 +213,7 @@ cudaError_t launch_tiled_one(const TiledConfig &cfg, const CUtensorMap &map, con
     auto kern = tiled_nhwc_kernel<T, R, JH, OP>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
     if (e != cudaSuccess) return e;
-    kern<<<cfg.grid, kTiledThreads, cfg.smem_bytes, st>>>(map, w, bias, pv.chan, (T *)io, partial, cfg.p);
+    kern<<<cfg.grid, cfg.threads, cfg.smem_bytes, st>>>(map, w, bias, pv.chan, (T *)io, partial, cfg.p);
     return cudaGetLastError();
 }
 
