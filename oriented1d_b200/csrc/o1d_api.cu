@@ -188,7 +188,7 @@ int try_tiled_wgrad(const void *dy, const void *x, const PlanHeader &ph, const v
     const MergeTables mt = merge_tables_for(cfg.jh);
     const int tot = C * (K + 1);
     tiled_wgrad_final_kernel<<<ceil_div(tot, 128), 128, 0, st>>>(partial, pv.chan, dw, db, C, K, cfg.p.CC, N,
-                                                                 cfg.p.total_items, cfg.grid, cfg.p.max_visits, mt);
+                                                                 cfg.p.total_items, cfg.grid, cfg.p.max_visits, cfg.p.order, mt);
     O1D_CUDA(cudaGetLastError());
     return O1D_OK;
 }
@@ -241,7 +241,7 @@ int o1d_offsets(const float *theta_host, int C, int K, int8_t *dh, int8_t *dw) {
 size_t o1d_plan_bytes(int C, int K) {
     if (C <= 0 || K <= 0) return 0;
     return sizeof(PlanHeader) + align16((uint32_t)C * 2) + align16((uint32_t)C * K * 2) + align16((uint32_t)C) +
-           align16(4 * sizeof(KindComp)) + align16((uint32_t)C);
+           align16(kNumChunkWidths * sizeof(KindComp)) + align16((uint32_t)C);
 }
 
 int o1d_plan_build(const float *theta_host, int C, int K, void *plan_host) {
@@ -279,7 +279,7 @@ int o1d_plan_build(const float *theta_host, int C, int K, void *plan_host) {
     h.taps_off = h.cls_off + align16((uint32_t)C * 2);
     h.canon_off = h.taps_off + align16((uint32_t)ncls * K * 2);
     h.comps_off = h.canon_off + align16((uint32_t)ncls);
-    h.chan_off = h.comps_off + align16(4 * sizeof(KindComp));
+    h.chan_off = h.comps_off + align16(kNumChunkWidths * sizeof(KindComp));
     h.total_bytes = h.chan_off + align16((uint32_t)C);
     char *b = static_cast<char *>(plan_host);
     memset(b, 0, o1d_plan_bytes(C, K));
@@ -303,9 +303,9 @@ int o1d_plan_build(const float *theta_host, int C, int K, void *plan_host) {
         canon_of[i] = canon;
         if (canon < 0) all_canon = 0;
     }
-    // distinct (axis, slant, diagonal) compositions of aligned chunks of 8/16/32/64 channels
-    KindComp comps[4];
-    for (int ci = 0; ci < 4; ci++) {
+    // distinct (axis, slant, diagonal) compositions of aligned chunks of 4/8/16/32/64 channels
+    KindComp comps[kNumChunkWidths];
+    for (int ci = 0; ci < kNumChunkWidths; ci++) {
         KindComp &kc = comps[ci];
         memset(&kc, 0, sizeof(kc));
         const int CC = kChunkWidths[ci];

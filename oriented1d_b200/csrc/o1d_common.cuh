@@ -12,7 +12,7 @@ namespace o1d {
 // ---------------------------------------------------------------------------------
 // Plan blob.  The same bytes live on the host and on the device.
 //   [PlanHeader (64 B)] [cls: C x uint16, padded to 16 B] [taps: ncls x K x (dh,dw) int8,
-//   padded to 16 B] [canon: ncls x int8, padded to 16 B] [comps: 4 x KindComp]
+//   padded to 16 B] [canon: ncls x int8, padded to 16 B] [comps: 5 x KindComp]
 //   [chan: C x int8, padded to 16 B]
 // cls[c]    orientation class of channel c
 // taps      rasterised offsets of each class, exactly the reference's
@@ -25,7 +25,8 @@ namespace o1d {
 //           their thread groups from it); n = -1 when C is not a multiple of the width or
 //           there are more than kMaxComps distinct triples
 // ---------------------------------------------------------------------------------
-constexpr int kChunkWidths[4] = {8, 16, 32, 64};
+constexpr int kNumChunkWidths = 5;
+constexpr int kChunkWidths[kNumChunkWidths] = {4, 8, 16, 32, 64};
 constexpr int kMaxComps = 16;
 struct KindComp {
     int32_t n;

@@ -67,6 +67,7 @@ struct TiledParams {
     int rezero;                   // planes must be cleared per item (H != W)
     int step_rows, step_cols;     // pixel advance of one thread per loop trip in restage/store
     int max_visits;               // weight gradient: partial slots per CTA
+    int order;                    // 0: image-major items (item = cta + i*grid), 1: chunk-major ranges
     // shared memory layout, in floats from the start of dynamic smem
     int off_planar, off_zero, off_out, off_wts, off_misc;
     int off_stage_bytes, stage_bytes, stage_stride, off_bar_bytes;
@@ -287,8 +288,12 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
     __syncthreads();
 
     // ---- item sequence of this CTA ------------------------------------------------------
+    // Image-major order makes neighbouring CTAs read neighbouring chunks of the same pixels at
+    // the same time (every DRAM sector and page is used while it is open); with a grid that is a
+    // multiple of the chunk count each CTA also stays on one chunk.  Chunk-major ranges are the
+    // weight gradient's fallback when no such grid exists (it must not hop between chunks).
     int my_items, item_base;
-    if (OP == OP_FPROP) {
+    if (p.order == 0) {
         my_items = (p.total_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
         item_base = blockIdx.x;
     } else {
@@ -296,7 +301,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
         my_items = wgrad_item_lo(blockIdx.x + 1, gridDim.x, p.total_items) - item_base;
     }
     auto item_of = [&](int it, int &n, int &chunk) {
-        if (OP == OP_FPROP) {           // image-major: neighbouring CTAs share DRAM pages
+        if (p.order == 0) {             // image-major
             const int item = item_base + it * gridDim.x;
             n = p.div_chunks.div(item); chunk = item - n * p.nchunks;
         } else {                        // chunk-major
@@ -721,7 +726,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
 __global__ void tiled_wgrad_final_kernel(const float *__restrict__ partial, const int8_t *__restrict__ chan,
                                          float *__restrict__ dw,
                                          float *__restrict__ db, int C, int K, int CC, int N, int total_items,
-                                         int ctas, int max_visits, const MergeTables mt) {
+                                         int ctas, int max_visits, int order, const MergeTables mt) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= C * (K + 1)) return;
     const int c = idx / (K + 1), k = idx % (K + 1);
@@ -738,6 +743,11 @@ __global__ void tiled_wgrad_final_kernel(const float *__restrict__ partial, cons
     const int item_lo = chunk * N, item_hi = item_lo + N;
     float sum = 0.f;
     // slot < 0: the tap cannot reach inside an image of this size; its gradient is exactly 0
+    if (order == 0) {     // every CTA stayed on chunk (cta % nchunks) and wrote one partial
+        const int nchunks = C / CC;
+        for (int b = chunk; b < ctas && slot >= 0; b += nchunks)
+            if (b < total_items) sum += partial[(((size_t)b * max_visits) * CC + i) * kPartialStride + slot];
+    } else
     for (int b = 0; b < ctas && slot >= 0; b++) {
         const int lo = wgrad_item_lo(b, ctas, total_items), hi = wgrad_item_lo(b + 1, ctas, total_items);
         if (hi <= item_lo || lo >= item_hi || hi == lo) continue;

@@ -86,9 +86,13 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
     bool found = false;
     TiledConfig best{};
     for (int NT = kTiledThreads; NT >= 128; NT /= 2)
-    for (int ci = 0; ci < 4; ci++) {
+    for (int ci = 0; ci < kNumChunkWidths; ci++) {
         const int CC = kChunkWidths[ci];
         if (CC % VE != 0 || C % CC != 0 || comps[ci].n <= 0 || NT % (CC / VE) != 0) continue;
+        // a chunk narrower than a 32-byte DRAM sector halves the useful bytes per sector fetched
+        // (measured slower even with two CTAs per SM); allowed only for 2-byte elements, where 8
+        // channels are the most whose planes fit at 56x56
+        if (CC * esize < 32 && !(esize == 2 && CC == 8)) continue;
         for (int BR = R; BR <= H; BR += R) {
             if (H % BR != 0) continue;
             const int nseg_line = BR * (W / R), nseg_diag = (W + R - 1) * (BR / R);
@@ -122,19 +126,19 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             p.stage_bytes = BR * W * CC * esize;
             const int stage_stride = (p.stage_bytes + 127) & ~127;
             const int NB = H / BR;
-            int room = smem_limit - bytes - 8 * kMaxStages - 128;
-            int nstg = room / stage_stride;
-            const int nstg_cap = NB + 2 > 3 ? NB + 2 : 3;        // about one item of read-ahead
-            if (nstg > nstg_cap) nstg = nstg_cap;
-            if (nstg > kMaxStages) nstg = kMaxStages;
-            if (nstg < 2 && !(nstg == 1 && NB == 1)) continue;
-            const int smem_total = bytes + nstg * stage_stride + 8 * kMaxStages;
-            // CTAs that fit one SM: 64K registers at 128 per thread, 228 KB of shared memory
-            // (1 KB reserved per CTA)
-            int ctas = kTiledThreads / NT;
-            const int by_smem = (228 * 1024) / (smem_total + 1024);
-            if (by_smem < ctas) ctas = by_smem;
-            if (ctas < 1) continue;
+            // CTAs that fit one SM: 64K registers at 128 per thread; 228 KB of shared memory with
+            // 1 KB reserved per CTA.  Staging depth is traded against co-residency: take the
+            // largest CTA count that still leaves two stages (one when the image is one band).
+            const int nstg_cap = NB + 2 > 3 ? (NB + 2 < kMaxStages ? NB + 2 : kMaxStages) : 3;
+            const int nstg_min = NB == 1 ? 1 : 2;
+            int ctas = 0, nstg = 0;
+            for (int t = kTiledThreads / NT; t >= 1 && !ctas; t--) {
+                int budget = (228 * 1024) / t - 1024;
+                if (budget > smem_limit) budget = smem_limit;
+                const int n_fit = (budget - bytes - 8 * kMaxStages) / stage_stride;
+                if (n_fit >= nstg_min) { ctas = t; nstg = n_fit < nstg_cap ? n_fit : nstg_cap; }
+            }
+            if (!ctas) continue;
             // Rank: lanes doing useful work per SM, with a bonus when two or more CTAs share an
             // SM (their load / restage / compute / store phases overlap); then larger tiles.
             const double util = active / NT;
@@ -162,11 +166,18 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             best.stage_stride = stage_stride;
             best.threads = NT; best.ctas_per_sm = ctas; best.score = score;
             best.grid = p.total_items < sms * ctas ? p.total_items : sms * ctas;
-            if (op == OP_FPROP && p.nchunks <= best.grid) {
-                // A grid that is a multiple of the chunk count keeps every CTA on one chunk, so
-                // its channel tables and weights are built once; worth giving up to 15% of the SMs.
+            best.p.order = (op == OP_WGRAD) ? 1 : 0;
+            if (p.nchunks <= best.grid) {
+                // A grid that is a multiple of the chunk count keeps every CTA on one chunk: its
+                // channel tables and weights are built once, and the weight gradient can use the
+                // DRAM-friendly image-major order with a single flush.  Worth giving up some SMs
+                // (forward: up to 15%; weight gradient: up to 30%, chunk-major order re-reads
+                // every DRAM sector).
                 const int g = (best.grid / p.nchunks) * p.nchunks;
-                if (g * 100 >= best.grid * 85) best.grid = g;
+                if (g * 100 >= best.grid * (op == OP_WGRAD ? 70 : 85)) {
+                    best.grid = g;
+                    best.p.order = 0;
+                }
             }
             best.jh = tiled_tap_reach(H, W, K);
             best.util = util;
@@ -174,9 +185,9 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
         }
     }
     if (found) {
-        if (op == OP_WGRAD) {   // contiguous item ranges; partial slots = chunks a CTA can touch
+        if (op == OP_WGRAD) {   // partial slots per CTA = chunks it can touch
             int mv = 1;
-            for (int b = 0; b < best.grid; b++) {
+            for (int b = 0; b < best.grid && best.p.order == 1; b++) {
                 const int lo = wgrad_item_lo(b, best.grid, best.p.total_items);
                 const int hi = wgrad_item_lo(b + 1, best.grid, best.p.total_items);
                 if (hi > lo) {
