@@ -316,6 +316,52 @@ def run_ours(args):
                 "frac": kernels[top]["frac"], "traffic": traffic, "peak_source": peak_src,
                 "alg_bytes_per_launch": kernels[top]["alg_bytes"], "us_per_launch": kernels[top]["us"]}
 
+    # ---- GPU baseline: the reference's own specialised CUDA kernels on this GPU --------
+    # (compiled from the reference checkout by oracle/build.py --gpu-reference; NCHW fp32 only;
+    # the "nhwc" figure adds the two layout transposes its module wraps around them)
+    ref_gpu = None
+    if rank == 0 and not args.no_ref_gpu:
+        try:
+            from oracle.oracle import ReferenceGPU
+            refg = ReferenceGPU() if ReferenceGPU.available() else None
+        except Exception:
+            refg = None
+        if refg is not None:
+            ref_gpu = {}
+            for L in layers32:
+                hw, C = L.hw, L.C
+                sets = [(x.permute(0, 3, 1, 2).contiguous(), dy.permute(0, 3, 1, 2).contiguous())
+                        for x, dy in zip(L.x, L.dy)]
+                theta_d = torch.from_numpy(round_robin_angles(C)).to(dev)
+                state = {"i": 0}
+
+                def nxt(sets=sets, state=state):
+                    state["i"] = (state["i"] + 1) % len(sets)
+                    return sets[state["i"]]
+
+                def r_fprop(L=L, theta_d=theta_d):
+                    refg.fprop(nxt()[0], L.w, theta_d)
+
+                def r_dgrad(L=L, theta_d=theta_d):
+                    refg.dgrad(nxt()[1], L.w, theta_d)
+
+                def r_wgrad(L=L, theta_d=theta_d):
+                    x, dy = nxt()
+                    refg.wgrad(dy, x, theta_d)
+
+                def r_fprop_nhwc(L=L, theta_d=theta_d, hw=hw, C=C):
+                    x = L.next()[0]
+                    xc = refg.transpose(x, BATCH, hw * hw, C, (BATCH, C, hw, hw))
+                    y = refg.fprop(xc, L.w, theta_d)
+                    refg.transpose(y, BATCH, C, hw * hw, (BATCH, hw, hw, C))
+
+                for name, fn in (("fprop", r_fprop), ("dgrad", r_dgrad), ("wgrad", r_wgrad),
+                                 ("fprop_nhwc", r_fprop_nhwc)):
+                    t_ms = timed(fn, 20, 3, graph_cycle=0 if args.no_graph else len(sets), all_ranks=False) / 20
+                    ref_gpu[f"{name}_f32_{hw}x{hw}x{C}"] = round(t_ms * 1e3, 2)
+                del sets
+                torch.cuda.empty_cache()
+
     # ---- end to end: the nn.Module on host buffers ------------------------------------
     mods, host = [], []
     for hw, C in STAGES:
@@ -373,6 +419,7 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": n_launch, "clocks": clocks, "kernels": kernels,
+            "reference_gpu_us": ref_gpu,
         }
         print(json.dumps(line))
     if world > 1:
@@ -431,6 +478,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's CUDA kernels")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graphs")
     ap.add_argument("--case", default=None, help="run one kernel case alone, e.g. fprop_f32_56x56x96")
     ap.add_argument("--batch", type=int, default=64, help="batch for --case")

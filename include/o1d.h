@@ -67,6 +67,13 @@ int o1d_set_route(int route);
  * checks no launch or device errors at all, kernels.h:529,542,555.) */
 int o1d_device_status(int *flag_out);
 
+/* 1 if o1d_fprop / o1d_dgrad / o1d_wgrad would take the tiled (TMA-staged) kernels for this
+ * request, 0 if the general kernels.  Lets a host decide whether converting an NCHW tensor
+ * to NHWC first pays off (the tiled kernels are NHWC only).  Host-only; no counterpart in
+ * the reference. */
+int o1d_uses_tiled(const void *plan_host, int N, int H, int W, int C, int K, int stride,
+                   int layout, int dtype);
+
 /* Rasterised tap offsets of C channels, computed on the host exactly as the reference's
  * CPU loops do (kernels.cpp:37,43-44).  theta_host: C floats (radians, fp32);
  * dh, dw: C*K int8 each.  Requires K odd, K <= 255. */

@@ -73,6 +73,31 @@ def build_ref(force: bool = False) -> str | None:
     return REF_SO
 
 
+REFGPU_SO = os.path.join(REF_DIR, "libo1d_refgpu.so")
+REFGPU_SUBDIR = os.path.join("models", "dwoconv1d_specialized", "kernels")
+
+
+def build_refgpu(force: bool = False) -> str | None:
+    """Compile the reference's specialised CUDA kernels (kernels.h, nhwc_utils.h) for sm_100a
+    through refgpu_shim.cu; None if there is no checkout.  Several minutes: the reference
+    fully unrolls its kernels per shape."""
+    root = os.environ.get("O1D_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+    src_dir = os.path.join(root, REFGPU_SUBDIR)
+    if not os.path.isfile(os.path.join(src_dir, "kernels.h")):
+        return REFGPU_SO if os.path.exists(REFGPU_SO) else None
+    shim = os.path.join(HERE, "refgpu_shim.cu")
+    if not (force or _stale(REFGPU_SO, [shim, os.path.join(src_dir, "kernels.h")])):
+        return REFGPU_SO
+    os.makedirs(REF_DIR, exist_ok=True)
+    nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-w", "-Xcompiler", "-fPIC",
+           "-shared", "-I" + src_dir, shim, "-o", REFGPU_SO]
+    subprocess.run(cmd, check=True)
+    return REFGPU_SO
+
+
 if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
     print(build_ref(force="--force" in sys.argv))
+    if "--gpu-reference" in sys.argv:
+        print(build_refgpu(force="--force" in sys.argv))

@@ -244,3 +244,62 @@ def backward_safe(loops, x, w, theta, dy, bias=None, stride=1, nhwc=False, resid
     if nhwc:
         dx = dx.transpose(0, 2, 3, 1)
     return np.ascontiguousarray(dx), dw, db
+
+
+class ReferenceGPU:
+    """The reference's own specialised CUDA kernels (models/dwoconv1d_specialized/kernels/
+    kernels.h) compiled for sm_100a through refgpu_shim.cu: the GPU baseline to beat.  Built
+    for H = W in {56, 28, 14, 7}, K = 31, stride 1, NCHW float32.  Takes and returns torch
+    CUDA tensors; launches on the current stream."""
+
+    SHAPES = (56, 28, 14, 7)
+
+    def __init__(self, path: str | None = None):
+        path = path or os.path.join(HERE, "_ref", "libo1d_refgpu.so")
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        self._lib = ctypes.CDLL(path)
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(os.path.join(HERE, "_ref", "libo1d_refgpu.so"))
+
+    @staticmethod
+    def _stream():
+        import torch
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _call(self, name, hw, *tensors, N, C):
+        rc = getattr(self._lib, name)(hw, *[ctypes.c_void_p(t.data_ptr()) for t in tensors], N, C, self._stream())
+        if rc:
+            raise RuntimeError(f"{name}: status {rc}")
+
+    def fprop(self, x, w, theta):
+        import torch
+        N, C, H, W = x.shape
+        y = torch.empty_like(x)
+        self._call("o1d_refgpu_fprop", H, y, w, x, theta, N=N, C=C)
+        return y
+
+    def dgrad(self, dy, w, theta):
+        import torch
+        N, C, H, W = dy.shape
+        dx = torch.empty_like(dy)
+        self._call("o1d_refgpu_dgrad", H, dx, w, dy, theta, N=N, C=C)
+        return dx
+
+    def wgrad(self, dy, x, theta, K=31):
+        import torch
+        N, C, H, W = x.shape
+        dw = torch.empty((C, 1, 1, K), dtype=x.dtype, device=x.device)
+        self._call("o1d_refgpu_wgrad", H, dw, dy, x, theta, N=N, C=C)
+        return dw
+
+    def transpose(self, t, n, a, b, out_shape):
+        import torch
+        out = torch.empty(out_shape, dtype=t.dtype, device=t.device)
+        rc = self._lib.o1d_refgpu_transpose(n, a, b, ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(t.data_ptr()),
+                                            self._stream())
+        if rc:
+            raise RuntimeError(f"o1d_refgpu_transpose: status {rc}")
+        return out

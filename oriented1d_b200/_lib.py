@@ -23,6 +23,7 @@ SIGNATURES = {
     "o1d_last_error": (ctypes.c_char_p, []),
     "o1d_set_route": (_c_int, [_c_int]),
     "o1d_device_status": (_c_int, [ctypes.POINTER(_c_int)]),
+    "o1d_uses_tiled": (_c_int, [_c_void_p] + [_c_int] * 8),
     "o1d_offsets": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p]),
     "o1d_plan_bytes": (_c_size_t, [_c_int, _c_int]),
     "o1d_plan_build": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p]),

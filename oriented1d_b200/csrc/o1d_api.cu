@@ -231,6 +231,16 @@ int o1d_device_status(int *flag_out) {
     return O1D_OK;
 }
 
+int o1d_uses_tiled(const void *plan_host, int N, int H, int W, int C, int K, int stride, int layout, int dtype) {
+    if (bad_common(N, H, W, C, K, stride, layout, dtype) || g_force_generic) return 0;
+    PlanHeader ph;
+    if (check_plan(plan_host, C, K, &ph)) return 0;
+    TiledConfig cfg;
+    // 148 SMs / 227 KB: the B200 values; the answer does not depend on a device being present
+    return tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, dtype == O1D_F32 ? 4 : 2, 232448, 148,
+                           OP_FPROP, &cfg) ? 1 : 0;
+}
+
 int o1d_offsets(const float *theta_host, int C, int K, int8_t *dh, int8_t *dw) {
     if (!theta_host || !dh || !dw || C <= 0 || K <= 0 || (K & 1) == 0 || K > 255) return O1D_ERR_INVALID;
     for (int c = 0; c < C; c++) raster(theta_host[c], K, dh + (size_t)c * K, dw + (size_t)c * K);

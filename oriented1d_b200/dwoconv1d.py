@@ -31,14 +31,29 @@ __all__ = ["DepthwiseOrientedConv1d", "get_dwoconv1d_kernel", "oriented_dwconv1d
 
 
 class _DepthwiseOrientedConv1d(torch.autograd.Function):
-    """Counterpart of the reference's autograd function (dwoconv1d.py:18-69)."""
+    """Counterpart of the reference's autograd function (dwoconv1d.py:18-69).
+
+    NCHW inputs whose NHWC form qualifies for the tiled kernels are converted once on the
+    way in and out (two 128-bit transposes cost far less than the general NCHW kernels); the
+    NHWC copy of x is what is saved for backward.  The reference does the opposite: it
+    converts NHWC inputs to NCHW around NCHW-only kernels (dwoconv1d.py:25-26,36-37)."""
 
     @staticmethod
     def forward(ctx, x, w, theta, bias, plan, stride, nhwc=False, add_identity=False):
         x = x.contiguous()
         ctx.set_materialize_grads(False)
+        via_nhwc = False
+        if not nhwc and x.is_cuda and x.dim() == 4:
+            N, C, H, W = x.shape
+            via_nhwc = (ops.uses_tiled(plan, N, H, W, stride, True, x.dtype)
+                        and not ops.uses_tiled(plan, N, H, W, stride, False, x.dtype))
         ctx.plan, ctx.stride, ctx.nhwc, ctx.add_identity = plan, stride, nhwc, add_identity
+        ctx.via_nhwc = via_nhwc
         ctx.has_bias = bias is not None
+        if via_nhwc:
+            xh = ops.nchw_to_nhwc(x)
+            ctx.save_for_backward(xh, w)
+            return ops.nhwc_to_nchw(ops.fprop(xh, w, bias, plan, stride, True, add_identity))
         ctx.save_for_backward(x, w)
         return ops.fprop(x, w, bias, plan, stride, nhwc, add_identity)
 
@@ -50,16 +65,21 @@ class _DepthwiseOrientedConv1d(torch.autograd.Function):
         dy = dy.contiguous()
         if dy.dtype != x.dtype:
             dy = dy.to(x.dtype)
+        nhwc = ctx.nhwc or ctx.via_nhwc           # layout of the saved x and of the kernels
+        if ctx.via_nhwc:
+            dy = ops.nchw_to_nhwc(dy)
         dx = dw = db = None
-        if ctx.nhwc:
+        if nhwc:
             H, W = x.shape[1], x.shape[2]
         else:
             H, W = x.shape[2], x.shape[3]
         if ctx.needs_input_grad[0]:
-            dx = ops.dgrad(dy, w, ctx.plan, H, W, ctx.stride, ctx.nhwc, ctx.add_identity)
+            dx = ops.dgrad(dy, w, ctx.plan, H, W, ctx.stride, nhwc, ctx.add_identity)
+            if ctx.via_nhwc:
+                dx = ops.nhwc_to_nchw(dx)
         need_db = ctx.has_bias and ctx.needs_input_grad[3]
         if ctx.needs_input_grad[1] or need_db:
-            dw, db = ops.wgrad(dy, x, ctx.plan, ctx.stride, ctx.nhwc, with_bias=need_db)
+            dw, db = ops.wgrad(dy, x, ctx.plan, ctx.stride, nhwc, with_bias=need_db)
             dw = dw.to(w.dtype) if ctx.needs_input_grad[1] else None
             # bias shares the weight's dtype in an nn.Conv2d
             db = db.to(w.dtype) if need_db else None

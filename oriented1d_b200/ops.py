@@ -158,6 +158,14 @@ def nchw_to_nhwc(x):
     return _transpose(x, N, C, H * W, (N, H, W, C))
 
 
+def uses_tiled(plan: Plan, N: int, H: int, W: int, stride: int, nhwc: bool, dtype: torch.dtype) -> bool:
+    """Would this request run on the tiled kernels (True) or the general ones (False)?"""
+    code = _DTYPES.get(dtype)
+    if code is None:
+        return False
+    return bool(lib.o1d_uses_tiled(plan.host.data_ptr(), N, H, W, plan.C, plan.K, stride, int(nhwc), code))
+
+
 def set_route(general_only: bool) -> None:
     """Testing aid: True routes every call to the general kernels, False restores the
     automatic choice (tiled kernels where they apply)."""

@@ -318,3 +318,44 @@ def test_tiled_short_kernels(oracle, K):
     assert rel_err(_to_nchw(y, True), oracle.fprop(x, w, th, 1)) <= TOL_FPROP
     assert rel_err(_to_nchw(dx, True), oracle.dgrad(dy, w, th, 1)) <= TOL_DGRAD
     assert rel_err(dw.cpu().numpy(), oracle.wgrad_f64(dy, x, th, K, 1)) <= TOL_WGRAD
+
+
+def test_nchw_module_takes_the_tiled_route(oracle):
+    """An NCHW module whose NHWC form qualifies for the tiled kernels converts layout on the
+    way in and out; results and gradients still match the oracle (NCHW)."""
+    N, C, hw, K = 3, 96, 28, 31
+    x, w, dy = make_inputs(77, N, C, hw, hw, K)
+    th = angle_list("model", C)
+    bias = np.linspace(-0.5, 0.5, C).astype(np.float32)
+    m = o1d.DepthwiseOrientedConv1d(C, C, K, groups=C, padding=K // 2, angle=[float(a) for a in th]).to(DEV)
+    with torch.no_grad():
+        m.weight.copy_(torch.from_numpy(w))
+        m.bias.copy_(torch.from_numpy(bias))
+    assert o1d.ops.uses_tiled(m._get_plan(), N, hw, hw, 1, True, torch.float32)
+    assert not o1d.ops.uses_tiled(m._get_plan(), N, hw, hw, 1, False, torch.float32)
+    xd = torch.from_numpy(x).to(DEV).requires_grad_(True)
+    y = m(xd)
+    assert y.shape == xd.shape and y.is_contiguous()
+    y.backward(torch.from_numpy(dy).to(DEV))
+    ry = O.module_forward(oracle, x, w, th, bias, 1, False, False)
+    rdx, rdw, rdb = O.module_backward(oracle, x, w, th, dy, bias, 1, False, False)
+    assert rel_err(y.detach().cpu().numpy(), ry) <= TOL_FPROP
+    assert rel_err(xd.grad.cpu().numpy(), rdx) <= TOL_DGRAD
+    assert rel_err(m.weight.grad.cpu().numpy(), oracle.wgrad_f64(dy, x, th, K, 1)) <= TOL_WGRAD
+    assert rel_err(m.bias.grad.cpu().numpy(), rdb) <= TOL_WGRAD
+
+
+@pytest.mark.skipif(not O.ReferenceGPU.available(), reason="reference CUDA kernels not built (oracle/build.py --gpu-reference)")
+@pytest.mark.parametrize("hw,C", [(56, 16), (28, 16), (14, 24), (7, 32)])
+def test_reference_cuda_kernels_agree_with_the_cpu_loops(oracle, hw, C):
+    """The reference's own specialised CUDA kernels (device sincosf rasterisation, fp32
+    atomics in wgrad) against its CPU loops: pins the GPU baseline that bench.py times, and
+    shows the device rasterisation lands on the same pixels as the host one."""
+    ref = O.ReferenceGPU()
+    N, K = 2, 31
+    x, w, dy = make_inputs(hw + C, N, C, hw, hw, K)
+    th = angle_list("rr", C)
+    xd, wd, dyd, thd = (torch.from_numpy(a).to(DEV) for a in (x, w, dy, th))
+    assert rel_err(ref.fprop(xd, wd, thd).cpu().numpy(), oracle.fprop(x, w, th, 1)) <= TOL_FPROP
+    assert rel_err(ref.dgrad(dyd, wd, thd).cpu().numpy(), oracle.dgrad(dy, w, th, 1)) <= TOL_DGRAD
+    assert rel_err(ref.wgrad(dyd, xd, thd).cpu().numpy(), oracle.wgrad_f64(dy, x, th, K, 1)) <= TOL_WGRAD
