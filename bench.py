@@ -464,6 +464,100 @@ def run_case(args):
                       "device_status": o1d.ops.device_status()}))
 
 
+def run_model(args):
+    """ConvNeXt-T-1D inference (BASELINE.json configs[2]): depths 3/3/9/3, dims 96..768, K=31
+    oriented convs in every block and in the stem, 1000 classes, random init, bf16, batch 256
+    per GPU of synthetic N(0,1) 224x224 images, batch-sharded over the GPUs with no collective."""
+    import torch
+    import torch.distributed as dist
+
+    import oriented1d_b200 as o1d
+    from oriented1d_b200 import convnext1d
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("NCCL_DEBUG", "WARN")
+        dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(rank)
+    batch = args.batch if args.batch != 64 else 256
+    model = convnext1d.convnext_tiny(variant="1d", drop_path_rate=0.0).to(dev).bfloat16().eval()
+    nsets = 3
+    imgs = [torch.randn((batch, 3, 224, 224), device=dev).bfloat16() for _ in range(nsets)]
+    host_img = torch.randn((batch, 3, 224, 224)).bfloat16().pin_memory()
+    host_out = torch.empty((batch, 1000), dtype=torch.bfloat16).pin_memory()
+    state = {"i": 0}
+
+    def step():
+        state["i"] = (state["i"] + 1) % nsets
+        with torch.no_grad():
+            return model(imgs[state["i"]])
+
+    def e2e_step():
+        with torch.no_grad():
+            out = model(host_img.to(dev, non_blocking=True))
+        host_out.copy_(out, non_blocking=True)
+
+    def timed(fn, steps, warmup, graph):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        runner, per = fn, 1
+        if graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(nsets):
+                    fn()
+            g.replay()
+            runner, per = g.replay, nsets
+        reps = max(1, -(-steps // per))
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            runner()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = e0.elapsed_time(e1) * steps / (reps * per)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    warm = max(args.warmup, 3)
+    with ClockSampler(local) as clk:
+        ms = timed(step, args.steps, warm, graph=not args.no_graph)
+        time.sleep(0.25)
+    e2e_ms = timed(e2e_step, max(2, min(args.steps, 5)), 2, graph=False)
+    n_e2e = max(2, min(args.steps, 5))
+    # oriented-conv launches per forward: 2 stem convs + 18 block convs
+    if rank == 0:
+        print(json.dumps({
+            "metric": "ConvNeXt-T-1D inference throughput @224", "value": batch * world * args.steps / (ms / 1e3),
+            "unit": "img/s", "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "ConvNeXt-T-1D inference: depths 3/3/9/3, dims 96-768, K=31, 8 orientations, "
+                                   f"batch {batch} per GPU, 224x224x3 bf16, random init, 1000 classes",
+                       "l2": "activations exceed L2; 3 input batches rotate",
+                       "launch": "eager" if args.no_graph else "CUDA graph replay",
+                       "parallelism": f"dp{world} (batch-sharded, no collective)"},
+            "e2e": {"value": batch * world * n_e2e / (e2e_ms / 1e3), "unit": "img/s",
+                    "h2d_bytes_per_step": host_img.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2,
+                    "ms_per_step": e2e_ms / n_e2e},
+            "gpu_launches": 20 * args.steps, "clocks": clk.summary(),
+            "roofline": None, "cpu_baseline": None}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def block_angles(C, n=8):
     """The models' assignment: blocks of ~C/n consecutive channels share an angle
     (reference: models/convnext.py:60-65)."""
@@ -480,6 +574,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's CUDA kernels")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graphs")
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "model"],
+                    help="sweep: kernel sweep at the stage shapes (default); model: ConvNeXt-T-1D inference")
     ap.add_argument("--case", default=None, help="run one kernel case alone, e.g. fprop_f32_56x56x96")
     ap.add_argument("--batch", type=int, default=64, help="batch for --case")
     ap.add_argument("--reps", type=int, default=3, help="launches for --case")
@@ -487,6 +583,8 @@ def main():
     args = ap.parse_args()
     if args.case:
         run_case(args)
+    elif args.workload == "model":
+        run_model(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -1,0 +1,220 @@
+"""ConvNeXt-1D / ConvNeXt-1D++ built on the oriented 1D depthwise convolution.
+
+The caller side of the hot path: a timm-free restatement of the reference model
+(``models/convnext.py``: angle helpers :60-77, ``get_convolution_1d`` :80-128, ``Stem1D``
+:132-191, ``Block1D`` :255-319, ``Block1DPP`` :322-399, ``ConvNeXt`` :495-610, factories
+:613-644) with the same module tree and therefore the same state-dict keys and shapes
+(``downsample_layers.0.dw1.weight [64,1,1,31]``, ``stages.0.0.dwconv.theta [96]`` ...), so
+reference checkpoints load with ``load_state_dict``.
+
+What differs is data movement only.  The reference keeps activations NCHW between blocks and
+makes two full ``permute().contiguous()`` copies per block around the channels-last MLP
+(``convnext.py:308,316``), and its NCHW kernels add two more transposes whenever a conv is
+NHWC.  Here activations stay channels-last (NHWC) from the stem to the pooling: every
+depthwise conv runs its native NHWC kernel, LayerNorm / Linear / GELU already want NHWC, and
+the 2x2 stride-2 downsampling conv sees the same memory as a channels_last NCHW view.  The
+arithmetic of every layer is unchanged.  Inputs and outputs keep the reference convention
+(images ``[N,3,H,W]`` in, logits out).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .dwoconv1d import DepthwiseOrientedConv1d
+
+__all__ = ["ConvNeXt1D", "convnext_tiny", "convnext_base", "get_convolution_1d"]
+
+BLOCK_KERNELS = {"1d": [[31]] * 4, "1dpp": [[15, 31]] * 4}     # convnext.py:483-488
+STEM_KERNEL = {"1d": 31, "1dpp": 15}                           # convnext.py:490
+
+
+def channel_cycle_offset(c, C, N):
+    """convnext.py:60-65: N groups of ~C/N channels, group n has angle n/N * 180 degrees."""
+    return ((N * (c + 1) - 1) // C) / N
+
+
+def layer_wise_rotation_offset(k, enable_layer_cycle=0):
+    """convnext.py:68-72: +90 degrees on layers at odd depth."""
+    return (k % 2) / 2 if enable_layer_cycle else 0
+
+
+def get_convolution_1d(channels, *, kernel_size, padding, stride=1, N=8, layer_offset=0, nhwc=False,
+                       resid=False, bias=True, arbitrary_size=False):
+    """convnext.py:80-128."""
+    theta = [math.pi * ((channel_cycle_offset(k, channels, N) + layer_offset) % 1) for k in range(channels)]
+    return DepthwiseOrientedConv1d(channels, channels, kernel_size, groups=channels, stride=stride, nhwc=nhwc,
+                                   resid=resid, padding=padding, bias=bias, angle=theta,
+                                   arbitrary_size=arbitrary_size)
+
+
+class LayerNorm(nn.Module):
+    """LayerNorm over channels with the reference's parameter names (convnext.py:28-56).  The
+    data here is always channels-last, for which the reference's channels_first formula and
+    F.layer_norm are the same computation."""
+
+    def __init__(self, normalized_shape, eps=1e-6, data_format="channels_last"):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(normalized_shape))
+        self.bias = nn.Parameter(torch.zeros(normalized_shape))
+        self.eps, self.data_format, self.normalized_shape = eps, data_format, (normalized_shape,)
+
+    def forward(self, x):
+        return F.layer_norm(x, self.normalized_shape, self.weight, self.bias, self.eps)
+
+
+class Stem1D(nn.Module):
+    """convnext.py:132-191; input and output channels-last."""
+
+    def __init__(self, dim0, dim1, dim2, kernel_size, enable_layer_cycle=0, arbitrary_size=False):
+        super().__init__()
+        self.pw1 = nn.Linear(dim0, dim1)
+        self.pw2 = nn.Linear(dim1, dim2)
+        pad = (kernel_size - 2) // 2
+        self.dw1 = get_convolution_1d(dim1, kernel_size=kernel_size, stride=2, padding=pad, nhwc=True,
+                                      layer_offset=layer_wise_rotation_offset(0, enable_layer_cycle),
+                                      arbitrary_size=arbitrary_size)
+        self.dw2 = get_convolution_1d(dim1, kernel_size=kernel_size, stride=2, padding=pad, nhwc=True,
+                                      layer_offset=layer_wise_rotation_offset(1, enable_layer_cycle),
+                                      arbitrary_size=arbitrary_size)
+        self.norm1 = LayerNorm(dim1)
+        self.norm2 = LayerNorm(dim1)
+        self.norm3 = LayerNorm(dim2)
+
+    def forward(self, x):                       # x: [N, H, W, 3]
+        x = self.pw1(x)
+        x = F.gelu(self.norm1(self.dw1(x)))
+        x = F.gelu(self.norm2(self.dw2(x)))
+        return self.norm3(self.pw2(x))
+
+
+class Block1D(nn.Module):
+    """convnext.py:255-319; channels-last in and out (no permute copies)."""
+
+    def __init__(self, dim, kernel_sizes=(31,), N=8, drop_path=0.0, layer_scale_init_value=1e-6, layer_offset=0,
+                 arbitrary_size=False):
+        super().__init__()
+        self.norm = LayerNorm(dim)
+        self.pwconv1 = nn.Linear(dim, 4 * dim)
+        self.pwconv2 = nn.Linear(4 * dim, dim)
+        self.gamma = (nn.Parameter(layer_scale_init_value * torch.ones(dim)) if layer_scale_init_value > 0 else None)
+        self.drop_path = drop_path
+        # the reference builds this conv NCHW (nhwc=False, convnext.py:297); the flag is not part
+        # of the checkpoint, and the data here is NHWC
+        self.dwconv = get_convolution_1d(dim, kernel_size=kernel_sizes[0], padding=kernel_sizes[0] // 2, nhwc=True,
+                                         N=N, layer_offset=layer_offset, arbitrary_size=arbitrary_size)
+
+    def _mlp_in(self, x):
+        return F.gelu(self.pwconv1(self.norm(x)))
+
+    def forward(self, x):
+        y = self.pwconv2(self._mlp_in(self.dwconv(x)))
+        if self.gamma is not None:
+            y = self.gamma * y
+        return x + _drop_path(y, self.drop_path, self.training)
+
+
+class Block1DPP(Block1D):
+    """convnext.py:322-399: a second oriented conv (K=31, identity tap) on the 4*dim hidden tensor."""
+
+    def __init__(self, dim, kernel_sizes=(15, 31), N=8, drop_path=0.0, layer_scale_init_value=1e-6,
+                 layer_offset=0, arbitrary_size=False):
+        super().__init__(dim, kernel_sizes[:1], N, drop_path, layer_scale_init_value, layer_offset, arbitrary_size)
+        self.dwconv1 = self.dwconv                     # reference names: dwconv1, dwconv2
+        del self.dwconv
+        self.dwconv2 = get_convolution_1d(4 * dim, kernel_size=kernel_sizes[1], padding=kernel_sizes[1] // 2,
+                                          nhwc=True, resid=True, N=N, layer_offset=layer_offset,
+                                          arbitrary_size=arbitrary_size)
+
+    def forward(self, x):
+        y = self.pwconv2(self.dwconv2(self._mlp_in(self.dwconv1(x))))
+        if self.gamma is not None:
+            y = self.gamma * y
+        return x + _drop_path(y, self.drop_path, self.training)
+
+
+def _drop_path(y, rate, training):
+    """Stochastic depth per sample (timm DropPath semantics, as used at convnext.py:292)."""
+    if rate == 0.0 or not training:
+        return y
+    keep = 1.0 - rate
+    mask = y.new_empty((y.shape[0],) + (1,) * (y.dim() - 1)).bernoulli_(keep)
+    return y * mask / keep
+
+
+class Downsample(nn.Sequential):
+    """LayerNorm + 2x2 stride-2 conv (convnext.py:553-559), on channels-last data: the conv
+    runs on the NCHW view of the same memory (channels_last strides, no copy)."""
+
+    def __init__(self, cin, cout):
+        super().__init__(LayerNorm(cin, data_format="channels_first"), nn.Conv2d(cin, cout, kernel_size=2, stride=2))
+
+    def forward(self, x):                       # [N, H, W, C] -> [N, H/2, W/2, C']
+        x = self[0](x)
+        y = self[1](x.permute(0, 3, 1, 2))      # view; memory format channels_last
+        return y.permute(0, 2, 3, 1).contiguous()     # contiguous already unless cuDNN chose NCHW
+
+
+class ConvNeXt1D(nn.Module):
+    """convnext.py:495-610 for variant in {"1d", "1dpp"}."""
+
+    def __init__(self, in_chans=3, num_classes=1000, depths=(3, 3, 9, 3), dims=(96, 192, 384, 768),
+                 drop_path_rate=0.0, layer_scale_init_value=1e-6, head_init_scale=1.0, variant="1d", N=8,
+                 stem_dim1=64, arbitrary_size=False):
+        super().__init__()
+        assert variant in ("1d", "1dpp")
+        Block = Block1D if variant == "1d" else Block1DPP
+        self.downsample_layers = nn.ModuleList([Stem1D(in_chans, stem_dim1, dims[0], STEM_KERNEL[variant], 1,
+                                                       arbitrary_size)])
+        for i in range(3):
+            self.downsample_layers.append(Downsample(dims[i], dims[i + 1]))
+        rates = torch.linspace(0, drop_path_rate, sum(depths)).tolist()
+        self.stages = nn.ModuleList()
+        cur = 0
+        for i in range(4):
+            self.stages.append(nn.Sequential(*[
+                Block(dims[i], kernel_sizes=BLOCK_KERNELS[variant][i], N=N, drop_path=rates[cur + j],
+                      layer_scale_init_value=layer_scale_init_value,
+                      layer_offset=layer_wise_rotation_offset(j, 1), arbitrary_size=arbitrary_size)
+                for j in range(depths[i])]))
+            cur += depths[i]
+        self.norm = nn.LayerNorm(dims[-1], eps=1e-6)
+        self.head = nn.Linear(dims[-1], num_classes)
+        self.apply(self._init_weights)
+        self.head.weight.data.mul_(head_init_scale)
+        self.head.bias.data.mul_(head_init_scale)
+
+    @staticmethod
+    def _init_weights(m):
+        if isinstance(m, (nn.Conv2d, nn.Linear)):           # the oriented conv is an nn.Conv2d too
+            nn.init.trunc_normal_(m.weight, std=0.02)
+            if m.bias is not None:
+                nn.init.constant_(m.bias, 0)
+
+    def forward_features(self, x, all_stages=False):
+        """x: images [N, 3, H, W].  Returns the last stage's map [N, C, H/32, W/32] (NCHW view),
+        or the four stage maps when all_stages is set (the dense-prediction backbones' outputs)."""
+        x = x.permute(0, 2, 3, 1)
+        outs = []
+        for i in range(4):
+            x = self.stages[i](self.downsample_layers[i](x))
+            outs.append(x.permute(0, 3, 1, 2))
+        return outs if all_stages else outs[-1]
+
+    def forward(self, x):
+        x = self.forward_features(x)
+        return self.head(self.norm(x.mean([-2, -1])))
+
+
+def convnext_tiny(variant="1d", drop_path_rate=0.1, **kw):
+    """convnext.py:613-627."""
+    return ConvNeXt1D(depths=(3, 3, 9, 3), dims=(96, 192, 384, 768), drop_path_rate=drop_path_rate, variant=variant, **kw)
+
+
+def convnext_base(variant="1d", drop_path_rate=0.5, **kw):
+    """convnext.py:630-644."""
+    return ConvNeXt1D(depths=(3, 3, 27, 3), dims=(128, 256, 512, 1024), drop_path_rate=drop_path_rate,
+                      variant=variant, **kw)

@@ -85,6 +85,24 @@ int launch_generic_fprop(const void *x, const float *w, const float *bias, const
                          int add_identity, cudaStream_t st, const DeviceInfo &d) {
     const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
     PlanView pv = plan_view(plan_dev, ph);
+    // NHWC with class-uniform channel vectors: 128-bit loads per tap
+    constexpr int VE = 16 / (int)sizeof(T);
+    const bool uniform = (VE == 4) ? ph.uniform4 != 0 : ph.uniform8 != 0;
+    if (LAYOUT == O1D_NHWC && uniform && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0) {
+        const int tapb = (ph.ncls * K * 2 + 15) & ~15;
+        const int wb = C * K * 4;
+        if (tapb <= kTapSmemBudget) {
+            const int w_staged = (tapb + wb <= 96 * 1024);
+            const int smem = tapb + (w_staged ? wb : 0);
+            auto kern = generic_fprop_nhwc_vec_kernel<T>;
+            if (smem > 48 * 1024) O1D_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            const int grid = grid_for((int64_t)N * P * Q * (C / VE), kGenericThreads, d, 8);
+            kern<<<grid, kGenericThreads, smem, st>>>((const T *)x, w, bias, pv.cls, pv.taps, ph.ncls, w_staged,
+                                                       (T *)y, N, H, W, C, K, stride, P, Q, add_identity);
+            O1D_CUDA(cudaGetLastError());
+            return O1D_OK;
+        }
+    }
     const int tap_bytes = ph.ncls * K * 2;
     const int staged = tap_bytes <= kTapSmemBudget;
     const int grid = grid_for((int64_t)N * P * Q * C, kGenericThreads, d, 16);
@@ -333,6 +351,12 @@ int o1d_plan_build(const float *theta_host, int C, int K, void *plan_host) {
     memcpy(b + h.comps_off, comps, sizeof(comps));
     for (int c = 0; c < C; c++) b[h.chan_off + c] = canon_of[cls[c]];
     h.all_canon = all_canon;
+    h.uniform4 = (C % 4 == 0);
+    h.uniform8 = (C % 8 == 0);
+    for (int c = 0; c < C; c++) {
+        if (cls[c] != cls[c & ~3]) h.uniform4 = 0;
+        if (cls[c] != cls[c & ~7]) h.uniform8 = 0;
+    }
     memcpy(b, &h, sizeof(h));
     return O1D_OK;
 }

@@ -42,7 +42,8 @@ struct PlanHeader {
     int32_t all_canon;        // 1 when every class has canon >= 0
     uint32_t cls_off, taps_off, canon_off, total_bytes;
     uint32_t comps_off, chan_off;
-    uint32_t reserved[3];
+    int32_t uniform4, uniform8;   // every aligned group of 4 / 8 channels shares one class
+    uint32_t reserved[1];
 };
 static_assert(sizeof(PlanHeader) == 64, "plan header is 64 bytes");
 

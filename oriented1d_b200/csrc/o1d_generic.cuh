@@ -68,6 +68,99 @@ generic_fprop_kernel(const T *__restrict__ x, const float *__restrict__ w,
     }
 }
 
+// Forward, NHWC, 16-byte channel vectors: a thread owns VE = 16/sizeof(T) consecutive channels
+// of one output pixel.  Requires that every aligned group of VE channels shares one
+// orientation class (true for the models' block assignment, models/convnext.py:60-65), so the
+// group moves along one line and each tap is one 128-bit load.  Weights are staged in shared
+// memory transposed ([k][C]) when they fit.  Used for what the tiled kernels do not take
+// (stride 2 stems, large images).
+template <typename T> struct GVec;
+template <> struct GVec<float> {
+    static constexpr int N = 4;
+    __device__ static void unpack(const uint4 &v, float (&f)[4]) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    }
+    __device__ static uint4 pack(const float (&f)[4]) {
+        return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+    }
+};
+template <> struct GVec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ static void unpack(const uint4 &v, float (&f)[8]) {
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) { f[2 * i] = __uint_as_float(u[i] << 16); f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+    }
+    __device__ static uint4 pack(const float (&f)[8]) {
+        uint32_t u[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            u[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(u[0], u[1], u[2], u[3]);
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kGenericThreads)
+generic_fprop_nhwc_vec_kernel(const T *__restrict__ x, const float *__restrict__ w,
+                              const float *__restrict__ bias, const uint16_t *__restrict__ cls,
+                              const int8_t *__restrict__ taps_gmem, int ncls, int w_staged,
+                              T *__restrict__ y, int N, int H, int W, int C, int K, int stride,
+                              int P, int Q, int add_identity) {
+    constexpr int VE = GVec<T>::N;
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    // [taps: ncls*K*2 bytes, padded to 16] [weights: K*C floats, if staged]
+    int8_t *s_taps = reinterpret_cast<int8_t *>(s_raw);
+    const int tap_bytes = (ncls * K * 2 + 15) & ~15;
+    float *s_w = reinterpret_cast<float *>(s_raw + tap_bytes);
+    for (int i = threadIdx.x; i < ncls * K * 2; i += blockDim.x) s_taps[i] = taps_gmem[i];
+    const int pad = K / 2;
+    if (w_staged)
+        for (int i = threadIdx.x; i < C * K; i += blockDim.x) {
+            const int c = i / K, k = i - c * K;
+            s_w[k * C + c] = __ldg(w + i) + ((add_identity && k == pad) ? 1.f : 0.f);
+        }
+    __syncthreads();
+    const int G = C / VE;
+    const int64_t total = (int64_t)N * P * Q * G;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        int64_t r = idx;
+        const int g = (int)(r % G); r /= G;
+        const int q = (int)(r % Q); r /= Q;
+        const int p = (int)(r % P);
+        const int n = (int)(r / P);
+        const int c0 = g * VE;
+        const int8_t *t = s_taps + (size_t)cls[c0] * K * 2;
+        float acc[VE];
+#pragma unroll
+        for (int j = 0; j < VE; j++) acc[j] = bias ? __ldg(bias + c0 + j) : 0.f;
+        for (int k = 0; k < K; k++) {
+            const int h = p * stride + t[2 * k], ww = q * stride + t[2 * k + 1];
+            if ((unsigned)h < (unsigned)H && (unsigned)ww < (unsigned)W) {
+                float xv[VE], wv[VE];
+                GVec<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(x + (((int64_t)n * H + h) * W + ww) * C + c0)), xv);
+                if (w_staged) {
+#pragma unroll
+                    for (int j = 0; j < VE; j += 4) {
+                        const float4 f = *reinterpret_cast<const float4 *>(s_w + k * C + c0 + j);
+                        wv[j] = f.x; wv[j + 1] = f.y; wv[j + 2] = f.z; wv[j + 3] = f.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < VE; j++)
+                        wv[j] = __ldg(w + (size_t)(c0 + j) * K + k) + ((add_identity && k == pad) ? 1.f : 0.f);
+                }
+#pragma unroll
+                for (int j = 0; j < VE; j++) acc[j] = fmaf(xv[j], wv[j], acc[j]);
+            }
+        }
+        *reinterpret_cast<uint4 *>(y + idx * VE) = GVec<T>::pack(acc);
+    }
+}
+
 // dx[n,c,h,w] = sum_k w'[c,k] dy[n,c,(h-dh_k)/s,(w-dw_k)/s], taken only where both
 // differences are non-negative multiples of s inside [0,P)x[0,Q)     (kernels.cpp:71-90)
 template <typename T, int LAYOUT>
