@@ -143,6 +143,16 @@ int o1d_wgrad_static(const void *dy, const void *x,
                      int N, int H, int W, int C, int K, int stride,
                      int layout, int dtype, void *stream);
 
+/* LayerNorm over the contiguous channel axis of a channels-last tensor, y = (x - mean) /
+ * sqrt(var + eps) * gamma + beta, optionally followed by exact (erf) GELU: the step that
+ * follows every oriented convolution in the reference's blocks and stems
+ * (models/convnext.py:28-56 LayerNorm, :183-189 stem LayerNorm+GELU, :309 block norm; the
+ * reference calls F.layer_norm / F.gelu).  x, y: [rows, C] fp32 or bf16; gamma, beta: [C]
+ * fp32; statistics in fp32, biased variance.  C must be a multiple of 4 (fp32) / 8 (bf16)
+ * and at most 1024 (fp32) / 2048 (bf16).  Forward only. */
+int o1d_layernorm_cl(const void *x, const float *gamma, const float *beta, void *y,
+                     long long rows, int C, float eps, int dtype, int gelu, void *stream);
+
 /* Batched 2-D transpose [n, a, b] -> [n, b, a].  Replaces nhwc_to_nchw / nchw_to_nhwc
  * (kernels.cu:56-68, nhwc_utils.h:46-110): NHWC->NCHW is (n=N, a=H*W, b=C),
  * NCHW->NHWC is (n=N, a=C, b=H*W). */

@@ -24,6 +24,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import ops
 from .dwoconv1d import DepthwiseOrientedConv1d
 
 __all__ = ["ConvNeXt1D", "convnext_tiny", "convnext_base", "get_convolution_1d"]
@@ -62,8 +63,15 @@ class LayerNorm(nn.Module):
         self.bias = nn.Parameter(torch.zeros(normalized_shape))
         self.eps, self.data_format, self.normalized_shape = eps, data_format, (normalized_shape,)
 
-    def forward(self, x):
-        return F.layer_norm(x, self.normalized_shape, self.weight, self.bias, self.eps)
+    def forward(self, x, gelu=False):
+        """gelu=True also applies exact GELU (the stem's LayerNorm -> GELU pairs)."""
+        C = x.shape[-1]
+        fast = (x.is_cuda and not torch.is_grad_enabled() and x.dtype in (torch.float32, torch.bfloat16)
+                and C % (4 if x.dtype == torch.float32 else 8) == 0 and C <= 1024)
+        if fast:      # inference: one pass over the tensor (see csrc/o1d_layernorm.cuh)
+            return ops.layer_norm_cl(x, self.weight, self.bias, self.eps, gelu)
+        y = F.layer_norm(x, self.normalized_shape, self.weight, self.bias, self.eps)
+        return F.gelu(y) if gelu else y
 
 
 class Stem1D(nn.Module):
@@ -86,8 +94,8 @@ class Stem1D(nn.Module):
 
     def forward(self, x):                       # x: [N, H, W, 3]
         x = self.pw1(x)
-        x = F.gelu(self.norm1(self.dw1(x)))
-        x = F.gelu(self.norm2(self.dw2(x)))
+        x = self.norm1(self.dw1(x), gelu=True)
+        x = self.norm2(self.dw2(x), gelu=True)
         return self.norm3(self.pw2(x))
 
 

@@ -10,6 +10,7 @@
 #include "o1d_common.cuh"
 #include "o1d_generic.cuh"
 #include "o1d_tiled_host.cuh"
+#include "o1d_layernorm.cuh"
 #include "o1d_transpose.cuh"
 
 using namespace o1d;
@@ -499,6 +500,49 @@ int o1d_wgrad_static(const void *dy, const void *x, const void *plan_host, const
     }
     return O1D_DISPATCH(launch_generic_wgrad, dy, x, ph, plan_dev, dw, db, (float *)scratch, N, H, W, C, K, stride,
                         st);
+}
+
+}  // extern "C"
+
+namespace {
+template <typename T, int G, int VPL>
+int launch_ln(const void *x, const float *gamma, const float *beta, void *y, int64_t rows, int C, float eps, int gelu,
+              cudaStream_t st, const DeviceInfo &d) {
+    const int64_t groups = (rows * G + kLnThreads - 1) / kLnThreads;
+    const int64_t cap = (int64_t)d.sms * 16;
+    const int grid = (int)(groups < cap ? (groups > 0 ? groups : 1) : cap);
+    layernorm_cl_kernel<T, G, VPL><<<grid, kLnThreads, 0, st>>>((const T *)x, gamma, beta, (T *)y, rows, C, eps, gelu);
+    O1D_CUDA(cudaGetLastError());
+    return O1D_OK;
+}
+template <typename T>
+int dispatch_ln(const void *x, const float *gamma, const float *beta, void *y, int64_t rows, int C, float eps,
+                int gelu, cudaStream_t st, const DeviceInfo &d) {
+    const int nvec = C / (16 / (int)sizeof(T));
+    if (nvec <= 8) return launch_ln<T, 8, 1>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
+    if (nvec <= 16) return launch_ln<T, 16, 1>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
+    if (nvec <= 32) return launch_ln<T, 32, 1>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
+    if (nvec <= 64) return launch_ln<T, 32, 2>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
+    if (nvec <= 128) return launch_ln<T, 32, 4>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
+    if (nvec <= 256) return launch_ln<T, 32, 8>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
+    return O1D_ERR_UNSUPPORTED;
+}
+}  // namespace
+
+extern "C" {
+
+int o1d_layernorm_cl(const void *x, const float *gamma, const float *beta, void *y, long long rows, int C,
+                     float eps, int dtype, int gelu, void *stream) {
+    if (!x || !gamma || !beta || !y || rows <= 0 || C <= 0 || (dtype != O1D_F32 && dtype != O1D_BF16))
+        return O1D_ERR_INVALID;
+    const int ve = dtype == O1D_F32 ? 4 : 8;
+    if (C % ve != 0 || ((uintptr_t)x & 15) || ((uintptr_t)y & 15)) return O1D_ERR_UNSUPPORTED;
+    DeviceInfo d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    return dtype == O1D_F32 ? dispatch_ln<float>(x, gamma, beta, y, rows, C, eps, gelu, st, d)
+                            : dispatch_ln<__nv_bfloat16>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
 }
 
 int o1d_transpose(const void *in, void *out, int n, int a, int b, int dtype, void *stream) {

@@ -158,6 +158,22 @@ def nchw_to_nhwc(x):
     return _transpose(x, N, C, H * W, (N, H, W, C))
 
 
+def layer_norm_cl(x, weight, bias, eps: float = 1e-6, gelu: bool = False):
+    """LayerNorm over the last (contiguous) axis, optionally fused with exact GELU.  Forward
+    only (no autograd): for inference and for callers that handle gradients themselves."""
+    _need_cuda(x, weight, bias)
+    x = x.contiguous()
+    C = x.shape[-1]
+    rows = x.numel() // C
+    y = torch.empty_like(x)
+    g32 = weight.detach().to(torch.float32).contiguous()
+    b32 = bias.detach().to(torch.float32).contiguous()
+    with torch.cuda.device(x.device):
+        check(lib.o1d_layernorm_cl(x.data_ptr(), g32.data_ptr(), b32.data_ptr(), y.data_ptr(), rows, C, float(eps),
+                                   _dtype_code(x), int(gelu), _stream()), "o1d_layernorm_cl")
+    return y
+
+
 def uses_tiled(plan: Plan, N: int, H: int, W: int, stride: int, nhwc: bool, dtype: torch.dtype) -> bool:
     """Would this request run on the tiled kernels (True) or the general ones (False)?"""
     code = _DTYPES.get(dtype)

@@ -359,3 +359,20 @@ def test_reference_cuda_kernels_agree_with_the_cpu_loops(oracle, hw, C):
     assert rel_err(ref.fprop(xd, wd, thd).cpu().numpy(), oracle.fprop(x, w, th, 1)) <= TOL_FPROP
     assert rel_err(ref.dgrad(dyd, wd, thd).cpu().numpy(), oracle.dgrad(dy, w, th, 1)) <= TOL_DGRAD
     assert rel_err(ref.wgrad(dyd, xd, thd).cpu().numpy(), oracle.wgrad_f64(dy, x, th, K, 1)) <= TOL_WGRAD
+
+
+@pytest.mark.parametrize("C", [64, 96, 192, 384, 768, 1024])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_layernorm_channels_last(C, dtype):
+    """o1d_layernorm_cl against F.layer_norm (+ exact GELU) in float64 on the same inputs."""
+    g = torch.Generator(device="cpu").manual_seed(C)
+    x = (2.0 * torch.randn((3, 5, 7, C), generator=g) + 0.5).to(DEV).to(dtype)
+    w = torch.randn((C,), generator=g).to(DEV)
+    b = torch.randn((C,), generator=g).to(DEV)
+    for gelu in (False, True):
+        y = o1d.ops.layer_norm_cl(x, w, b, 1e-6, gelu).double()
+        ref = torch.nn.functional.layer_norm(x.double(), (C,), w.double(), b.double(), 1e-6)
+        if gelu:
+            ref = torch.nn.functional.gelu(ref)
+        tol = 1e-5 if dtype == torch.float32 else 2 ** -7        # bf16: one rounding of the output
+        assert float(((y - ref).abs() / ref.abs().clamp_min(1.0)).max()) <= tol
