@@ -55,8 +55,8 @@ const char *o1d_strerror(int status);
 /* Text of the last CUDA failure seen by the calling thread ("" if none). */
 const char *o1d_last_error(void);
 
-/* Kernel routing, for tests and A/B timing: 0 = automatic (tiled kernels where they apply,
- * general kernels otherwise), 1 = general kernels only.  Process-wide.  (No counterpart in
+/* Kernel routing, for tests and A/B timing: 0 = automatic, 1 = general kernels only,
+ * 2 = prefer the tiled kernels, 3 = prefer the direct kernels.  Process-wide.  (No counterpart in
  * the reference, which picks general vs specialised kernels with the SPECIALIZED
  * environment variable at import time, models/convnext.py:16-23.) */
 int o1d_set_route(int route);
@@ -67,7 +67,7 @@ int o1d_set_route(int route);
  * checks no launch or device errors at all, kernels.h:529,542,555.) */
 int o1d_device_status(int *flag_out);
 
-/* 1 if o1d_fprop / o1d_dgrad / o1d_wgrad would take the tiled (TMA-staged) kernels for this
+/* 1 if o1d_fprop would take one of the TMA-staged kernel families (tiled or direct) for this
  * request, 0 if the general kernels.  Lets a host decide whether converting an NCHW tensor
  * to NHWC first pays off (the tiled kernels are NHWC only).  Host-only; no counterpart in
  * the reference. */

@@ -10,6 +10,7 @@
 #include "o1d_common.cuh"
 #include "o1d_generic.cuh"
 #include "o1d_tiled_host.cuh"
+#include "o1d_direct_host.cuh"
 #include "o1d_layernorm.cuh"
 #include "o1d_transpose.cuh"
 
@@ -18,7 +19,8 @@ using namespace o1d;
 namespace {
 
 thread_local char g_err[256] = "";
-int g_force_generic = 0;   // o1d_set_route(): 1 = skip the tiled kernels (testing aid)
+int g_force_generic = 0;   // o1d_set_route(): 1 = general kernels only (testing aid)
+int g_prefer = 0;          // o1d_set_route(): 2 = prefer the tiled kernels, 3 = prefer the direct kernels
 
 int cuda_fail(cudaError_t e, const char *what) {
     snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
@@ -184,6 +186,49 @@ int try_tiled(const void *x, const float *w, const float *bias, const PlanHeader
     return O1D_OK;
 }
 
+// Forward / stride-1 input gradient through the direct kernels; kNotTiled when they do not apply.
+int try_direct(const void *x, const float *w, const float *bias, const PlanHeader &ph, const void *plan_host,
+               const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride, int layout, int dtype,
+               int add_identity, int flip, cudaStream_t st, const DeviceInfo &d, bool whole_image_only) {
+    if (g_force_generic) return kNotTiled;
+    const int esize = dtype == O1D_F32 ? 4 : 2;
+    DirectConfig cfg;
+    if (!direct_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, &cfg))
+        return kNotTiled;
+    if (whole_image_only && !cfg.whole_image) return kNotTiled;
+    if (((uintptr_t)y & 3) != 0) return kNotTiled;
+    CUtensorMap map;
+    if (!make_direct_tensor_map(&map, x, N, H, W, C, esize, cfg.p)) return kNotTiled;
+    cfg.p.flip = flip;
+    cfg.p.add_identity = add_identity;
+    PlanView pv = plan_view(plan_dev, ph);
+    const cudaError_t e = dtype == O1D_F32 ? launch_direct<float>(cfg, map, w, bias, pv, y, st)
+                                           : launch_direct<__nv_bfloat16>(cfg, map, w, bias, pv, y, st);
+    if (e != cudaSuccess) return cuda_fail(e, "direct fprop launch");
+    return O1D_OK;
+}
+
+// Route of a forward-type call (flip = 1: stride-1 input gradient):
+//   1. direct kernels when one tile holds a whole image (small maps),
+//   2. tiled kernels (canonical lines, stride 1, sizes in multiples of 7/8),
+//   3. direct kernels with row/column tiles (stems, large maps, arbitrary angles),
+//   4. general kernels (the caller falls through on kNotTiled).
+int route_forward(const void *x, const float *w, const float *bias, const PlanHeader &ph, const void *plan_host,
+                  const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride, int layout,
+                  int dtype, int add_identity, int flip, cudaStream_t st, const DeviceInfo &d) {
+    int rc = kNotTiled;
+    if (g_prefer != 2) {
+        rc = try_direct(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
+                        flip, st, d, /*whole_image_only=*/g_prefer != 3);
+        if (rc != kNotTiled) return rc;
+    }
+    rc = try_tiled(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity, flip,
+                   st, d);
+    if (rc != kNotTiled) return rc;
+    return try_direct(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
+                      flip, st, d, false);
+}
+
 // Weight gradient through the tiled kernels.  `cfg_only`: just report the workspace size.
 int try_tiled_wgrad(const void *dy, const void *x, const PlanHeader &ph, const void *plan_host,
                     const void *plan_dev, float *dw, float *db, void *workspace, size_t workspace_bytes, int N,
@@ -239,8 +284,9 @@ const char *o1d_strerror(int status) {
 const char *o1d_last_error(void) { return g_err; }
 
 int o1d_set_route(int route) {
-    if (route != 0 && route != 1) return O1D_ERR_INVALID;
-    g_force_generic = route;
+    if (route < 0 || route > 3) return O1D_ERR_INVALID;
+    g_force_generic = (route == 1);
+    g_prefer = (route >= 2) ? route : 0;
     return O1D_OK;
 }
 
@@ -254,10 +300,12 @@ int o1d_uses_tiled(const void *plan_host, int N, int H, int W, int C, int K, int
     if (bad_common(N, H, W, C, K, stride, layout, dtype) || g_force_generic) return 0;
     PlanHeader ph;
     if (check_plan(plan_host, C, K, &ph)) return 0;
-    TiledConfig cfg;
     // 148 SMs / 227 KB: the B200 values; the answer does not depend on a device being present
-    return tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, dtype == O1D_F32 ? 4 : 2, 232448, 148,
-                           OP_FPROP, &cfg) ? 1 : 0;
+    const int esize = dtype == O1D_F32 ? 4 : 2;
+    TiledConfig cfg;
+    if (tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, 232448, 148, OP_FPROP, &cfg)) return 1;
+    DirectConfig dcfg;
+    return direct_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, 232448, 148, &dcfg) ? 1 : 0;
 }
 
 int o1d_offsets(const float *theta_host, int C, int K, int8_t *dh, int8_t *dw) {
@@ -379,8 +427,8 @@ int o1d_fprop(const void *x, const float *w, const float *bias, const void *plan
     DeviceInfo d;
     if ((rc = device_info(&d))) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    rc = try_tiled(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
-                   /*flip=*/0, st, d);
+    rc = route_forward(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
+                       /*flip=*/0, st, d);
     if (rc != kNotTiled) return rc;
     return O1D_DISPATCH(launch_generic_fprop, x, w, bias, ph, plan_dev, y, N, H, W, C, K, stride,
                         add_identity, st, d);
@@ -398,8 +446,9 @@ int o1d_dgrad(const void *dy, const float *w, const void *plan_host, const void 
     cudaStream_t st = (cudaStream_t)stream;
     // stride 1: dx = fprop(dy) with the taps mirrored, i.e. (the lines being odd-symmetric)
     // with the weights read in reverse order
-    rc = try_tiled(dy, w, nullptr, ph, plan_host, plan_dev, dx, N, H, W, C, K, stride, layout, dtype,
-                   add_identity, /*flip=*/1, st, d);
+    rc = stride == 1 ? route_forward(dy, w, nullptr, ph, plan_host, plan_dev, dx, N, H, W, C, K, stride, layout,
+                                     dtype, add_identity, /*flip=*/1, st, d)
+                     : kNotTiled;
     if (rc != kNotTiled) return rc;
     return O1D_DISPATCH(launch_generic_dgrad, dy, w, ph, plan_dev, dx, N, H, W, C, K, stride,
                         add_identity, st, d);

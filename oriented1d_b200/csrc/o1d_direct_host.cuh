@@ -1,0 +1,123 @@
+// Host side of the direct kernels: applicability, tile selection, TMA descriptor, launch.
+#pragma once
+
+#include "o1d_direct.cuh"
+#include "o1d_tiled_host.cuh"   // encode_tiled_fn
+
+namespace o1d {
+
+struct DirectConfig {
+    DirectParams p;
+    int smem_bytes, grid, kt;
+    bool whole_image;      // one tile covers a whole image (no halo re-reads)
+};
+
+inline bool direct_configure(const PlanHeader &ph, const void *plan_host, int N, int H, int W, int C, int K,
+                             int stride, int layout, int esize, int smem_limit, int sms, DirectConfig *out) {
+    if (layout != O1D_NHWC || K > kMaxTaps || stride < 1 || stride > 4) return false;
+    const int CCs = 32 / esize;
+    if (C % CCs != 0) return false;
+    DirectParams p{};
+    p.N = N; p.H = H; p.W = W; p.C = C; p.K = K; p.stride = stride;
+    p.P = ceil_div(H, stride); p.Q = ceil_div(W, stride);
+    p.CCs = CCs; p.nchunks = C / CCs;
+    p.hh = ph.max_dh < H - 1 ? ph.max_dh : H - 1;
+    p.hw = ph.max_dw < W - 1 ? ph.max_dw : W - 1;
+    // longest tap list after dropping taps that cannot reach the image
+    PlanView pv = plan_view(plan_host, ph);
+    int longest = 0;
+    for (int i = 0; i < ph.ncls; i++) {
+        int n = 0;
+        for (int k = 0; k < K; k++) {
+            const int dh = pv.taps[((size_t)i * K + k) * 2], dw = pv.taps[((size_t)i * K + k) * 2 + 1];
+            if ((dh < 0 ? -dh : dh) <= p.hh && (dw < 0 ? -dw : dw) <= p.hw) n++;
+        }
+        if (n > longest) longest = n;
+    }
+    const int kt = longest <= 15 ? 15 : longest <= 23 ? 23 : 31;
+    auto tile_bytes = [&](int th, int tq, int ni) {
+        return (long long)((th - 1) * stride + 1 + 2 * p.hh) * ((tq - 1) * stride + 1 + 2 * p.hw) * CCs * esize * ni;
+    };
+    const long long kSmall = 40 * 1024, kLarge = 100 * 1024;
+    int Th = p.P, Tq = p.Q, NI = 1;
+    bool whole = true;
+    if ((Tq - 1) * stride + 1 + 2 * p.hw > 256 || (Th - 1) * stride + 1 + 2 * p.hh > 256 || tile_bytes(Th, Tq, 1) > kLarge) {
+        whole = false;
+        while ((Tq - 1) * stride + 1 + 2 * p.hw > 256) Tq = (Tq + 1) / 2;
+        // rows: as many as fit the large budget (at least as many output rows as halo rows,
+        // so that re-read rows stay below ~2x)
+        while (Th > 1 && ((Th - 1) * stride + 1 + 2 * p.hh > 256 || tile_bytes(Th, Tq, 1) > kLarge)) Th = (Th + 1) / 2;
+        if (tile_bytes(Th, Tq, 1) > kLarge) {          // still too wide: split columns further
+            while (Tq > 8 && tile_bytes(Th, Tq, 1) > kLarge) Tq = (Tq + 1) / 2;
+            if (tile_bytes(Th, Tq, 1) > kLarge) return false;
+        }
+    } else {
+        const long long one = tile_bytes(Th, Tq, 1);
+        NI = (int)(kSmall / one);
+        if (NI < 1) NI = 1;
+        if (NI > 16) NI = 16;
+        if (NI > N) NI = N;
+    }
+    p.Th = Th; p.Tq = Tq; p.NI = NI;
+    p.THp = (Th - 1) * stride + 1 + 2 * p.hh;
+    p.TWp = (Tq - 1) * stride + 1 + 2 * p.hw;
+    p.tiles_p = ceil_div(p.P, Th); p.tiles_q = ceil_div(p.Q, Tq); p.tiles_n = ceil_div(N, NI);
+    p.tiles_per_chunk = p.tiles_p * p.tiles_q * p.tiles_n;
+    p.tile_bytes = (int)tile_bytes(Th, Tq, NI);
+    p.tile_stride = (p.tile_bytes + 127) & ~127;
+    p.off_taps_bytes = 2 * p.tile_stride;
+    p.off_bar_bytes = p.off_taps_bytes + CCs * kt * 8;
+    const int smem = p.off_bar_bytes + 16;
+    if (smem > smem_limit) return false;
+    int ctas = (228 * 1024) / (smem + 1024);
+    if (ctas > 2) ctas = 2;
+    if (ctas < 1) ctas = 1;
+    int groups = (sms * ctas) / p.nchunks;
+    if (groups < 1) groups = 1;
+    if (groups > p.tiles_per_chunk) groups = p.tiles_per_chunk;
+    p.div_tq = FastDiv::make(Tq); p.div_thtq = FastDiv::make(Th * Tq);
+    p.div_tiles_q = FastDiv::make(p.tiles_q); p.div_tiles_pq = FastDiv::make(p.tiles_p * p.tiles_q);
+    out->p = p;
+    out->smem_bytes = smem;
+    out->grid = groups * p.nchunks;
+    out->kt = kt;
+    out->whole_image = whole;
+    return true;
+}
+
+// 4-D tensor map over an NHWC tensor with a box CCs x TWp x THp x NI.
+inline bool make_direct_tensor_map(CUtensorMap *map, const void *base, int N, int H, int W, int C, int esize,
+                                   const DirectParams &p) {
+    PFN_encodeTiled enc = encode_tiled_fn();
+    if (!enc || ((uintptr_t)base & 15) || (C * esize) % 16 != 0) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)W * C * esize, (cuuint64_t)H * W * C * esize};
+    cuuint32_t box[4] = {(cuuint32_t)p.CCs, (cuuint32_t)p.TWp, (cuuint32_t)p.THp, (cuuint32_t)p.NI};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+               const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int KT>
+cudaError_t launch_direct_one(const DirectConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
+                              const PlanView &pv, void *y, cudaStream_t st) {
+    auto kern = direct_fprop_nhwc_kernel<T, KT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
+    if (e != cudaSuccess) return e;
+    kern<<<cfg.grid, kDirectThreads, cfg.smem_bytes, st>>>(map, w, bias, pv.cls, pv.taps, (T *)y, cfg.p);
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_direct(const DirectConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
+                          const PlanView &pv, void *y, cudaStream_t st) {
+    switch (cfg.kt) {
+        case 15: return launch_direct_one<T, 15>(cfg, map, w, bias, pv, y, st);
+        case 23: return launch_direct_one<T, 23>(cfg, map, w, bias, pv, y, st);
+        default: return launch_direct_one<T, 31>(cfg, map, w, bias, pv, y, st);
+    }
+}
+
+}  // namespace o1d

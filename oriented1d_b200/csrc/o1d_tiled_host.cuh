@@ -142,7 +142,7 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             // Rank: lanes doing useful work per SM, with a bonus when two or more CTAs share an
             // SM (their load / restage / compute / store phases overlap); then larger tiles.
             const double util = active / NT;
-            const double score = util * (double)(ctas * NT) / kTiledThreads * (ctas >= 2 ? 1.25 : 1.0);
+            const double score = util * (double)(ctas * NT) / kTiledThreads * (ctas >= 4 ? 1.4 : ctas >= 2 ? 1.25 : 1.0);
             const bool better = !found || score > best.score + 1e-9 ||
                                 (score > best.score - 1e-9 && BR * CC > best.p.BR * best.p.CC);
             if (!better) continue;

@@ -182,10 +182,10 @@ def uses_tiled(plan: Plan, N: int, H: int, W: int, stride: int, nhwc: bool, dtyp
     return bool(lib.o1d_uses_tiled(plan.host.data_ptr(), N, H, W, plan.C, plan.K, stride, int(nhwc), code))
 
 
-def set_route(general_only: bool) -> None:
-    """Testing aid: True routes every call to the general kernels, False restores the
-    automatic choice (tiled kernels where they apply)."""
-    check(lib.o1d_set_route(1 if general_only else 0), "o1d_set_route")
+def set_route(route) -> None:
+    """Testing aid.  False/0: automatic choice; True/1: general kernels only; 2: prefer the
+    tiled kernels; 3: prefer the direct kernels."""
+    check(lib.o1d_set_route(int(route)), "o1d_set_route")
 
 
 def device_status(device=None) -> int:

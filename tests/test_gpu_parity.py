@@ -288,8 +288,20 @@ def test_tiled_route_equals_general_route(hw, C, mode, dtype):
         dw_ref, db_ref = o1d.wgrad(dy, x, plan, 1, True, True)
     finally:
         o1d.ops.set_route(False)
-    y = o1d.fprop(x, w, bias, plan, 1, True, True).float()
-    dx = o1d.dgrad(x, w, plan, hw, hw, 1, True, False).float()
+    for route in (2, 3, 0):          # tiled preferred, direct preferred, automatic
+        try:
+            o1d.ops.set_route(route)
+            y = o1d.fprop(x, w, bias, plan, 1, True, True).float()
+            dx = o1d.dgrad(x, w, plan, hw, hw, 1, True, False).float()
+        finally:
+            o1d.ops.set_route(0)
+        assert o1d.ops.device_status() == 0
+        if dtype == torch.float32:
+            assert float((y - y_ref).abs().max()) <= 1e-5 * float(y_ref.abs().max()), route
+            assert float((dx - dx_ref).abs().max()) <= 1e-5 * float(dx_ref.abs().max()), route
+        else:
+            assert float(((y - y_ref).abs() / y_ref.abs().clamp_min(1e-2)).max()) <= 2 ** -7, route
+            assert float(((dx - dx_ref).abs() / dx_ref.abs().clamp_min(1e-2)).max()) <= 2 ** -7, route
     dw, db = o1d.wgrad(dy, x, plan, 1, True, True)
     dw2, db2 = o1d.wgrad(dy, x, plan, 1, True, True)
     assert o1d.ops.device_status() == 0
