@@ -595,7 +595,12 @@ def main():
     ap.add_argument("--batch", type=int, default=64, help="batch for --case")
     ap.add_argument("--reps", type=int, default=3, help="launches for --case")
     ap.add_argument("--angles", default="rr", choices=["rr", "block"], help="channel->orientation map for --case")
+    ap.add_argument("--route", type=int, default=0, choices=[0, 1, 2, 3],
+                    help="kernel family: 0 automatic (default), 1 general only, 2 prefer tiled, 3 prefer direct")
     args = ap.parse_args()
+    if args.route and args.impl == "ours":
+        from oriented1d_b200 import ops
+        ops.set_route(args.route)
     if args.case:
         run_case(args)
     elif args.workload == "model":

@@ -196,6 +196,9 @@ int try_direct(const void *x, const float *w, const float *bias, const PlanHeade
     if (!direct_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, &cfg))
         return kNotTiled;
     if (whole_image_only && !cfg.whole_image) return kNotTiled;
+    // 2-byte elements pay a conversion per load here; measured against the tiled kernels the
+    // direct ones only win while several images share a tile (7x7 yes, 14x14 no)
+    if (whole_image_only && esize == 2 && cfg.p.NI < 2) return kNotTiled;
     if (((uintptr_t)y & 3) != 0) return kNotTiled;
     CUtensorMap map;
     if (!make_direct_tensor_map(&map, x, N, H, W, C, esize, cfg.p)) return kNotTiled;

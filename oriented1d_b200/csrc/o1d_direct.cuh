@@ -38,15 +38,29 @@ struct DirectParams {
     int tile_bytes, tile_stride;  // bytes of one box / spacing of the two buffers
     int off_taps_bytes, off_bar_bytes;
     int flip, add_identity;
-    FastDiv div_tq, div_thtq, div_tiles_q, div_tiles_pq;
+    int segs_q;                   // column segments (of PLW*NPX pixels) per tile row
+    FastDiv div_sq, div_thsq, div_tiles_q, div_tiles_pq;
 };
 
-template <typename T> __device__ __forceinline__ float ld_smem(const T *p);
-template <> __device__ __forceinline__ float ld_smem<float>(const float *p) { return *p; }
-template <> __device__ __forceinline__ float ld_smem<__nv_bfloat16>(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+// Load one element from a 32-bit shared-memory address (no generic-pointer arithmetic).
+template <typename T> __device__ __forceinline__ float ld_smem(uint32_t addr);
+template <> __device__ __forceinline__ float ld_smem<float>(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+template <> __device__ __forceinline__ float ld_smem<__nv_bfloat16>(uint32_t addr) {
+    unsigned short h;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
+    return __uint_as_float((uint32_t)h << 16);
+}
 
-// KT: taps kept in registers per thread (>= the longest clipped tap list of any channel)
-template <typename T, int KT>
+// KT: taps kept in registers per thread (>= the longest clipped tap list of any channel).
+// NPX: outputs per thread and unit.  A warp works on one row segment of PLW*NPX pixels
+// (PLW = 32/CCs pixel lanes); a thread's NPX pixels are PLW apart, so their tile addresses
+// differ by the compile-time constant 32*sizeof(T)*STRIDE bytes and share one address add per
+// tap, while the lanes of every single load still cover 32 different banks.
+template <typename T, int KT, int NPX, int STRIDE>
 __global__ void __launch_bounds__(kDirectThreads, 2)
 direct_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restrict__ wgt,
                          const float *__restrict__ bias, const uint16_t *__restrict__ cls,
@@ -59,9 +73,11 @@ direct_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *
 
     const int tid = threadIdx.x;
     const int CCs = p.CCs;
-    const int cl = tid % CCs;                 // channel within the chunk
-    const int pl = tid / CCs;                 // pixel lane
-    const int PL = kDirectThreads / CCs;      // pixels per pass
+    const int lane = tid & 31, warp = tid >> 5;
+    const int cl = lane % CCs;                // channel within the chunk
+    const int pl = lane / CCs;                // pixel lane within the warp
+    const int PLW = 32 / CCs;                 // pixel lanes per warp
+    constexpr int DELTA = 32 * (int)sizeof(T) * STRIDE;   // bytes between a thread's pixels
     const int groups = gridDim.x / p.nchunks; // CTAs per chunk
     const int chunk = blockIdx.x % p.nchunks;
     const int first = blockIdx.x / p.nchunks;
@@ -87,7 +103,8 @@ direct_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *
             const int kk = p.flip ? p.K - 1 - k : k;         // input gradient: mirrored line
             float wv = __ldg(wgt + (size_t)c * p.K + kk);
             if (p.add_identity && kk == pad) wv += 1.f;
-            if (n < KT) { s_w[tid * KT + n] = wv; s_off[tid * KT + n] = (dh * p.TWp + dw) * CCs; n++; }
+            // tile offsets are kept in BYTES so that a tap is one 32-bit add + one LDS
+            if (n < KT) { s_w[tid * KT + n] = wv; s_off[tid * KT + n] = (dh * p.TWp + dw) * CCs * (int)sizeof(T); n++; }
         }
         for (; n < KT; n++) { s_w[tid * KT + n] = 0.f; s_off[tid * KT + n] = 0; }
     }
@@ -117,7 +134,7 @@ direct_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *
         if (my_tiles > 1) issue(1);
     }
 
-    const int tile_pixels = p.Th * p.Tq;
+    const int units = p.NI * p.Th * p.segs_q;           // (image, row, column segment)
     const int img_elems = p.THp * p.TWp * CCs;
     bool failed = false;
     for (int it = 0; it < my_tiles; it++) {
@@ -125,17 +142,29 @@ direct_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *
         tile_coords(it, n0, p0, q0);
         const int b = it & 1;
         if (!failed && !mbar_wait(&full[b], (it >> 1) & 1)) failed = true;
-        const T *tile = reinterpret_cast<const T *>(smem_raw + (size_t)b * p.tile_stride);
-        for (int e = pl; e < p.NI * tile_pixels; e += PL) {
-            const int img = p.div_thtq.div(e), pix = e - img * tile_pixels;
-            const int pr = p.div_tq.div(pix), pc = pix - pr * p.Tq;
-            const int n = n0 + img, pp = p0 + pr, qq = q0 + pc;
-            if (n >= p.N || pp >= p.P || qq >= p.Q) continue;
-            const T *base = tile + img * img_elems + ((pr * p.stride + p.hh) * p.TWp + pc * p.stride + p.hw) * CCs + cl;
-            float acc = bv;
+        const uint32_t tile_b = smem_u32(smem_raw) + b * p.tile_stride;   // shared address of the buffer
+        for (int u = warp; u < units; u += kDirectThreads / 32) {
+            const int img = p.div_thsq.div(u), r = u - img * (p.Th * p.segs_q);
+            const int pr = p.div_sq.div(r), sq = r - pr * p.segs_q;
+            const int pc0 = sq * (PLW * NPX) + pl;
+            const int n = n0 + img, pp = p0 + pr;
+            if (n >= p.N || pp >= p.P) continue;
+            const uint32_t base = tile_b + (img * img_elems + ((pr * STRIDE + p.hh) * p.TWp + pc0 * STRIDE + p.hw) * CCs + cl) * (int)sizeof(T);
+            float acc[NPX];
 #pragma unroll
-            for (int k = 0; k < KT; k++) acc = fmaf(w[k], ld_smem<T>(base + off[k]), acc);
-            st(y + (((size_t)n * p.P + pp) * p.Q + qq) * p.C + c0 + cl, acc);
+            for (int j = 0; j < NPX; j++) acc[j] = bv;
+#pragma unroll
+            for (int k = 0; k < KT; k++) {
+                const uint32_t a = base + off[k];
+#pragma unroll
+                for (int j = 0; j < NPX; j++) acc[j] = fmaf(w[k], ld_smem<T>(a + j * DELTA), acc[j]);
+            }
+            T *yrow = y + (((size_t)n * p.P + pp) * p.Q + q0) * p.C + c0 + cl;
+#pragma unroll
+            for (int j = 0; j < NPX; j++) {
+                const int pc = pc0 + PLW * j;
+                if (pc < p.Tq && q0 + pc < p.Q) st(yrow + (size_t)pc * p.C, acc[j]);
+            }
         }
         __syncthreads();                                   // everyone is done with buffer b
         if (tid == 0 && it + 2 < my_tiles) issue(it + 2);

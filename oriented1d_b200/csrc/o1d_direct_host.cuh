@@ -8,13 +8,13 @@ namespace o1d {
 
 struct DirectConfig {
     DirectParams p;
-    int smem_bytes, grid, kt;
+    int smem_bytes, grid, kt, npx;
     bool whole_image;      // one tile covers a whole image (no halo re-reads)
 };
 
 inline bool direct_configure(const PlanHeader &ph, const void *plan_host, int N, int H, int W, int C, int K,
                              int stride, int layout, int esize, int smem_limit, int sms, DirectConfig *out) {
-    if (layout != O1D_NHWC || K > kMaxTaps || stride < 1 || stride > 4) return false;
+    if (layout != O1D_NHWC || K > kMaxTaps || (stride != 1 && stride != 2)) return false;
     const int CCs = 32 / esize;
     if (C % CCs != 0) return false;
     DirectParams p{};
@@ -52,19 +52,22 @@ inline bool direct_configure(const PlanHeader &ph, const void *plan_host, int N,
             if (tile_bytes(Th, Tq, 1) > kLarge) return false;
         }
     } else {
-        const long long one = tile_bytes(Th, Tq, 1);
-        NI = (int)(kSmall / one);
-        if (NI < 1) NI = 1;
-        if (NI > 16) NI = 16;
-        if (NI > N) NI = N;
+        NI = (int)(kSmall / tile_bytes(Th, Tq, 1));
     }
+    if (NI < 1) NI = 1;
+    if (NI > 16) NI = 16;
+    if (NI > N) NI = N;
     p.Th = Th; p.Tq = Tq; p.NI = NI;
     p.THp = (Th - 1) * stride + 1 + 2 * p.hh;
     p.TWp = (Tq - 1) * stride + 1 + 2 * p.hw;
     p.tiles_p = ceil_div(p.P, Th); p.tiles_q = ceil_div(p.Q, Tq); p.tiles_n = ceil_div(N, NI);
     p.tiles_per_chunk = p.tiles_p * p.tiles_q * p.tiles_n;
-    p.tile_bytes = (int)tile_bytes(Th, Tq, NI);
-    p.tile_stride = (p.tile_bytes + 127) & ~127;
+    p.tile_bytes = p.THp * p.TWp * CCs * esize * NI;
+    // slack after each buffer: the last row segment of a tile may read up to 16 pixels past it
+    p.tile_stride = ((p.tile_bytes + 127) & ~127) + 16 * stride * CCs * esize;
+    const int plw = 32 / CCs;
+    const int npx = (Tq >= 3 * plw) ? 4 : (Tq > plw ? 2 : 1);
+    p.segs_q = ceil_div(Tq, plw * npx);
     p.off_taps_bytes = 2 * p.tile_stride;
     p.off_bar_bytes = p.off_taps_bytes + CCs * kt * 8;
     const int smem = p.off_bar_bytes + 16;
@@ -75,12 +78,13 @@ inline bool direct_configure(const PlanHeader &ph, const void *plan_host, int N,
     int groups = (sms * ctas) / p.nchunks;
     if (groups < 1) groups = 1;
     if (groups > p.tiles_per_chunk) groups = p.tiles_per_chunk;
-    p.div_tq = FastDiv::make(Tq); p.div_thtq = FastDiv::make(Th * Tq);
+    p.div_sq = FastDiv::make(p.segs_q); p.div_thsq = FastDiv::make(Th * p.segs_q);
     p.div_tiles_q = FastDiv::make(p.tiles_q); p.div_tiles_pq = FastDiv::make(p.tiles_p * p.tiles_q);
     out->p = p;
     out->smem_bytes = smem;
     out->grid = groups * p.nchunks;
     out->kt = kt;
+    out->npx = npx;
     out->whole_image = whole;
     return true;
 }
@@ -100,24 +104,41 @@ inline bool make_direct_tensor_map(CUtensorMap *map, const void *base, int N, in
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename T, int KT>
+template <typename T, int KT, int NPX, int STRIDE>
 cudaError_t launch_direct_one(const DirectConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
                               const PlanView &pv, void *y, cudaStream_t st) {
-    auto kern = direct_fprop_nhwc_kernel<T, KT>;
+    auto kern = direct_fprop_nhwc_kernel<T, KT, NPX, STRIDE>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
     if (e != cudaSuccess) return e;
     kern<<<cfg.grid, kDirectThreads, cfg.smem_bytes, st>>>(map, w, bias, pv.cls, pv.taps, (T *)y, cfg.p);
     return cudaGetLastError();
 }
 
+template <typename T, int KT, int STRIDE>
+cudaError_t launch_direct_npx(const DirectConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
+                              const PlanView &pv, void *y, cudaStream_t st) {
+    switch (cfg.npx) {
+        case 4: return launch_direct_one<T, KT, 4, STRIDE>(cfg, map, w, bias, pv, y, st);
+        case 2: return launch_direct_one<T, KT, 2, STRIDE>(cfg, map, w, bias, pv, y, st);
+        default: return launch_direct_one<T, KT, 1, STRIDE>(cfg, map, w, bias, pv, y, st);
+    }
+}
+
+template <typename T, int STRIDE>
+cudaError_t launch_direct_kt(const DirectConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
+                             const PlanView &pv, void *y, cudaStream_t st) {
+    switch (cfg.kt) {
+        case 15: return launch_direct_npx<T, 15, STRIDE>(cfg, map, w, bias, pv, y, st);
+        case 23: return launch_direct_npx<T, 23, STRIDE>(cfg, map, w, bias, pv, y, st);
+        default: return launch_direct_npx<T, 31, STRIDE>(cfg, map, w, bias, pv, y, st);
+    }
+}
+
 template <typename T>
 cudaError_t launch_direct(const DirectConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
                           const PlanView &pv, void *y, cudaStream_t st) {
-    switch (cfg.kt) {
-        case 15: return launch_direct_one<T, 15>(cfg, map, w, bias, pv, y, st);
-        case 23: return launch_direct_one<T, 23>(cfg, map, w, bias, pv, y, st);
-        default: return launch_direct_one<T, 31>(cfg, map, w, bias, pv, y, st);
-    }
+    return cfg.p.stride == 1 ? launch_direct_kt<T, 1>(cfg, map, w, bias, pv, y, st)
+                             : launch_direct_kt<T, 2>(cfg, map, w, bias, pv, y, st);
 }
 
 }  // namespace o1d
