@@ -42,17 +42,18 @@ struct DirectParams {
     FastDiv div_sq, div_thsq, div_tiles_q, div_tiles_pq;
 };
 
-// Load one element from a 32-bit shared-memory address (no generic-pointer arithmetic).
-template <typename T> __device__ __forceinline__ float ld_smem(uint32_t addr);
-template <> __device__ __forceinline__ float ld_smem<float>(uint32_t addr) {
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
-    return v;
-}
-template <> __device__ __forceinline__ float ld_smem<__nv_bfloat16>(uint32_t addr) {
-    unsigned short h;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
-    return __uint_as_float((uint32_t)h << 16);
+// Load one element from a 32-bit shared-memory address plus a compile-time byte offset (the
+// offset is an immediate of the load, so a thread's NPX pixels share one address register).
+template <typename T, int IMM> __device__ __forceinline__ float ld_smem(uint32_t addr) {
+    if constexpr (sizeof(T) == 4) {
+        float v;
+        asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(IMM));
+        return v;
+    } else {
+        unsigned short h;
+        asm volatile("ld.shared.u16 %0, [%1+%2];" : "=h"(h) : "r"(addr), "n"(IMM));
+        return __uint_as_float((uint32_t)h << 16);
+    }
 }
 
 // KT: taps kept in registers per thread (>= the longest clipped tap list of any channel).
@@ -156,8 +157,7 @@ direct_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *
 #pragma unroll
             for (int k = 0; k < KT; k++) {
                 const uint32_t a = base + off[k];
-#pragma unroll
-                for (int j = 0; j < NPX; j++) acc[j] = fmaf(w[k], ld_smem<T>(a + j * DELTA), acc[j]);
+                static_for<0, NPX>([&](auto j) { acc[j] = fmaf(w[k], ld_smem<T, j * DELTA>(a), acc[j]); });
             }
             T *yrow = y + (((size_t)n * p.P + pp) * p.Q + q0) * p.C + c0 + cl;
 #pragma unroll
