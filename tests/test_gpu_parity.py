@@ -357,6 +357,57 @@ def test_nchw_module_takes_the_tiled_route(oracle):
     assert rel_err(m.bias.grad.cpu().numpy(), rdb) <= TOL_WGRAD
 
 
+DENSE = [
+    # C, H, W, K, stride: the dense-prediction backbone at 800x1280 input — stage maps with the
+    # kernel lengths that backbone crops to (semantic_segmentation/backbone/convnext.py:316-327)
+    # and the second stem convolution (400x640 -> 200x320)
+    (96, 200, 320, 31, 1),
+    (192, 100, 160, 31, 1),
+    (384, 50, 80, 27, 1),
+    (768, 25, 40, 13, 1),
+    (64, 400, 640, 31, 2),
+]
+
+
+@pytest.mark.parametrize("shape", DENSE, ids=lambda s: "x".join(map(str, s)))
+def test_dense_prediction_shapes(oracle, shape):
+    """Large-spatial / small-batch maps (row/column tiles with line halos), forward, input and
+    weight gradients against the oracle, NHWC, through the module's arbitrary-size entry."""
+    C, H, W, K, s = shape
+    x, w, dy = make_inputs(H + W, 1, C, H, W, K, stride=s)
+    th = angle_list("model+", C)
+    m = o1d.DepthwiseOrientedConv1d(C, C, K, groups=C, stride=s, padding=K // 2, nhwc=True, bias=False,
+                                    angle=[float(a) for a in th], arbitrary_size=True).to(DEV)
+    with torch.no_grad():
+        m.weight.copy_(torch.from_numpy(w))
+    xd = _to_dev(x, True).requires_grad_(True)
+    y = m(xd)
+    y.backward(_to_dev(dy, True))
+    assert o1d.ops.device_status() == 0
+    assert rel_err(_to_nchw(y.detach(), True), oracle.fprop(x, w, th, s)) <= TOL_FPROP
+    assert rel_err(_to_nchw(xd.grad, True), oracle.dgrad(dy, w, th, s)) <= TOL_DGRAD
+    assert rel_err(m.weight.grad.cpu().numpy(), oracle.wgrad_f64(dy, x, th, K, s)) <= TOL_WGRAD
+
+
+def test_first_stem_conv_at_detection_size():
+    """800x1280x64, K=31, stride 2 (models/convnext.py:158-160 at the detection input size): the
+    automatic route against the general kernels on the same device inputs."""
+    C, H, W, K, s = 64, 800, 1280, 31, 2
+    g = torch.Generator(device="cpu").manual_seed(5)
+    x = torch.randn((1, H, W, C), generator=g).to(DEV)
+    w = (0.02 * torch.randn((C, 1, 1, K), generator=g)).to(DEV)
+    plan = o1d.Plan(angle_list("model", C), K)
+    y = o1d.fprop(x, w, None, plan, s, True)
+    try:
+        o1d.ops.set_route(1)
+        y_ref = o1d.fprop(x, w, None, plan, s, True)
+    finally:
+        o1d.ops.set_route(0)
+    assert o1d.ops.device_status() == 0
+    assert y.shape == (1, H // 2, W // 2, C)
+    assert float((y - y_ref).abs().max()) <= 1e-5 * float(y_ref.abs().max())
+
+
 @pytest.mark.skipif(not O.ReferenceGPU.available(), reason="reference CUDA kernels not built (oracle/build.py --gpu-reference)")
 @pytest.mark.parametrize("hw,C", [(56, 16), (28, 16), (14, 24), (7, 32)])
 def test_reference_cuda_kernels_agree_with_the_cpu_loops(oracle, hw, C):
