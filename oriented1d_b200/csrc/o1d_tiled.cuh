@@ -40,6 +40,7 @@ constexpr int kTiledThreads = 512;
 constexpr int kMaxStages = 8;
 constexpr int kMaxCC = 64;
 constexpr int kZeroFloats = 64;              // block of zeros a missing line is redirected to
+constexpr int kHaloLines = 10;               // zero lines around a plane that make every line exist (largest |dl|)
 constexpr uint32_t kSpinLimit = 1u << 22;    // mbarrier polls before giving up
 constexpr int kPartialStride = 32;           // floats per channel in a weight-gradient partial:
                                              // 31 stored taps + the bias-gradient sum
@@ -61,6 +62,9 @@ struct TiledParams {
     int R, BR, NB, NSTG;
     int pitch_n, pitch_t;         // line pitch of non-transposed / transposed planes (floats)
     int plane_stride;             // floats between channel planes
+    int plane_base;               // index of (line 0, position 0) of channel 0's plane
+    int halo;                     // zero lines before the first and after every plane (0: lines are bounds-checked)
+    int grp;                      // restage: bands copied between CTA barriers (stages handed back together)
     int out_pitch_n, out_pitch_t, out_plane_stride;
     int nseg_line, nseg_diag;     // segments per channel per band
     int flip, add_identity;
@@ -273,6 +277,10 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
     int *err_s = misc + 3;
 
     constexpr int VE = Vec16<T>::N;
+    // Segments of 7 (maps of 7..49 pixels, where shared memory has room): every plane is
+    // surrounded by zero lines, so no line is ever missing and the checked paths are not
+    // instantiated.  Segments of 8 (56x56 fills shared memory): lines are bounds-checked.
+    constexpr bool HALO = (R == 7);
     const int tid = threadIdx.x, nt = blockDim.x;
     // hot parameters in registers
     const int CC = p.CC, GV = CC / VE, W = p.W, H = p.H, BR = p.BR, NB = p.NB, NSTG = p.NSTG;
@@ -418,7 +426,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
             for (int i = tid; i < CC; i += nt) {
                 const int o = chan[c0 + i];
                 const int mode = canon_mode(o);
-                const int pbase = p.off_planar + 32 + i * p.plane_stride;
+                const int pbase = p.plane_base + i * p.plane_stride;
                 const int obase = i * p.out_plane_stride;
                 int4 mi, mo;   // storage index = x*h + y*w + z
                 if (mode & MODE_T) {
@@ -452,7 +460,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
             }
         }
         if (p.rezero) {
-            for (int i = tid; i < CC * p.plane_stride; i += nt) sm[p.off_planar + 32 + i] = 0.f;
+            for (int i = tid; i < p.off_zero - 32; i += nt) sm[p.off_planar + 32 + i] = 0.f;
         }
         if (new_chunk || p.rezero) __syncthreads();
 
@@ -481,7 +489,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
             // geometry of the segment, hoisted out of the band loop
             const int mode = map_in[ch].w;
             const bool transposed = (mode & MODE_T) != 0, fp = (mode & MODE_FP) != 0;
-            const int pbase = p.off_planar + 32 + ch * p.plane_stride;
+            const int pbase = p.plane_base + ch * p.plane_stride;
             const int obase = ch * p.out_plane_stride;
             if (kind == KIND_DIAG) {
                 const int wd = W + R - 1;
@@ -522,6 +530,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 dwrap[j] = m.x - m.y * W;
                 dband[j] = m.x * BR;
             }
+            int pending = 0;
             for (int b = 0; b < NB; b++) {
                 if (*err_s == 0 && !mbar_wait(&full[stage], parity)) *err_s = 1;
                 const uint4 *stg = reinterpret_cast<const uint4 *>(smem_raw + p.off_stage_bytes + (size_t)stage * p.stage_stride);
@@ -542,18 +551,30 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 }
 #pragma unroll
                 for (int j = 0; j < VE; j++) ia[j] += dband[j];
-                __syncthreads();
-                if (tid == 0 && gb + NSTG < total_bands) issue(gb + NSTG);
                 gb++;
                 if (++stage == NSTG) { stage = 0; parity ^= 1; }
+                // A stage may be refilled once every thread has read it: one CTA barrier per
+                // group of bands (and after the last band, before the planes are read).
+                if (++pending == p.grp || b + 1 == NB) {
+                    __syncthreads();
+                    if (tid == 0)
+                        for (int g = gb - pending; g < gb; g++)
+                            if (g + NSTG < total_bands) issue(g + NSTG);
+                    pending = 0;
+                }
             }
         }
 
         // ---- compute -----------------------------------------------------------------
         float w[kMaxTaps];
         if (OP == OP_FPROP) {
+            const float4 *wp = reinterpret_cast<const float4 *>(wts + ch * 32);
 #pragma unroll
-            for (int k = 0; k < kMaxTaps; k++) w[k] = wts[ch * 32 + k];
+            for (int q = 0; q < 8; q++) {
+                const float4 v = wp[q];
+                w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z;
+                if (4 * q + 3 < kMaxTaps) w[4 * q + 3] = v.w;
+            }
             if (kind == KIND_AXIS) merge_weights<KIND_AXIS, JH>(w);
             else if (kind == KIND_SLANT) merge_weights<KIND_SLANT, JH>(w);
             else if (kind == KIND_DIAG) merge_weights<KIND_DIAG, JH>(w);
@@ -636,7 +657,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 constexpr int TLO = PD::p.row_lo[0], THI = PD::p.row_hi[0] + R - 1;   // t range read
                 lane_inside = line - THI >= 0 && line - TLO < nlines;
             }
-            const bool inside = __all_sync(0xffffffffu, lane_inside);
+            const bool inside = HALO || __all_sync(0xffffffffu, lane_inside);
             if (kind == KIND_AXIS) {
                 // a single line row (d = 0) and the segment's own line always exists: no checks
                 if constexpr (OP == OP_FPROP) {

@@ -81,7 +81,11 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
     const KindComp *comps = reinterpret_cast<const KindComp *>(static_cast<const char *>(plan_host) + ph.comps_off);
     const int G = (R == 8) ? 17 : 16;
     const int pitch_n = make_odd(W + G), pitch_t = make_odd(H + G);
-    const int PLS0 = (H * pitch_n > W * pitch_t) ? H * pitch_n : W * pitch_t;
+    // R == 7 kernels surround every plane with kHaloLines zero lines (shared between neighbouring
+    // planes) instead of bounds-checking lines; see tiled_nhwc_kernel.
+    const int halo = (R == 7) ? kHaloLines : 0;
+    const int halo_floats = halo * (pitch_n > pitch_t ? pitch_n : pitch_t);
+    const int PLS0 = ((H * pitch_n > W * pitch_t) ? H * pitch_n : W * pitch_t) + halo_floats;
 
     bool found = false;
     TiledConfig best{};
@@ -113,11 +117,13 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             if (op == OP_WGRAD && (2 * CC * OPS) / NT < 1) continue;
             TiledParams p{};
             p.off_planar = 0;
-            const int planar_floats = 32 + CC * PLS;
+            const int planar_floats = (32 + halo_floats + CC * PLS + 3) & ~3;
+            p.plane_base = 32 + halo_floats;
+            p.halo = halo;
             p.off_zero = planar_floats;
             p.zero_floats_total = planar_floats + kZeroFloats;
             p.off_out = p.zero_floats_total;
-            p.off_wts = p.off_out + 2 * CC * OPS;
+            p.off_wts = (p.off_out + 2 * CC * OPS + 3) & ~3;     // read as float4
             p.off_misc = p.off_wts + CC * 32;
             const int misc_ints = 4 + kMaxCC + 2 * kMaxCC * 4 + kMaxCC + 2 * kMaxCC;
             int bytes = (p.off_misc + misc_ints) * 4;
@@ -149,6 +155,9 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             p.N = N; p.H = H; p.W = W; p.C = C; p.K = K;
             p.CC = CC; p.nchunks = C / CC; p.total_items = N * p.nchunks;
             p.R = R; p.BR = BR; p.NB = NB; p.NSTG = nstg;
+            // grouping shortens the prefetch distance, which costs more than the barriers it saves
+            // when an item has more bands than there are stages
+            p.grp = (NB <= nstg && nstg / 2 > 1) ? nstg / 2 : 1;
             p.pitch_n = pitch_n; p.pitch_t = pitch_t; p.plane_stride = PLS;
             p.out_pitch_n = out_pitch_n; p.out_pitch_t = out_pitch_t; p.out_plane_stride = OPS;
             p.nseg_line = nseg_line; p.nseg_diag = nseg_diag;
