@@ -69,7 +69,7 @@ struct TiledParams {
     int nseg_line, nseg_diag;     // segments per channel per band
     int flip, add_identity;
     int rezero;                   // planes must be cleared per item (H != W)
-    int step_rows, step_cols;     // pixel advance of one thread per loop trip in restage/store
+    int TR;                       // restage/store: rows of a band the movers cover per pass
     int max_visits;               // weight gradient: partial slots per CTA
     int order;                    // 0: image-major items (item = cta + i*grid), 1: chunk-major ranges
     // shared memory layout, in floats from the start of dynamic smem
@@ -331,11 +331,14 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
     if (tid == 0)
         for (int gb = 0; gb < NSTG && gb < total_bands; gb++) issue(gb);
 
-    // fixed per-thread walk over the (pixel, 16-byte vector) pairs of one band
+    // Band <-> NHWC movement (restage, store, dy fetch): thread -> (row, column, 16-byte vector)
+    // of the first TR rows of a band, then the same column TR rows further down: no column
+    // wrap, so every index advances by a per-thread constant.  Threads past TR rows idle here.
     const int g_vec = tid % GV;
     const int pix_first = tid / GV;
-    const int pix_step = nt / GV;
     const int rl_first = p.div_w.div(pix_first), col_first = pix_first - rl_first * W;
+    const bool mover = rl_first < p.TR;
+    const int pix_step = p.TR * W;          // pixels between a thread's passes
     const int band_pixels = BR * W;
     const int band_floats = CC * p.out_plane_stride;
     float *const outb = sm + p.off_out;
@@ -521,13 +524,12 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
 
         // ---- restage: staging bands -> planes -------------------------------------------
         {
-            int ia[VE], dstep[VE], dwrap[VE], dband[VE];
+            int ia[VE], dstep[VE], dband[VE];
 #pragma unroll
             for (int j = 0; j < VE; j++) {
                 const int4 m = map_in[g_vec * VE + j];
                 ia[j] = m.x * rl_first + m.y * col_first + m.z;
-                dstep[j] = m.x * p.step_rows + m.y * p.step_cols;
-                dwrap[j] = m.x - m.y * W;
+                dstep[j] = m.x * p.TR;
                 dband[j] = m.x * BR;
             }
             int pending = 0;
@@ -537,17 +539,11 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 int idx[VE];
 #pragma unroll
                 for (int j = 0; j < VE; j++) idx[j] = ia[j];
-                int col = col_first;
-                for (int pix = pix_first; pix < band_pixels; pix += pix_step) {
+                for (int pix = mover ? pix_first : band_pixels; pix < band_pixels; pix += pix_step) {
                     float f[VE];
                     Vec16<T>::unpack(stg[pix * GV + g_vec], f);
 #pragma unroll
-                    for (int j = 0; j < VE; j++) sm[idx[j]] = f[j];
-                    col += p.step_cols;
-                    const bool wrap = col >= W;
-                    if (wrap) col -= W;
-#pragma unroll
-                    for (int j = 0; j < VE; j++) idx[j] += dstep[j] + (wrap ? dwrap[j] : 0);
+                    for (int j = 0; j < VE; j++) { sm[idx[j]] = f[j]; idx[j] += dstep[j]; }
                 }
 #pragma unroll
                 for (int j = 0; j < VE; j++) ia[j] += dband[j];
@@ -581,14 +577,13 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
         }
 
         // band buffer <-> global: per-thread constants (index walk as in restage)
-        int oa[VE], ostep[VE], owrap[VE];
+        int oa[VE], ostep[VE];
         float bs[VE];
 #pragma unroll
         for (int j = 0; j < VE; j++) {
             const int4 m = map_out[g_vec * VE + j];
             oa[j] = m.x * rl_first + m.y * col_first + m.z;
-            ostep[j] = m.x * p.step_rows + m.y * p.step_cols;
-            owrap[j] = m.x - m.y * W;
+            ostep[j] = m.x * p.TR;
             bs[j] = bias_s[g_vec * VE + j];
         }
         T *gbase = io + ((size_t)n * H * W) * C + c0 + g_vec * VE;
@@ -601,27 +596,22 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
 #pragma unroll
             for (int u = 0; u < kPre; u++) {
                 const int pix = pix_first + u * pix_step;
-                if (pix < band_pixels) pre[u] = __ldg(reinterpret_cast<const uint4 *>(src_band + (size_t)pix * C));
+                if (mover && pix < band_pixels) pre[u] = __ldg(reinterpret_cast<const uint4 *>(src_band + (size_t)pix * C));
             }
         };
         auto dy_commit = [&](const T *src_band, float *dstb) {
             int idx[VE];
 #pragma unroll
             for (int j = 0; j < VE; j++) idx[j] = oa[j];
-            int col = col_first, u = 0;
-            for (int pix = pix_first; pix < band_pixels; pix += pix_step, u++) {
+            int u = 0;
+            for (int pix = mover ? pix_first : band_pixels; pix < band_pixels; pix += pix_step, u++) {
                 uint4 v;
                 if (u < kPre) v = (u == 0) ? pre[0] : pre[kPre - 1];
                 else v = __ldg(reinterpret_cast<const uint4 *>(src_band + (size_t)pix * C));
                 float f[VE];
                 Vec16<T>::unpack(v, f);
 #pragma unroll
-                for (int j = 0; j < VE; j++) dstb[idx[j]] = f[j];
-                col += p.step_cols;
-                const bool wrap = col >= W;
-                if (wrap) col -= W;
-#pragma unroll
-                for (int j = 0; j < VE; j++) idx[j] += ostep[j] + (wrap ? owrap[j] : 0);
+                for (int j = 0; j < VE; j++) { dstb[idx[j]] = f[j]; idx[j] += ostep[j]; }
             }
         };
         if (OP == OP_WGRAD && !have_next_band) {       // first band of the item, not prefetched
@@ -724,17 +714,11 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 int idx[VE];
 #pragma unroll
                 for (int j = 0; j < VE; j++) idx[j] = oa[j];
-                int col = col_first;
-                for (int pix = pix_first; pix < band_pixels; pix += pix_step) {
+                for (int pix = mover ? pix_first : band_pixels; pix < band_pixels; pix += pix_step) {
                     float f[VE];
 #pragma unroll
-                    for (int j = 0; j < VE; j++) f[j] = src[idx[j]] + bs[j];
+                    for (int j = 0; j < VE; j++) { f[j] = src[idx[j]] + bs[j]; idx[j] += ostep[j]; }
                     *reinterpret_cast<uint4 *>(gdst + (size_t)pix * C) = Vec16<T>::pack(f);
-                    col += p.step_cols;
-                    const bool wrap = col >= W;
-                    if (wrap) col -= W;
-#pragma unroll
-                    for (int j = 0; j < VE; j++) idx[j] += ostep[j] + (wrap ? owrap[j] : 0);
                 }
             }
         }

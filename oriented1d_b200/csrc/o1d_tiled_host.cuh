@@ -109,6 +109,12 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
                 active += (double)((a + s) * nseg_line + d * nseg_diag) / comps[ci].n;
             }
             if (worst > NT) continue;
+            // movers: as many whole rows as the CTA has (pixel, vector) threads for, evened out
+            // over the passes a band needs
+            const int tr_max = NT / (CC / VE) / W;
+            if (tr_max < 1) continue;
+            const int passes = (BR + (tr_max < BR ? tr_max : BR) - 1) / (tr_max < BR ? tr_max : BR);
+            const int tr = (BR + passes - 1) / passes;
             const int out_pitch_n = make_odd(W), out_pitch_t = make_odd(BR);
             // Plane strides are padded so that the channel groups a warp touches together in
             // the restage / store loops (VE channels apart) fall into different banks.
@@ -168,8 +174,7 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
             p.div_nseg_line = FastDiv::make(nseg_line); p.div_nseg_diag = FastDiv::make(nseg_diag);
             p.div_br = FastDiv::make(BR); p.div_wline = FastDiv::make(W); p.div_wdiag = FastDiv::make(W + R - 1);
             p.div_chunks = FastDiv::make(p.nchunks); p.div_nb = FastDiv::make(NB); p.div_n = FastDiv::make(N);
-            const int pix_step = NT / (CC / VE);
-            p.step_rows = pix_step / W; p.step_cols = pix_step % W;
+            p.TR = tr;
             best.p = p;
             best.smem_bytes = p.off_bar_bytes + 8 * kMaxStages;
             best.stage_stride = stage_stride;
