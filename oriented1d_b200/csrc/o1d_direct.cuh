@@ -35,7 +35,8 @@ struct DirectParams {
     int THp, TWp;                 // input tile extents incl. halo
     int hh, hw;                   // halo rows / columns on each side
     int tiles_p, tiles_q, tiles_n, tiles_per_chunk;
-    int tile_bytes, tile_stride;  // bytes of one box / spacing of the two buffers
+    int tile_bytes, tile_stride;  // bytes of one input box / of the buffer part that holds it
+    int dy_bytes, buf_stride;     // weight gradient: bytes of one dy box; spacing of the two buffers (both ops)
     int off_taps_bytes, off_bar_bytes;
     int flip, add_identity;
     int segs_q;                   // column segments (of PLW*NPX pixels) per tile row
@@ -127,7 +128,7 @@ direct_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *
         tile_coords(it, n0, p0, q0);
         const int b = it & 1;
         mbar_expect_tx(&full[b], p.tile_bytes);
-        tma_load_4d(smem_raw + (size_t)b * p.tile_stride, &tmap, &full[b], c0, q0 * p.stride - p.hw,
+        tma_load_4d(smem_raw + (size_t)b * p.buf_stride, &tmap, &full[b], c0, q0 * p.stride - p.hw,
                     p0 * p.stride - p.hh, n0);
     };
     if (tid == 0) {
@@ -143,7 +144,7 @@ direct_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *
         tile_coords(it, n0, p0, q0);
         const int b = it & 1;
         if (!failed && !mbar_wait(&full[b], (it >> 1) & 1)) failed = true;
-        const uint32_t tile_b = smem_u32(smem_raw) + b * p.tile_stride;   // shared address of the buffer
+        const uint32_t tile_b = smem_u32(smem_raw) + b * p.buf_stride;    // shared address of the buffer
         for (int u = warp; u < units; u += kDirectThreads / 32) {
             const int img = p.div_thsq.div(u), r = u - img * (p.Th * p.segs_q);
             const int pr = p.div_sq.div(r), sq = r - pr * p.segs_q;
@@ -169,6 +170,174 @@ direct_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *
         __syncthreads();                                   // everyone is done with buffer b
         if (tid == 0 && it + 2 < my_tiles) issue(it + 2);
     }
+}
+
+
+constexpr int kDirectPartialStride = 32;   // floats per channel in a partial: up to 31 taps + bias-gradient sum
+
+// Weight gradient with the same tiles and the same thread layout as the forward kernel:
+//   dw[c][k] = sum over (n, p, q) of x[n, p*s+dh_k, q*s+dw_k, c] * dy[n, p, q, c],  db[c] = sum dy.
+// A second TMA box per tile brings dy[NI][Th][Tq][CCs]; out-of-range rows, columns and images of
+// both boxes are hardware zero fill, so edge tiles need no masks beyond the segment overrun.
+// Each thread keeps one accumulator per kept tap of its channel for the whole launch; at the
+// end the accumulators are added across the pixel lanes of a warp (shuffles), across the warps
+// (shared memory, warp order) and written as one partial per (CTA, channel);
+// direct_wgrad_final_kernel adds the partials of a chunk's CTAs in CTA order.  No atomics:
+// bit-reproducible.  (Reference: models/dwoconv1d/kernels/kernels.h:402-518, 31 atomicAdd per block.)
+template <typename T, int KT, int NPX, int STRIDE>
+__global__ void __launch_bounds__(kDirectThreads, 2)
+direct_wgrad_nhwc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_dy,
+                         const uint16_t *__restrict__ cls, const int8_t *__restrict__ taps,
+                         float *__restrict__ partial, const DirectParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + p.off_bar_bytes);
+    int *s_off = reinterpret_cast<int *>(smem_raw + p.off_taps_bytes);   // [CCs][KT] byte offsets
+
+    const int tid = threadIdx.x;
+    const int CCs = p.CCs;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int cl = lane % CCs, pl = lane / CCs;
+    const int PLW = 32 / CCs;
+    constexpr int DELTA = 32 * (int)sizeof(T) * STRIDE;
+    constexpr int DDY = 32 * (int)sizeof(T);              // dy pixels of one thread are PLW apart too
+    const int groups = gridDim.x / p.nchunks;
+    const int chunk = blockIdx.x % p.nchunks;
+    const int first = blockIdx.x / p.nchunks;
+    const int c0 = chunk * CCs;
+    const int my_tiles = (p.tiles_per_chunk - first + groups - 1) / groups;
+
+    if (tid == 0) {
+        mbar_init(&full[0], 1);
+        mbar_init(&full[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (tid < CCs) {       // same compression as the forward kernel: slot n <-> n-th tap that can reach the image
+        const int8_t *t = taps + (size_t)cls[c0 + tid] * p.K * 2;
+        int n = 0;
+        for (int k = 0; k < p.K; k++) {
+            const int dh = t[2 * k], dw = t[2 * k + 1];
+            const int adh = dh < 0 ? -dh : dh, adw = dw < 0 ? -dw : dw;
+            if (adh > p.hh || adw > p.hw) continue;
+            if (n < KT) s_off[tid * KT + n++] = (dh * p.TWp + dw) * CCs * (int)sizeof(T);
+        }
+        for (; n < KT; n++) s_off[tid * KT + n] = 0;
+    }
+    __syncthreads();
+    int off[KT];
+    float acc[KT];
+#pragma unroll
+    for (int k = 0; k < KT; k++) { off[k] = s_off[cl * KT + k]; acc[k] = 0.f; }
+    float acc_db = 0.f;
+    // The slack behind each input tile is read (times a zero dy) by the overrun pixels of the
+    // last row segment: it must hold finite numbers.  TMA never writes there.
+    for (int b = 0; b < 2; b++)
+        for (int i = p.tile_bytes / 4 + tid; i < p.tile_stride / 4; i += kDirectThreads)
+            reinterpret_cast<uint32_t *>(smem_raw + (size_t)b * p.buf_stride)[i] = 0u;
+    __syncthreads();
+
+    auto tile_coords = [&](int it, int &n0, int &p0, int &q0) {
+        const int t = first + it * groups;
+        const int tn = p.div_tiles_pq.div(t), r = t - tn * (p.tiles_p * p.tiles_q);
+        const int tp = p.div_tiles_q.div(r), tq = r - tp * p.tiles_q;
+        n0 = tn * p.NI; p0 = tp * p.Th; q0 = tq * p.Tq;
+    };
+    auto issue = [&](int it) {
+        int n0, p0, q0;
+        tile_coords(it, n0, p0, q0);
+        const int b = it & 1;
+        unsigned char *buf = smem_raw + (size_t)b * p.buf_stride;
+        mbar_expect_tx(&full[b], p.tile_bytes + p.dy_bytes);
+        tma_load_4d(buf, &tmap_x, &full[b], c0, q0 * p.stride - p.hw, p0 * p.stride - p.hh, n0);
+        tma_load_4d(buf + p.tile_stride, &tmap_dy, &full[b], c0, q0, p0, n0);
+    };
+    if (tid == 0) {
+        if (my_tiles > 0) issue(0);
+        if (my_tiles > 1) issue(1);
+    }
+
+    const int units = p.NI * p.Th * p.segs_q;
+    const int img_elems = p.THp * p.TWp * CCs;
+    bool failed = false;
+    for (int it = 0; it < my_tiles; it++) {
+        int n0, p0, q0;
+        tile_coords(it, n0, p0, q0);
+        const int b = it & 1;
+        if (!failed && !mbar_wait(&full[b], (it >> 1) & 1)) failed = true;
+        const uint32_t tile_b = smem_u32(smem_raw) + b * p.buf_stride;
+        const uint32_t dy_b = tile_b + p.tile_stride;
+        for (int u = warp; u < units; u += kDirectThreads / 32) {
+            const int img = p.div_thsq.div(u), r = u - img * (p.Th * p.segs_q);
+            const int pr = p.div_sq.div(r), sq = r - pr * p.segs_q;
+            const int pc0 = sq * (PLW * NPX) + pl;
+            if (n0 + img >= p.N || p0 + pr >= p.P) continue;      // zero-filled part of an edge tile
+            const uint32_t gaddr = dy_b + (((img * p.Th + pr) * p.Tq + pc0) * CCs + cl) * (int)sizeof(T);
+            float g[NPX];
+            static_for<0, NPX>([&](auto j) {
+                // columns past the tile belong to the next row of the box
+                g[j] = (pc0 + PLW * j < p.Tq) ? ld_smem<T, j * DDY>(gaddr) : 0.f;
+                acc_db += g[j];
+            });
+            const uint32_t base = tile_b + (img * img_elems + ((pr * STRIDE + p.hh) * p.TWp + pc0 * STRIDE + p.hw) * CCs + cl) * (int)sizeof(T);
+#pragma unroll
+            for (int k = 0; k < KT; k++) {
+                const uint32_t a = base + off[k];
+                static_for<0, NPX>([&](auto j) { acc[k] = fmaf(ld_smem<T, j * DELTA>(a), g[j], acc[k]); });
+            }
+        }
+        __syncthreads();
+        if (tid == 0 && it + 2 < my_tiles) issue(it + 2);
+    }
+
+    // ---- reduction: pixel lanes (shuffles), then warps (shared memory, fixed order) ----------
+#pragma unroll
+    for (int k = 0; k < KT; k++)
+        for (int d = CCs; d < 32; d <<= 1) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], d);
+    for (int d = CCs; d < 32; d <<= 1) acc_db += __shfl_xor_sync(0xffffffffu, acc_db, d);
+    float *red = reinterpret_cast<float *>(smem_raw);        // [warps][CCs][32]; the tiles are done with
+    if (pl == 0) {
+        float *r = red + (warp * CCs + cl) * kDirectPartialStride;
+#pragma unroll
+        for (int k = 0; k < KT; k++) r[k] = acc[k];
+        r[kDirectPartialStride - 1] = acc_db;
+    }
+    __syncthreads();
+    for (int e = tid; e < CCs * kDirectPartialStride; e += kDirectThreads) {
+        const int k = e % kDirectPartialStride;
+        float sum = 0.f;
+        if (k < KT || k == kDirectPartialStride - 1)
+            for (int w = 0; w < kDirectThreads / 32; w++) sum += red[w * CCs * kDirectPartialStride + e];
+        partial[(size_t)blockIdx.x * CCs * kDirectPartialStride + e] = sum;
+    }
+}
+
+// dw[c][k] = sum over the CTAs of c's chunk, in CTA order, of their partial for the slot tap k was kept in
+// (0 if the tap cannot reach inside an image of this size).
+__global__ void direct_wgrad_final_kernel(const float *__restrict__ partial, const uint16_t *__restrict__ cls,
+                                          const int8_t *__restrict__ taps, float *__restrict__ dw,
+                                          float *__restrict__ db, int C, int K, int CCs, int nchunks, int groups,
+                                          int hh, int hw) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= C * (K + 1)) return;
+    const int c = idx / (K + 1), k = idx % (K + 1);
+    if (k == K && db == nullptr) return;
+    const int chunk = c / CCs, cl = c % CCs;
+    int slot = kDirectPartialStride - 1;
+    if (k < K) {
+        const int8_t *t = taps + (size_t)cls[c] * K * 2;
+        slot = 0;
+        bool kept = false;
+        for (int i = 0; i <= k; i++) {
+            const int dh = t[2 * i], dwv = t[2 * i + 1];
+            const bool in = (dh < 0 ? -dh : dh) <= hh && (dwv < 0 ? -dwv : dwv) <= hw;
+            if (i < k) slot += in ? 1 : 0; else kept = in;
+        }
+        if (!kept) slot = -1;
+    }
+    float sum = 0.f;
+    for (int g = 0; g < groups && slot >= 0; g++)
+        sum += partial[((size_t)(g * nchunks + chunk) * CCs + cl) * kDirectPartialStride + slot];
+    if (k == K) db[c] = sum; else dw[(size_t)c * K + k] = sum;
 }
 
 }  // namespace o1d

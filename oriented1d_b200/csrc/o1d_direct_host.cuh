@@ -12,8 +12,10 @@ struct DirectConfig {
     bool whole_image;      // one tile covers a whole image (no halo re-reads)
 };
 
+// wgrad: also reserve room for the dy tiles and the end-of-kernel reduction scratch.
 inline bool direct_configure(const PlanHeader &ph, const void *plan_host, int N, int H, int W, int C, int K,
-                             int stride, int layout, int esize, int smem_limit, int sms, DirectConfig *out) {
+                             int stride, int layout, int esize, int smem_limit, int sms, bool wgrad,
+                             DirectConfig *out) {
     if (layout != O1D_NHWC || K > kMaxTaps || (stride != 1 && stride != 2)) return false;
     const int CCs = 32 / esize;
     if (C % CCs != 0) return false;
@@ -38,7 +40,7 @@ inline bool direct_configure(const PlanHeader &ph, const void *plan_host, int N,
     auto tile_bytes = [&](int th, int tq, int ni) {
         return (long long)((th - 1) * stride + 1 + 2 * p.hh) * ((tq - 1) * stride + 1 + 2 * p.hw) * CCs * esize * ni;
     };
-    const long long kSmall = 40 * 1024, kLarge = 100 * 1024;
+    const long long kSmall = 40 * 1024, kLarge = (wgrad ? 84 : 100) * 1024;
     int Th = p.P, Tq = p.Q, NI = 1;
     bool whole = true;
     if ((Tq - 1) * stride + 1 + 2 * p.hw > 256 || (Th - 1) * stride + 1 + 2 * p.hh > 256 || tile_bytes(Th, Tq, 1) > kLarge) {
@@ -65,12 +67,16 @@ inline bool direct_configure(const PlanHeader &ph, const void *plan_host, int N,
     p.tile_bytes = p.THp * p.TWp * CCs * esize * NI;
     // slack after each buffer: the last row segment of a tile may read up to 16 pixels past it
     p.tile_stride = ((p.tile_bytes + 127) & ~127) + 16 * stride * CCs * esize;
+    p.dy_bytes = wgrad ? Th * Tq * CCs * esize * NI : 0;
+    p.buf_stride = p.tile_stride + (wgrad ? ((p.dy_bytes + 127) & ~127) + 16 * CCs * esize : 0);
     const int plw = 32 / CCs;
     const int npx = (Tq >= 3 * plw) ? 4 : (Tq > plw ? 2 : 1);
     p.segs_q = ceil_div(Tq, plw * npx);
-    p.off_taps_bytes = 2 * p.tile_stride;
+    p.off_taps_bytes = 2 * p.buf_stride;
     p.off_bar_bytes = p.off_taps_bytes + CCs * kt * 8;
-    const int smem = p.off_bar_bytes + 16;
+    int smem = p.off_bar_bytes + 16;
+    const int red_bytes = (kDirectThreads / 32) * CCs * kDirectPartialStride * 4;   // reuses the tile buffers
+    if (wgrad && smem < red_bytes) smem = red_bytes;
     if (smem > smem_limit) return false;
     int ctas = (228 * 1024) / (smem + 1024);
     if (ctas > 2) ctas = 2;
@@ -102,6 +108,55 @@ inline bool make_direct_tensor_map(CUtensorMap *map, const void *base, int N, in
                const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// 4-D tensor map over dy [N][P][Q][C] with a box CCs x Tq x Th x NI.
+inline bool make_direct_dy_tensor_map(CUtensorMap *map, const void *base, int N, int P, int Q, int C, int esize,
+                                      const DirectParams &p) {
+    PFN_encodeTiled enc = encode_tiled_fn();
+    if (!enc || ((uintptr_t)base & 15) || (C * esize) % 16 != 0) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)Q, (cuuint64_t)P, (cuuint64_t)N};
+    cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)Q * C * esize, (cuuint64_t)P * Q * C * esize};
+    cuuint32_t box[4] = {(cuuint32_t)p.CCs, (cuuint32_t)p.Tq, (cuuint32_t)p.Th, (cuuint32_t)p.NI};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+               const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int KT, int NPX, int STRIDE>
+cudaError_t launch_direct_wgrad_one(const DirectConfig &cfg, const CUtensorMap &mx, const CUtensorMap &mdy,
+                                    const PlanView &pv, float *partial, cudaStream_t st) {
+    auto kern = direct_wgrad_nhwc_kernel<T, KT, NPX, STRIDE>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
+    if (e != cudaSuccess) return e;
+    kern<<<cfg.grid, kDirectThreads, cfg.smem_bytes, st>>>(mx, mdy, pv.cls, pv.taps, partial, cfg.p);
+    return cudaGetLastError();
+}
+template <typename T, int KT, int STRIDE>
+cudaError_t launch_direct_wgrad_npx(const DirectConfig &cfg, const CUtensorMap &mx, const CUtensorMap &mdy,
+                                    const PlanView &pv, float *partial, cudaStream_t st) {
+    switch (cfg.npx) {
+        case 4: return launch_direct_wgrad_one<T, KT, 4, STRIDE>(cfg, mx, mdy, pv, partial, st);
+        case 2: return launch_direct_wgrad_one<T, KT, 2, STRIDE>(cfg, mx, mdy, pv, partial, st);
+        default: return launch_direct_wgrad_one<T, KT, 1, STRIDE>(cfg, mx, mdy, pv, partial, st);
+    }
+}
+template <typename T, int STRIDE>
+cudaError_t launch_direct_wgrad_kt(const DirectConfig &cfg, const CUtensorMap &mx, const CUtensorMap &mdy,
+                                   const PlanView &pv, float *partial, cudaStream_t st) {
+    switch (cfg.kt) {
+        case 15: return launch_direct_wgrad_npx<T, 15, STRIDE>(cfg, mx, mdy, pv, partial, st);
+        case 23: return launch_direct_wgrad_npx<T, 23, STRIDE>(cfg, mx, mdy, pv, partial, st);
+        default: return launch_direct_wgrad_npx<T, 31, STRIDE>(cfg, mx, mdy, pv, partial, st);
+    }
+}
+template <typename T>
+cudaError_t launch_direct_wgrad(const DirectConfig &cfg, const CUtensorMap &mx, const CUtensorMap &mdy,
+                                const PlanView &pv, float *partial, cudaStream_t st) {
+    return cfg.p.stride == 1 ? launch_direct_wgrad_kt<T, 1>(cfg, mx, mdy, pv, partial, st)
+                             : launch_direct_wgrad_kt<T, 2>(cfg, mx, mdy, pv, partial, st);
 }
 
 template <typename T, int KT, int NPX, int STRIDE>

@@ -302,12 +302,17 @@ def test_tiled_route_equals_general_route(hw, C, mode, dtype):
         else:
             assert float(((y - y_ref).abs() / y_ref.abs().clamp_min(1e-2)).max()) <= 2 ** -7, route
             assert float(((dx - dx_ref).abs() / dx_ref.abs().clamp_min(1e-2)).max()) <= 2 ** -7, route
-    dw, db = o1d.wgrad(dy, x, plan, 1, True, True)
-    dw2, db2 = o1d.wgrad(dy, x, plan, 1, True, True)
-    assert o1d.ops.device_status() == 0
-    assert torch.equal(dw, dw2) and torch.equal(db, db2)          # deterministic
-    assert float((dw - dw_ref).abs().max()) <= 1e-4 * float(dw_ref.abs().max())
-    assert float((db - db_ref).abs().max()) <= 1e-4 * float(db_ref.abs().max())
+    for route in (0, 3):             # automatic (tiled where it applies), direct preferred
+        try:
+            o1d.ops.set_route(route)
+            dw, db = o1d.wgrad(dy, x, plan, 1, True, True)
+            dw2, db2 = o1d.wgrad(dy, x, plan, 1, True, True)
+        finally:
+            o1d.ops.set_route(0)
+        assert o1d.ops.device_status() == 0
+        assert torch.equal(dw, dw2) and torch.equal(db, db2), route          # deterministic
+        assert float((dw - dw_ref).abs().max()) <= 1e-4 * float(dw_ref.abs().max()), route
+        assert float((db - db_ref).abs().max()) <= 1e-4 * float(db_ref.abs().max()), route
     if dtype == torch.float32:
         assert float((y - y_ref).abs().max()) <= 1e-5 * float(y_ref.abs().max())
         assert float((dx - dx_ref).abs().max()) <= 1e-5 * float(dx_ref.abs().max())
