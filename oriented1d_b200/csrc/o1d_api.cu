@@ -260,6 +260,26 @@ int try_tiled_wgrad(const void *dy, const void *x, const PlanHeader &ph, const v
     return O1D_OK;
 }
 
+// Stride-2 input gradient through the direct kernel (tiles of the dy grid, one pass per output parity class).
+int try_direct_dgrad2(const void *dy, const float *w, const PlanHeader &ph, const void *plan_host,
+                      const void *plan_dev, void *dx, int N, int H, int W, int C, int K, int layout, int dtype,
+                      int add_identity, cudaStream_t st, const DeviceInfo &d) {
+    if (g_force_generic) return kNotTiled;
+    const int esize = dtype == O1D_F32 ? 4 : 2;
+    DirectConfig cfg;
+    if (!direct_configure_dgrad2(ph, plan_host, N, H, W, C, K, layout, esize, d.smem_optin, d.sms, &cfg))
+        return kNotTiled;
+    if (((uintptr_t)dx & 3) != 0) return kNotTiled;
+    CUtensorMap map;
+    if (!make_direct_tensor_map(&map, dy, N, cfg.p.H, cfg.p.W, C, esize, cfg.p)) return kNotTiled;
+    cfg.p.add_identity = add_identity;
+    PlanView pv = plan_view(plan_dev, ph);
+    const cudaError_t e = dtype == O1D_F32 ? launch_direct_dgrad2<float>(cfg, map, w, pv, dx, H, W, st)
+                                           : launch_direct_dgrad2<__nv_bfloat16>(cfg, map, w, pv, dx, H, W, st);
+    if (e != cudaSuccess) return cuda_fail(e, "direct stride-2 dgrad launch");
+    return O1D_OK;
+}
+
 // Weight gradient through the direct kernels (any angles, stride 1 or 2); kNotTiled when they do not apply.
 int try_direct_wgrad(const void *dy, const void *x, const PlanHeader &ph, const void *plan_host,
                      const void *plan_dev, float *dw, float *db, void *workspace, size_t workspace_bytes, int N,
@@ -481,7 +501,9 @@ int o1d_dgrad(const void *dy, const float *w, const void *plan_host, const void 
     // with the weights read in reverse order
     rc = stride == 1 ? route_forward(dy, w, nullptr, ph, plan_host, plan_dev, dx, N, H, W, C, K, stride, layout,
                                      dtype, add_identity, /*flip=*/1, st, d)
-                     : kNotTiled;
+         : stride == 2 ? try_direct_dgrad2(dy, w, ph, plan_host, plan_dev, dx, N, H, W, C, K, layout, dtype,
+                                           add_identity, st, d)
+                       : kNotTiled;
     if (rc != kNotTiled) return rc;
     return O1D_DISPATCH(launch_generic_dgrad, dy, w, ph, plan_dev, dx, N, H, W, C, K, stride,
                         add_identity, st, d);

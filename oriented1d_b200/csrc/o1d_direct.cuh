@@ -340,4 +340,143 @@ __global__ void direct_wgrad_final_kernel(const float *__restrict__ partial, con
     if (k == K) db[c] = sum; else dw[(size_t)c * K + k] = sum;
 }
 
+
+constexpr int kDgrad2Slots = 16;   // merged taps per parity class (a line of 31 offsets has at most 16 of one parity)
+
+// Input gradient for stride 2, gathered per output pixel:
+//   dx[n,h,w,c] = sum over taps k with (h-dh_k, w-dw_k) both even of w'[c,k] * dy[n,(h-dh_k)/2,(w-dw_k)/2,c].
+// Output pixels split into four parity classes (h&1, w&1); class (ph,pw) only sees taps with
+// dh_k = ph, dw_k = pw (mod 2), for which (h-dh_k)/2 = a - e_k with h = 2a+ph, e_k = (dh_k-ph)/2.
+// So the kernel is the forward kernel's tile machinery run over the dy grid (a, b) with
+// stride 1 and a halo of ceil(max|d|/2): a TMA box of dy per tile (zero fill outside is the
+// range test), and per class a short tap list (weight, byte offset -(e*TWp+f)*32) in registers.
+// The four classes are four passes over the tile; passes whose longest list in this CTA's
+// channel chunk is 0 or <= 8 run a shorter unrolled loop.  p.H/p.W are the dy grid extents here;
+// Hx, Wx those of dx.  (Reference: models/dwoconv1d/kernels/kernels.h:312-399 tests `%` and `/`
+// by the stride for every tap of every pixel.)
+template <typename T, int NPX>
+__global__ void __launch_bounds__(kDirectThreads, 2)
+direct_dgrad2_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restrict__ wgt,
+                          const uint16_t *__restrict__ cls, const int8_t *__restrict__ taps,
+                          T *__restrict__ dx, int Hx, int Wx, const DirectParams p) {
+    constexpr int KS = kDgrad2Slots;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + p.off_bar_bytes);
+    float *s_w = reinterpret_cast<float *>(smem_raw + p.off_taps_bytes);     // [4][CCs][KS]
+    int *s_off = reinterpret_cast<int *>(s_w + 4 * p.CCs * KS);               // [4][CCs][KS]
+    int *s_len = s_off + 4 * p.CCs * KS;                                      // [4][CCs]
+
+    const int tid = threadIdx.x;
+    const int CCs = p.CCs;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int cl = lane % CCs, pl = lane / CCs;
+    const int PLW = 32 / CCs;
+    constexpr int DELTA = 32 * (int)sizeof(T);
+    const int groups = gridDim.x / p.nchunks;
+    const int chunk = blockIdx.x % p.nchunks;
+    const int first = blockIdx.x / p.nchunks;
+    const int c0 = chunk * CCs;
+    const int my_tiles = (p.tiles_per_chunk - first + groups - 1) / groups;
+
+    if (tid == 0) {
+        mbar_init(&full[0], 1);
+        mbar_init(&full[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (tid < CCs) {
+        const int c = c0 + tid;
+        const int8_t *t = taps + (size_t)cls[c] * p.K * 2;
+        const int pad = p.K / 2;
+        int n[4] = {0, 0, 0, 0};
+        for (int k = 0; k < p.K; k++) {
+            const int dh = t[2 * k], dw = t[2 * k + 1];
+            const int ph = dh & 1, pw = dw & 1, q = ph * 2 + pw;
+            const int e = (dh - ph) >> 1, f = (dw - pw) >> 1;          // exact: dh-ph and dw-pw are even
+            float wv = __ldg(wgt + (size_t)c * p.K + k);
+            if (p.add_identity && k == pad) wv += 1.f;
+            const int off = -(e * p.TWp + f) * CCs * (int)sizeof(T);
+            float *lw = s_w + (q * CCs + tid) * KS;
+            int *lo = s_off + (q * CCs + tid) * KS;
+            int hit = -1;
+            for (int i = 0; i < n[q]; i++) if (lo[i] == off) hit = i;   // colliding taps add their weights
+            if (hit >= 0) lw[hit] += wv;
+            else if (n[q] < KS) { lw[n[q]] = wv; lo[n[q]] = off; n[q]++; }
+        }
+        for (int q = 0; q < 4; q++) {
+            for (int i = n[q]; i < KS; i++) { s_w[(q * CCs + tid) * KS + i] = 0.f; s_off[(q * CCs + tid) * KS + i] = 0; }
+            s_len[q * CCs + tid] = n[q];
+        }
+    }
+    __syncthreads();
+
+    auto tile_coords = [&](int it, int &n0, int &p0, int &q0) {
+        const int t = first + it * groups;
+        const int tn = p.div_tiles_pq.div(t), r = t - tn * (p.tiles_p * p.tiles_q);
+        const int tp = p.div_tiles_q.div(r), tq = r - tp * p.tiles_q;
+        n0 = tn * p.NI; p0 = tp * p.Th; q0 = tq * p.Tq;
+    };
+    auto issue = [&](int it) {
+        int n0, p0, q0;
+        tile_coords(it, n0, p0, q0);
+        const int b = it & 1;
+        mbar_expect_tx(&full[b], p.tile_bytes);
+        tma_load_4d(smem_raw + (size_t)b * p.buf_stride, &tmap, &full[b], c0, q0 - p.hw, p0 - p.hh, n0);
+    };
+    if (tid == 0) {
+        if (my_tiles > 0) issue(0);
+        if (my_tiles > 1) issue(1);
+    }
+
+    const int units = p.NI * p.Th * p.segs_q;
+    const int img_elems = p.THp * p.TWp * CCs;
+    bool failed = false;
+    for (int it = 0; it < my_tiles; it++) {
+        int n0, p0, q0;
+        tile_coords(it, n0, p0, q0);
+        const int b = it & 1;
+        if (!failed && !mbar_wait(&full[b], (it >> 1) & 1)) failed = true;
+        const uint32_t tile_b = smem_u32(smem_raw) + b * p.buf_stride;
+        for (int q = 0; q < 4; q++) {
+            const int ph = q >> 1, pw = q & 1;
+            int lmax = 0;
+            for (int i = 0; i < CCs; i++) lmax = max(lmax, s_len[q * CCs + i]);    // uniform over the CTA
+            float w[KS];
+            int off[KS];
+#pragma unroll
+            for (int k = 0; k < KS; k++) { w[k] = s_w[(q * CCs + cl) * KS + k]; off[k] = s_off[(q * CCs + cl) * KS + k]; }
+            auto pass = [&](auto nslots) {
+                constexpr int NS = decltype(nslots)::value;
+                for (int u = warp; u < units; u += kDirectThreads / 32) {
+                    const int img = p.div_thsq.div(u), r = u - img * (p.Th * p.segs_q);
+                    const int pr = p.div_sq.div(r), sq = r - pr * p.segs_q;
+                    const int pc0 = sq * (PLW * NPX) + pl;
+                    const int n = n0 + img, h = 2 * (p0 + pr) + ph;
+                    if (n >= p.N || h >= Hx) continue;
+                    const uint32_t base = tile_b + (img * img_elems + ((pr + p.hh) * p.TWp + pc0 + p.hw) * CCs + cl) * (int)sizeof(T);
+                    float acc[NPX];
+#pragma unroll
+                    for (int j = 0; j < NPX; j++) acc[j] = 0.f;
+#pragma unroll
+                    for (int k = 0; k < NS; k++) {
+                        const uint32_t a = base + off[k];
+                        static_for<0, NPX>([&](auto j) { acc[j] = fmaf(w[k], ld_smem<T, j * DELTA>(a), acc[j]); });
+                    }
+                    T *row = dx + (((size_t)n * Hx + h) * Wx) * p.C + c0 + cl;
+#pragma unroll
+                    for (int j = 0; j < NPX; j++) {
+                        const int pc = pc0 + PLW * j, wx = 2 * (q0 + pc) + pw;
+                        if (pc < p.Tq && wx < Wx) st(row + (size_t)wx * p.C, acc[j]);
+                    }
+                }
+            };
+            if (lmax == 0) pass(std::integral_constant<int, 0>{});
+            else if (lmax <= KS / 2) pass(std::integral_constant<int, KS / 2>{});
+            else pass(std::integral_constant<int, KS>{});
+        }
+        __syncthreads();
+        if (tid == 0 && it + 2 < my_tiles) issue(it + 2);
+    }
+}
+
 }  // namespace o1d

@@ -12,31 +12,16 @@ struct DirectConfig {
     bool whole_image;      // one tile covers a whole image (no halo re-reads)
 };
 
+// Tile selection for an H x W map with halo (hh, hw) and `tap_bytes` of per-CTA tap tables.
 // wgrad: also reserve room for the dy tiles and the end-of-kernel reduction scratch.
-inline bool direct_configure(const PlanHeader &ph, const void *plan_host, int N, int H, int W, int C, int K,
-                             int stride, int layout, int esize, int smem_limit, int sms, bool wgrad,
-                             DirectConfig *out) {
-    if (layout != O1D_NHWC || K > kMaxTaps || (stride != 1 && stride != 2)) return false;
+inline bool direct_configure_tiles(int N, int H, int W, int C, int K, int stride, int esize, int smem_limit, int sms,
+                                   bool wgrad, int hh, int hw, int kt, int tap_bytes, DirectConfig *out) {
     const int CCs = 32 / esize;
-    if (C % CCs != 0) return false;
     DirectParams p{};
     p.N = N; p.H = H; p.W = W; p.C = C; p.K = K; p.stride = stride;
     p.P = ceil_div(H, stride); p.Q = ceil_div(W, stride);
     p.CCs = CCs; p.nchunks = C / CCs;
-    p.hh = ph.max_dh < H - 1 ? ph.max_dh : H - 1;
-    p.hw = ph.max_dw < W - 1 ? ph.max_dw : W - 1;
-    // longest tap list after dropping taps that cannot reach the image
-    PlanView pv = plan_view(plan_host, ph);
-    int longest = 0;
-    for (int i = 0; i < ph.ncls; i++) {
-        int n = 0;
-        for (int k = 0; k < K; k++) {
-            const int dh = pv.taps[((size_t)i * K + k) * 2], dw = pv.taps[((size_t)i * K + k) * 2 + 1];
-            if ((dh < 0 ? -dh : dh) <= p.hh && (dw < 0 ? -dw : dw) <= p.hw) n++;
-        }
-        if (n > longest) longest = n;
-    }
-    const int kt = longest <= 15 ? 15 : longest <= 23 ? 23 : 31;
+    p.hh = hh; p.hw = hw;
     auto tile_bytes = [&](int th, int tq, int ni) {
         return (long long)((th - 1) * stride + 1 + 2 * p.hh) * ((tq - 1) * stride + 1 + 2 * p.hw) * CCs * esize * ni;
     };
@@ -73,7 +58,7 @@ inline bool direct_configure(const PlanHeader &ph, const void *plan_host, int N,
     const int npx = (Tq >= 3 * plw) ? 4 : (Tq > plw ? 2 : 1);
     p.segs_q = ceil_div(Tq, plw * npx);
     p.off_taps_bytes = 2 * p.buf_stride;
-    p.off_bar_bytes = p.off_taps_bytes + CCs * kt * 8;
+    p.off_bar_bytes = p.off_taps_bytes + tap_bytes;
     int smem = p.off_bar_bytes + 16;
     const int red_bytes = (kDirectThreads / 32) * CCs * kDirectPartialStride * 4;   // reuses the tile buffers
     if (wgrad && smem < red_bytes) smem = red_bytes;
@@ -92,6 +77,58 @@ inline bool direct_configure(const PlanHeader &ph, const void *plan_host, int N,
     out->kt = kt;
     out->npx = npx;
     out->whole_image = whole;
+    return true;
+}
+
+// Forward / weight gradient: halo = the lines' reach clipped to the image, KT = longest clipped tap list.
+inline bool direct_configure(const PlanHeader &ph, const void *plan_host, int N, int H, int W, int C, int K,
+                             int stride, int layout, int esize, int smem_limit, int sms, bool wgrad,
+                             DirectConfig *out) {
+    if (layout != O1D_NHWC || K > kMaxTaps || (stride != 1 && stride != 2)) return false;
+    const int CCs = 32 / esize;
+    if (C % CCs != 0) return false;
+    const int hh = ph.max_dh < H - 1 ? ph.max_dh : H - 1;
+    const int hw = ph.max_dw < W - 1 ? ph.max_dw : W - 1;
+    // longest tap list after dropping taps that cannot reach the image
+    PlanView pv = plan_view(plan_host, ph);
+    int longest = 0;
+    for (int i = 0; i < ph.ncls; i++) {
+        int n = 0;
+        for (int k = 0; k < K; k++) {
+            const int dh = pv.taps[((size_t)i * K + k) * 2], dw = pv.taps[((size_t)i * K + k) * 2 + 1];
+            if ((dh < 0 ? -dh : dh) <= hh && (dw < 0 ? -dw : dw) <= hw) n++;
+        }
+        if (n > longest) longest = n;
+    }
+    const int kt = longest <= 15 ? 15 : longest <= 23 ? 23 : 31;
+    return direct_configure_tiles(N, H, W, C, K, stride, esize, smem_limit, sms, wgrad, hh, hw, kt, CCs * kt * 8, out);
+}
+
+// Stride-2 input gradient: tiles of the dy grid (P x Q) with a halo of half the lines' reach.
+// Not applicable when some class has more than kDgrad2Slots distinct taps of one parity.
+inline bool direct_configure_dgrad2(const PlanHeader &ph, const void *plan_host, int N, int H, int W, int C, int K,
+                                    int layout, int esize, int smem_limit, int sms, DirectConfig *out) {
+    if (layout != O1D_NHWC || K > kMaxTaps) return false;
+    const int CCs = 32 / esize;
+    if (C % CCs != 0) return false;
+    PlanView pv = plan_view(plan_host, ph);
+    for (int i = 0; i < ph.ncls; i++) {
+        int n[4] = {0, 0, 0, 0};
+        int seen[4][kMaxTaps];
+        for (int k = 0; k < K; k++) {
+            const int dh = pv.taps[((size_t)i * K + k) * 2], dw = pv.taps[((size_t)i * K + k) * 2 + 1];
+            const int q = (dh & 1) * 2 + (dw & 1), key = dh * 64 + dw;
+            bool dup = false;
+            for (int j = 0; j < n[q]; j++) dup = dup || seen[q][j] == key;
+            if (!dup) seen[q][n[q]++] = key;
+        }
+        for (int q = 0; q < 4; q++) if (n[q] > kDgrad2Slots) return false;
+    }
+    const int P = ceil_div(H, 2), Q = ceil_div(W, 2);
+    const int hh = (ph.max_dh + 1) / 2, hw = (ph.max_dw + 1) / 2;
+    const int tap_bytes = 4 * CCs * kDgrad2Slots * 8 + 4 * CCs * 4;
+    if (!direct_configure_tiles(N, P, Q, C, K, 1, esize, smem_limit, sms, false, hh, hw, kDgrad2Slots, tap_bytes, out))
+        return false;
     return true;
 }
 
@@ -157,6 +194,25 @@ cudaError_t launch_direct_wgrad(const DirectConfig &cfg, const CUtensorMap &mx, 
                                 const PlanView &pv, float *partial, cudaStream_t st) {
     return cfg.p.stride == 1 ? launch_direct_wgrad_kt<T, 1>(cfg, mx, mdy, pv, partial, st)
                              : launch_direct_wgrad_kt<T, 2>(cfg, mx, mdy, pv, partial, st);
+}
+
+template <typename T, int NPX>
+cudaError_t launch_direct_dgrad2_one(const DirectConfig &cfg, const CUtensorMap &map, const float *w, const PlanView &pv,
+                                     void *dx, int Hx, int Wx, cudaStream_t st) {
+    auto kern = direct_dgrad2_nhwc_kernel<T, NPX>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
+    if (e != cudaSuccess) return e;
+    kern<<<cfg.grid, kDirectThreads, cfg.smem_bytes, st>>>(map, w, pv.cls, pv.taps, (T *)dx, Hx, Wx, cfg.p);
+    return cudaGetLastError();
+}
+template <typename T>
+cudaError_t launch_direct_dgrad2(const DirectConfig &cfg, const CUtensorMap &map, const float *w, const PlanView &pv,
+                                 void *dx, int Hx, int Wx, cudaStream_t st) {
+    switch (cfg.npx) {
+        case 4: return launch_direct_dgrad2_one<T, 4>(cfg, map, w, pv, dx, Hx, Wx, st);
+        case 2: return launch_direct_dgrad2_one<T, 2>(cfg, map, w, pv, dx, Hx, Wx, st);
+        default: return launch_direct_dgrad2_one<T, 1>(cfg, map, w, pv, dx, Hx, Wx, st);
+    }
 }
 
 template <typename T, int KT, int NPX, int STRIDE>

@@ -96,6 +96,7 @@ SHAPES = [
     (4, 768, 7, 7, 31, 1, "rr"),
     (2, 64, 32, 48, 31, 2, "model"),       # stem-like: stride 2
     (2, 64, 32, 48, 15, 2, "model+"),
+    (2, 16, 21, 27, 31, 2, "random"),      # stride 2, odd sizes, arbitrary angles
     (2, 16, 20, 28, 15, 1, "random"),
     (1, 24, 25, 40, 13, 1, "model+"),      # odd sizes
     (2, 16, 14, 14, 27, 1, "model"),
