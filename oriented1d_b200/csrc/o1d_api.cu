@@ -220,9 +220,19 @@ int route_forward(const void *x, const float *w, const float *bias, const PlanHe
                   const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride, int layout,
                   int dtype, int add_identity, int flip, cudaStream_t st, const DeviceInfo &d) {
     int rc = kNotTiled;
+    // Layers whose chunks are all of one line kind (the models' block-wise angle assignment) can
+    // leave half of a tiled CTA's threads without a segment; the direct kernels then win even
+    // with row tiles (28x28x192 fp32, batch 128: 167 vs 250 us).
+    bool weak_tiled = false;
+    if (g_prefer == 0 && stride == 1) {
+        TiledConfig t;
+        if (tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, dtype == O1D_F32 ? 4 : 2, d.smem_optin, d.sms,
+                            OP_FPROP, &t))
+            weak_tiled = t.util < 0.7;
+    }
     if (g_prefer != 2) {
         rc = try_direct(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
-                        flip, st, d, /*whole_image_only=*/g_prefer != 3);
+                        flip, st, d, /*whole_image_only=*/g_prefer != 3 && !weak_tiled);
         if (rc != kNotTiled) return rc;
     }
     rc = try_tiled(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity, flip,
@@ -535,7 +545,14 @@ int o1d_wgrad(const void *dy, const void *x, const void *plan_host, const void *
     // 84, 7x7 33 vs 59; bf16 only at 7x7, 40 vs 64, since every 2-byte load needs a widening shift).
     // Otherwise tiled, then direct (stems, dense-prediction maps, arbitrary angles), then general.
     const bool small_map = (dtype == O1D_F32) ? (H * W <= 32 * 32) : (H * W <= 10 * 10);
-    const bool direct_first = g_prefer == 3 || (g_prefer == 0 && small_map);
+    bool weak_tiled = false;     // see route_forward
+    if (g_prefer == 0 && !small_map) {
+        TiledConfig t;
+        if (tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, dtype == O1D_F32 ? 4 : 2, d.smem_optin, d.sms,
+                            OP_WGRAD, &t))
+            weak_tiled = t.util < 0.7;
+    }
+    const bool direct_first = g_prefer == 3 || (g_prefer == 0 && (small_map || weak_tiled));
     if (direct_first) {
         rc = try_direct_wgrad(dy, x, ph, plan_host, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K,
                               stride, layout, dtype, st, d, nullptr);
