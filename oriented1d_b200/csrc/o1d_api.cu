@@ -192,21 +192,26 @@ int try_direct(const void *x, const float *w, const float *bias, const PlanHeade
                int add_identity, int flip, cudaStream_t st, const DeviceInfo &d, bool whole_image_only) {
     if (g_force_generic) return kNotTiled;
     const int esize = dtype == O1D_F32 ? 4 : 2;
-    DirectConfig cfg;
-    if (!direct_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, false, &cfg))
+    DirectLaunchSet ls;
+    if (!direct_plan_launches(ph, plan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, DIRECT_FPROP, &ls))
         return kNotTiled;
-    if (whole_image_only && !cfg.whole_image) return kNotTiled;
+    if (whole_image_only && !ls.whole_image) return kNotTiled;
     // 2-byte elements pay a conversion per load here; measured against the tiled kernels the
     // direct ones only win while several images share a tile (7x7 yes, 14x14 no)
-    if (whole_image_only && esize == 2 && cfg.p.NI < 2) return kNotTiled;
+    if (whole_image_only && esize == 2 && ls.cfg[0].p.NI < 2) return kNotTiled;
     if (((uintptr_t)y & 3) != 0) return kNotTiled;
-    CUtensorMap map;
-    if (!make_direct_tensor_map(&map, x, N, H, W, C, esize, cfg.p)) return kNotTiled;
-    cfg.p.flip = flip;
-    cfg.p.add_identity = add_identity;
+    for (int i = 0; i < ls.n; i++) {
+        ls.cfg[i].p.flip = flip;
+        ls.cfg[i].p.add_identity = add_identity;
+    }
+    DirectMulti mp;
+    DirectMaps maps;
+    direct_fill_multi(ls, &mp);
+    for (int i = 0; i < ls.n; i++)
+        if (!make_direct_tensor_map(&maps.map[i], x, N, H, W, C, esize, ls.cfg[i].p)) return kNotTiled;
     PlanView pv = plan_view(plan_dev, ph);
-    const cudaError_t e = dtype == O1D_F32 ? launch_direct<float>(cfg, map, w, bias, pv, y, st)
-                                           : launch_direct<__nv_bfloat16>(cfg, map, w, bias, pv, y, st);
+    const cudaError_t e = dtype == O1D_F32 ? launch_direct<float>(ls, mp, maps, w, bias, pv, y, st)
+                                           : launch_direct<__nv_bfloat16>(ls, mp, maps, w, bias, pv, y, st);
     if (e != cudaSuccess) return cuda_fail(e, "direct fprop launch");
     return O1D_OK;
 }
@@ -276,16 +281,20 @@ int try_direct_dgrad2(const void *dy, const float *w, const PlanHeader &ph, cons
                       int add_identity, cudaStream_t st, const DeviceInfo &d) {
     if (g_force_generic) return kNotTiled;
     const int esize = dtype == O1D_F32 ? 4 : 2;
-    DirectConfig cfg;
-    if (!direct_configure_dgrad2(ph, plan_host, N, H, W, C, K, layout, esize, d.smem_optin, d.sms, &cfg))
+    DirectLaunchSet ls;
+    if (!direct_plan_launches(ph, plan_host, N, H, W, C, K, 2, layout, esize, d.smem_optin, d.sms, DIRECT_DGRAD2, &ls))
         return kNotTiled;
     if (((uintptr_t)dx & 3) != 0) return kNotTiled;
-    CUtensorMap map;
-    if (!make_direct_tensor_map(&map, dy, N, cfg.p.H, cfg.p.W, C, esize, cfg.p)) return kNotTiled;
-    cfg.p.add_identity = add_identity;
+    for (int i = 0; i < ls.n; i++) ls.cfg[i].p.add_identity = add_identity;
+    DirectMulti mp;
+    DirectMaps maps;
+    direct_fill_multi(ls, &mp);
+    for (int i = 0; i < ls.n; i++)
+        if (!make_direct_tensor_map(&maps.map[i], dy, N, ls.cfg[i].p.H, ls.cfg[i].p.W, C, esize, ls.cfg[i].p))
+            return kNotTiled;
     PlanView pv = plan_view(plan_dev, ph);
-    const cudaError_t e = dtype == O1D_F32 ? launch_direct_dgrad2<float>(cfg, map, w, pv, dx, H, W, st)
-                                           : launch_direct_dgrad2<__nv_bfloat16>(cfg, map, w, pv, dx, H, W, st);
+    const cudaError_t e = dtype == O1D_F32 ? launch_direct_dgrad2<float>(ls, mp, maps, w, pv, dx, H, W, st)
+                                           : launch_direct_dgrad2<__nv_bfloat16>(ls, mp, maps, w, pv, dx, H, W, st);
     if (e != cudaSuccess) return cuda_fail(e, "direct stride-2 dgrad launch");
     return O1D_OK;
 }
@@ -297,25 +306,28 @@ int try_direct_wgrad(const void *dy, const void *x, const PlanHeader &ph, const 
                      const DeviceInfo &d, size_t *need_bytes) {
     if (g_force_generic) return kNotTiled;
     const int esize = dtype == O1D_F32 ? 4 : 2;
-    DirectConfig cfg;
-    if (!direct_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, true, &cfg))
+    DirectLaunchSet ls;
+    if (!direct_plan_launches(ph, plan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, DIRECT_WGRAD, &ls))
         return kNotTiled;
-    const size_t need = (size_t)cfg.grid * cfg.p.CCs * kDirectPartialStride * sizeof(float);
+    const size_t need = ls.partial_floats * sizeof(float);
     if (need_bytes) { *need_bytes = need; return O1D_OK; }
     if (((uintptr_t)workspace & 15) != 0) return kNotTiled;
     if (workspace_bytes < need) return O1D_ERR_WORKSPACE;
-    CUtensorMap mx, mdy;
-    if (!make_direct_tensor_map(&mx, x, N, H, W, C, esize, cfg.p)) return kNotTiled;
-    if (!make_direct_dy_tensor_map(&mdy, dy, N, cfg.p.P, cfg.p.Q, C, esize, cfg.p)) return kNotTiled;
+    DirectMulti mp;
+    DirectMaps maps, dym;
+    direct_fill_multi(ls, &mp);
+    for (int i = 0; i < ls.n; i++) {
+        const DirectParams &p = ls.cfg[i].p;
+        if (!make_direct_tensor_map(&maps.map[i], x, N, H, W, C, esize, p)) return kNotTiled;
+        if (!make_direct_dy_tensor_map(&dym.map[i], dy, N, p.P, p.Q, C, esize, p)) return kNotTiled;
+    }
     PlanView pv = plan_view(plan_dev, ph);
     float *partial = (float *)workspace;
-    const cudaError_t e = dtype == O1D_F32 ? launch_direct_wgrad<float>(cfg, mx, mdy, pv, partial, st)
-                                           : launch_direct_wgrad<__nv_bfloat16>(cfg, mx, mdy, pv, partial, st);
+    const cudaError_t e = dtype == O1D_F32 ? launch_direct_wgrad<float>(ls, mp, maps, dym, pv, partial, st)
+                                           : launch_direct_wgrad<__nv_bfloat16>(ls, mp, maps, dym, pv, partial, st);
     if (e != cudaSuccess) return cuda_fail(e, "direct wgrad launch");
     const int tot = C * (K + 1);
-    direct_wgrad_final_kernel<<<ceil_div(tot, 128), 128, 0, st>>>(partial, pv.cls, pv.taps, dw, db, C, K, cfg.p.CCs,
-                                                                  cfg.p.nchunks, cfg.grid / cfg.p.nchunks, cfg.p.hh,
-                                                                  cfg.p.hw);
+    direct_wgrad_final_kernel<<<ceil_div(tot, 128), 128, 0, st>>>(mp, partial, pv.cls, pv.taps, dw, db, C, K);
     O1D_CUDA(cudaGetLastError());
     return O1D_OK;
 }
@@ -368,7 +380,8 @@ int o1d_uses_tiled(const void *plan_host, int N, int H, int W, int C, int K, int
     TiledConfig cfg;
     if (tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, 232448, 148, OP_FPROP, &cfg)) return 1;
     DirectConfig dcfg;
-    return direct_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, 232448, 148, false, &dcfg) ? 1 : 0;
+    const ChunkRange all{0, C / (32 / esize), ph.max_dh, ph.max_dw};
+    return direct_configure(ph, plan_host, all, N, H, W, C, K, stride, layout, esize, 232448, 148, false, &dcfg) ? 1 : 0;
 }
 
 int o1d_offsets(const float *theta_host, int C, int K, int8_t *dh, int8_t *dw) {

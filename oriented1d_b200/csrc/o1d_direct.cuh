@@ -30,7 +30,7 @@ constexpr int kDirectThreads = 256;
 
 struct DirectParams {
     int N, H, W, C, K, stride, P, Q;
-    int CCs, nchunks;
+    int CCs, nchunks, chunk0;     // this launch covers chunks [chunk0, chunk0 + nchunks)
     int Th, Tq, NI;               // output rows / columns / images per tile
     int THp, TWp;                 // input tile extents incl. halo
     int hh, hw;                   // halo rows / columns on each side
@@ -40,8 +40,29 @@ struct DirectParams {
     int off_taps_bytes, off_bar_bytes;
     int flip, add_identity;
     int segs_q;                   // column segments (of PLW*NPX pixels) per tile row
+    int partial_off;              // weight gradient: first float of this range's partials
     FastDiv div_sq, div_thsq, div_tiles_q, div_tiles_pq;
 };
+
+// One launch covers up to kMaxChunkRanges channel-chunk ranges, each with its own tile shape,
+// halo and tensor map (contiguous CTA index ranges): layers whose chunks reach differently far
+// (the models' block-wise angle assignment) get small halos where the lines allow it without
+// paying one launch per range.
+constexpr int kMaxChunkRanges = 8;
+struct DirectMulti {
+    int n;
+    int start[kMaxChunkRanges + 1];          // first CTA of each range; start[n] = grid
+    DirectParams p[kMaxChunkRanges];
+};
+// Tensor maps travel in a parameter of their own: their address is taken (TMA wants a pointer),
+// and a parameter whose address is taken is no longer read through constant-bank operands.
+struct DirectMaps { CUtensorMap map[kMaxChunkRanges]; };
+
+__device__ __forceinline__ int direct_range_of(const DirectMulti &mp, int cta) {
+    int r = 0;
+    while (r + 1 < mp.n && cta >= mp.start[r + 1]) r++;
+    return r;
+}
 
 // Load one element from a 32-bit shared-memory address plus a compile-time byte offset (the
 // offset is an immediate of the load, so a thread's NPX pixels share one address register).
@@ -62,12 +83,18 @@ template <typename T, int IMM> __device__ __forceinline__ float ld_smem(uint32_t
 // (PLW = 32/CCs pixel lanes); a thread's NPX pixels are PLW apart, so their tile addresses
 // differ by the compile-time constant 32*sizeof(T)*STRIDE bytes and share one address add per
 // tap, while the lanes of every single load still cover 32 different banks.
-template <typename T, int KT, int NPX, int STRIDE>
-__global__ void __launch_bounds__(kDirectThreads, 2)
-direct_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restrict__ wgt,
+// MULTI: the launch holds several chunk ranges (parameters are then indexed by range at run
+// time, which costs registers; such launches use large tiles and one CTA per SM anyway).
+template <typename T, int KT, int NPX, int STRIDE, bool MULTI>
+__global__ void __launch_bounds__(kDirectThreads, MULTI ? 1 : 2)
+direct_fprop_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMaps maps, const float *__restrict__ wgt,
                          const float *__restrict__ bias, const uint16_t *__restrict__ cls,
-                         const int8_t *__restrict__ taps, T *__restrict__ y, const DirectParams p) {
+                         const int8_t *__restrict__ taps, T *__restrict__ y) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int rng = MULTI ? direct_range_of(mp, blockIdx.x) : 0;
+    const DirectParams &p = mp.p[rng];
+    const CUtensorMap *tmap = &maps.map[rng];
+    const int bid = blockIdx.x - mp.start[rng], gsz = mp.start[rng + 1] - mp.start[rng];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + p.off_bar_bytes);
     // per-channel compressed tap lists, built once: [CCs][KT] (weight, offset)
     float *s_w = reinterpret_cast<float *>(smem_raw + p.off_taps_bytes);
@@ -80,9 +107,9 @@ direct_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *
     const int pl = lane / CCs;                // pixel lane within the warp
     const int PLW = 32 / CCs;                 // pixel lanes per warp
     constexpr int DELTA = 32 * (int)sizeof(T) * STRIDE;   // bytes between a thread's pixels
-    const int groups = gridDim.x / p.nchunks; // CTAs per chunk
-    const int chunk = blockIdx.x % p.nchunks;
-    const int first = blockIdx.x / p.nchunks;
+    const int groups = gsz / p.nchunks;        // CTAs per chunk
+    const int chunk = p.chunk0 + bid % p.nchunks;
+    const int first = bid / p.nchunks;
     const int c0 = chunk * CCs;
     const int my_tiles = (p.tiles_per_chunk - first + groups - 1) / groups;
 
@@ -128,7 +155,7 @@ direct_fprop_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *
         tile_coords(it, n0, p0, q0);
         const int b = it & 1;
         mbar_expect_tx(&full[b], p.tile_bytes);
-        tma_load_4d(smem_raw + (size_t)b * p.buf_stride, &tmap, &full[b], c0, q0 * p.stride - p.hw,
+        tma_load_4d(smem_raw + (size_t)b * p.buf_stride, tmap, &full[b], c0, q0 * p.stride - p.hw,
                     p0 * p.stride - p.hh, n0);
     };
     if (tid == 0) {
@@ -184,12 +211,17 @@ constexpr int kDirectPartialStride = 32;   // floats per channel in a partial: u
 // (shared memory, warp order) and written as one partial per (CTA, channel);
 // direct_wgrad_final_kernel adds the partials of a chunk's CTAs in CTA order.  No atomics:
 // bit-reproducible.  (Reference: models/dwoconv1d/kernels/kernels.h:402-518, 31 atomicAdd per block.)
-template <typename T, int KT, int NPX, int STRIDE>
-__global__ void __launch_bounds__(kDirectThreads, 2)
-direct_wgrad_nhwc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_dy,
+template <typename T, int KT, int NPX, int STRIDE, bool MULTI>
+__global__ void __launch_bounds__(kDirectThreads, MULTI ? 1 : 2)
+direct_wgrad_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMaps maps,
+                         const __grid_constant__ DirectMaps dym,
                          const uint16_t *__restrict__ cls, const int8_t *__restrict__ taps,
-                         float *__restrict__ partial, const DirectParams p) {
+                         float *__restrict__ partial) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int rng = MULTI ? direct_range_of(mp, blockIdx.x) : 0;
+    const DirectParams &p = mp.p[rng];
+    const CUtensorMap *tmap_x = &maps.map[rng], *tmap_dy = &dym.map[rng];
+    const int bid = blockIdx.x - mp.start[rng], gsz = mp.start[rng + 1] - mp.start[rng];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + p.off_bar_bytes);
     int *s_off = reinterpret_cast<int *>(smem_raw + p.off_taps_bytes);   // [CCs][KT] byte offsets
 
@@ -200,9 +232,9 @@ direct_wgrad_nhwc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
     const int PLW = 32 / CCs;
     constexpr int DELTA = 32 * (int)sizeof(T) * STRIDE;
     constexpr int DDY = 32 * (int)sizeof(T);              // dy pixels of one thread are PLW apart too
-    const int groups = gridDim.x / p.nchunks;
-    const int chunk = blockIdx.x % p.nchunks;
-    const int first = blockIdx.x / p.nchunks;
+    const int groups = gsz / p.nchunks;
+    const int chunk = p.chunk0 + bid % p.nchunks;
+    const int first = bid / p.nchunks;
     const int c0 = chunk * CCs;
     const int my_tiles = (p.tiles_per_chunk - first + groups - 1) / groups;
 
@@ -248,8 +280,8 @@ direct_wgrad_nhwc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
         const int b = it & 1;
         unsigned char *buf = smem_raw + (size_t)b * p.buf_stride;
         mbar_expect_tx(&full[b], p.tile_bytes + p.dy_bytes);
-        tma_load_4d(buf, &tmap_x, &full[b], c0, q0 * p.stride - p.hw, p0 * p.stride - p.hh, n0);
-        tma_load_4d(buf + p.tile_stride, &tmap_dy, &full[b], c0, q0, p0, n0);
+        tma_load_4d(buf, tmap_x, &full[b], c0, q0 * p.stride - p.hw, p0 * p.stride - p.hh, n0);
+        tma_load_4d(buf + p.tile_stride, tmap_dy, &full[b], c0, q0, p0, n0);
     };
     if (tid == 0) {
         if (my_tiles > 0) issue(0);
@@ -307,21 +339,25 @@ direct_wgrad_nhwc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
         float sum = 0.f;
         if (k < KT || k == kDirectPartialStride - 1)
             for (int w = 0; w < kDirectThreads / 32; w++) sum += red[w * CCs * kDirectPartialStride + e];
-        partial[(size_t)blockIdx.x * CCs * kDirectPartialStride + e] = sum;
+        partial[p.partial_off + (size_t)bid * CCs * kDirectPartialStride + e] = sum;
     }
 }
 
 // dw[c][k] = sum over the CTAs of c's chunk, in CTA order, of their partial for the slot tap k was kept in
 // (0 if the tap cannot reach inside an image of this size).
-__global__ void direct_wgrad_final_kernel(const float *__restrict__ partial, const uint16_t *__restrict__ cls,
-                                          const int8_t *__restrict__ taps, float *__restrict__ dw,
-                                          float *__restrict__ db, int C, int K, int CCs, int nchunks, int groups,
-                                          int hh, int hw) {
+__global__ void direct_wgrad_final_kernel(const DirectMulti mp, const float *__restrict__ partial,
+                                          const uint16_t *__restrict__ cls, const int8_t *__restrict__ taps,
+                                          float *__restrict__ dw, float *__restrict__ db, int C, int K) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= C * (K + 1)) return;
     const int c = idx / (K + 1), k = idx % (K + 1);
     if (k == K && db == nullptr) return;
-    const int chunk = c / CCs, cl = c % CCs;
+    const int CCs = mp.p[0].CCs;
+    int r = 0;
+    while (r + 1 < mp.n && c / CCs >= mp.p[r + 1].chunk0) r++;
+    const DirectParams &p = mp.p[r];
+    const int chunk = c / CCs - p.chunk0, cl = c % CCs;
+    const int groups = (mp.start[r + 1] - mp.start[r]) / p.nchunks;
     int slot = kDirectPartialStride - 1;
     if (k < K) {
         const int8_t *t = taps + (size_t)cls[c] * K * 2;
@@ -329,17 +365,16 @@ __global__ void direct_wgrad_final_kernel(const float *__restrict__ partial, con
         bool kept = false;
         for (int i = 0; i <= k; i++) {
             const int dh = t[2 * i], dwv = t[2 * i + 1];
-            const bool in = (dh < 0 ? -dh : dh) <= hh && (dwv < 0 ? -dwv : dwv) <= hw;
+            const bool in = (dh < 0 ? -dh : dh) <= p.hh && (dwv < 0 ? -dwv : dwv) <= p.hw;
             if (i < k) slot += in ? 1 : 0; else kept = in;
         }
         if (!kept) slot = -1;
     }
     float sum = 0.f;
     for (int g = 0; g < groups && slot >= 0; g++)
-        sum += partial[((size_t)(g * nchunks + chunk) * CCs + cl) * kDirectPartialStride + slot];
+        sum += partial[p.partial_off + ((size_t)(g * p.nchunks + chunk) * CCs + cl) * kDirectPartialStride + slot];
     if (k == K) db[c] = sum; else dw[(size_t)c * K + k] = sum;
 }
-
 
 constexpr int kDgrad2Slots = 16;   // merged taps per parity class (a line of 31 offsets has at most 16 of one parity)
 
@@ -354,13 +389,17 @@ constexpr int kDgrad2Slots = 16;   // merged taps per parity class (a line of 31
 // channel chunk is 0 or <= 8 run a shorter unrolled loop.  p.H/p.W are the dy grid extents here;
 // Hx, Wx those of dx.  (Reference: models/dwoconv1d/kernels/kernels.h:312-399 tests `%` and `/`
 // by the stride for every tap of every pixel.)
-template <typename T, int NPX>
-__global__ void __launch_bounds__(kDirectThreads, 2)
-direct_dgrad2_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restrict__ wgt,
+template <typename T, int NPX, bool MULTI>
+__global__ void __launch_bounds__(kDirectThreads, MULTI ? 1 : 2)
+direct_dgrad2_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMaps maps, const float *__restrict__ wgt,
                           const uint16_t *__restrict__ cls, const int8_t *__restrict__ taps,
-                          T *__restrict__ dx, int Hx, int Wx, const DirectParams p) {
+                          T *__restrict__ dx, int Hx, int Wx) {
     constexpr int KS = kDgrad2Slots;
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int rng = MULTI ? direct_range_of(mp, blockIdx.x) : 0;
+    const DirectParams &p = mp.p[rng];
+    const CUtensorMap *tmap = &maps.map[rng];
+    const int bid = blockIdx.x - mp.start[rng], gsz = mp.start[rng + 1] - mp.start[rng];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + p.off_bar_bytes);
     float *s_w = reinterpret_cast<float *>(smem_raw + p.off_taps_bytes);     // [4][CCs][KS]
     int *s_off = reinterpret_cast<int *>(s_w + 4 * p.CCs * KS);               // [4][CCs][KS]
@@ -372,9 +411,9 @@ direct_dgrad2_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float 
     const int cl = lane % CCs, pl = lane / CCs;
     const int PLW = 32 / CCs;
     constexpr int DELTA = 32 * (int)sizeof(T);
-    const int groups = gridDim.x / p.nchunks;
-    const int chunk = blockIdx.x % p.nchunks;
-    const int first = blockIdx.x / p.nchunks;
+    const int groups = gsz / p.nchunks;
+    const int chunk = p.chunk0 + bid % p.nchunks;
+    const int first = bid / p.nchunks;
     const int c0 = chunk * CCs;
     const int my_tiles = (p.tiles_per_chunk - first + groups - 1) / groups;
 
@@ -421,7 +460,7 @@ direct_dgrad2_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float 
         tile_coords(it, n0, p0, q0);
         const int b = it & 1;
         mbar_expect_tx(&full[b], p.tile_bytes);
-        tma_load_4d(smem_raw + (size_t)b * p.buf_stride, &tmap, &full[b], c0, q0 - p.hw, p0 - p.hh, n0);
+        tma_load_4d(smem_raw + (size_t)b * p.buf_stride, tmap, &full[b], c0, q0 - p.hw, p0 - p.hh, n0);
     };
     if (tid == 0) {
         if (my_tiles > 0) issue(0);
