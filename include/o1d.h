@@ -153,6 +153,14 @@ int o1d_wgrad_static(const void *dy, const void *x,
 int o1d_layernorm_cl(const void *x, const float *gamma, const float *beta, void *y,
                      long long rows, int C, float eps, int dtype, int gelu, void *stream);
 
+/* Stem input projection: y[n,hw,o] = bias[o] + sum_c w[o,c] * x[n,c,hw], x an NCHW image
+ * tensor with Cin <= 4 channels, y channels-last with Cout (a multiple of 8) channels: the
+ * `x.permute(0,2,3,1)` + `nn.Linear(in_chans, 64)` that opens the reference's 1D stem
+ * (models/convnext.py:143,170-176), in one pass.  x, y fp32 or bf16; w [Cout,Cin], bias [Cout]
+ * (or NULL) fp32.  Forward only. */
+int o1d_pointwise_in(const void *x, const float *w, const float *bias, void *y,
+                     int N, int Cin, long long HW, int Cout, int dtype, void *stream);
+
 /* Batched 2-D transpose [n, a, b] -> [n, b, a].  Replaces nhwc_to_nchw / nchw_to_nhwc
  * (kernels.cu:56-68, nhwc_utils.h:46-110): NHWC->NCHW is (n=N, a=H*W, b=C),
  * NCHW->NHWC is (n=N, a=C, b=H*W). */

@@ -92,8 +92,14 @@ class Stem1D(nn.Module):
         self.norm2 = LayerNorm(dim1)
         self.norm3 = LayerNorm(dim2)
 
-    def forward(self, x):                       # x: [N, H, W, 3]
-        x = self.pw1(x)
+    def forward(self, x, nchw_input=False):     # x: [N, H, W, 3], or the [N, 3, H, W] image itself
+        if nchw_input:
+            fast = (x.is_cuda and not torch.is_grad_enabled() and x.dtype in (torch.float32, torch.bfloat16)
+                    and x.shape[1] <= 4 and self.pw1.out_features % 8 == 0)
+            # inference: projection and layout change in one pass (see csrc/o1d_pointwise.cuh)
+            x = ops.pointwise_in(x, self.pw1.weight, self.pw1.bias) if fast else self.pw1(x.permute(0, 2, 3, 1))
+        else:
+            x = self.pw1(x)
         x = self.norm1(self.dw1(x), gelu=True)
         x = self.norm2(self.dw2(x), gelu=True)
         return self.norm3(self.pw2(x))
@@ -120,6 +126,12 @@ class Block1D(nn.Module):
 
     def forward(self, x):
         y = self.pwconv2(self._mlp_in(self.dwconv(x)))
+        return self._residual(x, y)
+
+    def _residual(self, x, y):
+        """x + drop_path(gamma * y) (convnext.py:314-318); one fused pass when nothing is dropped."""
+        if self.drop_path == 0.0 or not self.training:
+            return x + y if self.gamma is None else torch.addcmul(x, y, self.gamma)
         if self.gamma is not None:
             y = self.gamma * y
         return x + _drop_path(y, self.drop_path, self.training)
@@ -139,9 +151,7 @@ class Block1DPP(Block1D):
 
     def forward(self, x):
         y = self.pwconv2(self.dwconv2(self._mlp_in(self.dwconv1(x))))
-        if self.gamma is not None:
-            y = self.gamma * y
-        return x + _drop_path(y, self.drop_path, self.training)
+        return self._residual(x, y)
 
 
 def _drop_path(y, rate, training):
@@ -205,10 +215,10 @@ class ConvNeXt1D(nn.Module):
     def forward_features(self, x, all_stages=False):
         """x: images [N, 3, H, W].  Returns the last stage's map [N, C, H/32, W/32] (NCHW view),
         or the four stage maps when all_stages is set (the dense-prediction backbones' outputs)."""
-        x = x.permute(0, 2, 3, 1)
         outs = []
         for i in range(4):
-            x = self.stages[i](self.downsample_layers[i](x))
+            x = self.downsample_layers[i](x, nchw_input=True) if i == 0 else self.downsample_layers[i](x)
+            x = self.stages[i](x)
             outs.append(x.permute(0, 3, 1, 2))
         return outs if all_stages else outs[-1]
 

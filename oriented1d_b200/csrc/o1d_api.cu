@@ -13,6 +13,7 @@
 #include "o1d_direct_host.cuh"
 #include "o1d_layernorm.cuh"
 #include "o1d_transpose.cuh"
+#include "o1d_pointwise.cuh"
 
 using namespace o1d;
 
@@ -692,6 +693,30 @@ int o1d_layernorm_cl(const void *x, const float *gamma, const float *beta, void 
     cudaStream_t st = (cudaStream_t)stream;
     return dtype == O1D_F32 ? dispatch_ln<float>(x, gamma, beta, y, rows, C, eps, gelu, st, d)
                             : dispatch_ln<__nv_bfloat16>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
+}
+
+int o1d_pointwise_in(const void *x, const float *w, const float *bias, void *y, int N, int Cin, long long HW,
+                     int Cout, int dtype, void *stream) {
+    if (!x || !w || !y || N <= 0 || HW <= 0 || Cin <= 0 || Cout <= 0 || (dtype != O1D_F32 && dtype != O1D_BF16))
+        return O1D_ERR_INVALID;
+    if (Cin > 4 || Cout % 8 != 0 || HW > 0x7fffffffLL || ((uintptr_t)y & 15)) return O1D_ERR_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long npix = (long long)N * HW, total = npix * (Cout / 8);
+    const long long blocks = (total + kPointwiseThreads - 1) / kPointwiseThreads;
+    if (blocks > 0x7fffffffLL) return O1D_ERR_UNSUPPORTED;
+#define O1D_PW(T, CIN)                                                                                     \
+    pointwise_in_kernel<T, CIN><<<(unsigned)blocks, kPointwiseThreads, 0, st>>>((const T *)x, w, bias, (T *)y, npix, \
+                                                                                (int)HW, Cout)
+    if (dtype == O1D_F32) {
+        switch (Cin) { case 1: O1D_PW(float, 1); break; case 2: O1D_PW(float, 2); break;
+                       case 3: O1D_PW(float, 3); break; default: O1D_PW(float, 4); break; }
+    } else {
+        switch (Cin) { case 1: O1D_PW(__nv_bfloat16, 1); break; case 2: O1D_PW(__nv_bfloat16, 2); break;
+                       case 3: O1D_PW(__nv_bfloat16, 3); break; default: O1D_PW(__nv_bfloat16, 4); break; }
+    }
+#undef O1D_PW
+    O1D_CUDA(cudaGetLastError());
+    return O1D_OK;
 }
 
 int o1d_transpose(const void *in, void *out, int n, int a, int b, int dtype, void *stream) {

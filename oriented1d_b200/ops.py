@@ -174,6 +174,23 @@ def layer_norm_cl(x, weight, bias, eps: float = 1e-6, gelu: bool = False):
     return y
 
 
+def pointwise_in(x, weight, bias):
+    """Channels-last ``Linear`` over the few channels of an NCHW image: x [N,Cin,H,W] (Cin <= 4),
+    weight [Cout,Cin], bias [Cout] or None -> [N,H,W,Cout] (models/convnext.py:143,170-176 in one
+    pass).  Forward only."""
+    _need_cuda(x, weight)
+    x = x.contiguous()
+    N, Cin, H, W = x.shape
+    Cout = weight.shape[0]
+    y = torch.empty((N, H, W, Cout), dtype=x.dtype, device=x.device)
+    w32 = weight.detach().to(torch.float32).contiguous()
+    b32 = None if bias is None else bias.detach().to(torch.float32).contiguous()
+    with torch.cuda.device(x.device):
+        check(lib.o1d_pointwise_in(x.data_ptr(), w32.data_ptr(), 0 if b32 is None else b32.data_ptr(), y.data_ptr(),
+                                   N, Cin, H * W, Cout, _dtype_code(x), _stream()), "o1d_pointwise_in")
+    return y
+
+
 def uses_tiled(plan: Plan, N: int, H: int, W: int, stride: int, nhwc: bool, dtype: torch.dtype) -> bool:
     """Would this request run on the tiled kernels (True) or the general ones (False)?"""
     code = _DTYPES.get(dtype)

@@ -445,3 +445,22 @@ def test_layernorm_channels_last(C, dtype):
             ref = torch.nn.functional.gelu(ref)
         tol = 1e-5 if dtype == torch.float32 else 2 ** -7        # bf16: one rounding of the output
         assert float(((y - ref).abs() / ref.abs().clamp_min(1.0)).max()) <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("cin,cout", [(3, 64), (1, 8), (4, 96)])
+def test_pointwise_in(dtype, cin, cout):
+    """Stem input projection (NCHW image -> channels-last, Linear over the input channels)
+    against torch in float64 on the same (rounded) inputs."""
+    g = torch.Generator(device="cpu").manual_seed(cin * 100 + cout)
+    x = torch.randn((3, cin, 17, 23), generator=g).to(DEV).to(dtype)
+    w = torch.randn((cout, cin), generator=g).to(DEV)
+    b = torch.randn((cout,), generator=g).to(DEV)
+    y = o1d.ops.pointwise_in(x, w, b)
+    ref = torch.nn.functional.linear(x.double().permute(0, 2, 3, 1), w.double(), b.double())
+    assert y.shape == ref.shape and y.is_contiguous()
+    tol = 1e-6 if dtype == torch.float32 else 2 ** -8
+    assert float(((y.double() - ref).abs() / ref.abs().clamp_min(1.0)).max()) <= tol
+    y0 = o1d.ops.pointwise_in(x, w, None)
+    ref0 = ref - b.double()
+    assert float(((y0.double() - ref0).abs() / ref0.abs().clamp_min(1.0)).max()) <= tol
