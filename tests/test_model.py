@@ -33,23 +33,27 @@ def test_state_dict_layout_matches_reference(name, factory, variant):
 
 
 def _dense_kernel(conv):
-    """(2pad+1)^2 dense kernel of an oriented conv: w[c,k] scatter-added at its rasterised offset."""
+    """(2pad+1)^2 dense kernel of an oriented conv: w[c,k] scatter-added at its rasterised offset
+    (differentiable with respect to conv.weight)."""
     C, K = conv.weight.shape[0], conv.weight.shape[-1]
     pad = K // 2
     dh, dw = o1d.offsets(conv.theta.detach().float().cpu().numpy().reshape(-1), K)
-    w = conv.weight.detach().double().cpu().reshape(C, K).clone()
+    w = conv.weight.double().reshape(C, K)
     if conv.add_identity:
-        w[:, pad] += 1
-    k2d = torch.zeros((C, 1, 2 * pad + 1, 2 * pad + 1), dtype=torch.float64)
-    for c in range(C):
-        for k in range(K):
-            k2d[c, 0, dh[c, k] + pad, dw[c, k] + pad] += w[c, k]
+        eye = torch.zeros((C, K), dtype=torch.float64, device=w.device)
+        eye[:, pad] = 1
+        w = w + eye
+    ci = torch.arange(C).repeat_interleave(K).to(w.device)
+    ri = torch.from_numpy(np.ascontiguousarray(dh, dtype=np.int64)).reshape(-1).to(w.device) + pad
+    qi = torch.from_numpy(np.ascontiguousarray(dw, dtype=np.int64)).reshape(-1).to(w.device) + pad
+    k2d = torch.zeros((C, 1, 2 * pad + 1, 2 * pad + 1), dtype=torch.float64, device=w.device)
+    k2d = k2d.index_put((ci, torch.zeros_like(ci), ri, qi), w.reshape(-1), accumulate=True)
     return k2d, pad
 
 
 def _ref_conv(conv, x_nhwc):
     k2d, pad = _dense_kernel(conv)
-    y = F.conv2d(x_nhwc.permute(0, 3, 1, 2), k2d.to(x_nhwc.device), conv.bias.double(), conv.stride, pad, 1,
+    y = F.conv2d(x_nhwc.permute(0, 3, 1, 2), k2d, conv.bias.double(), conv.stride, pad, 1,
                  conv.weight.shape[0])
     return y.permute(0, 2, 3, 1)
 
@@ -98,3 +102,36 @@ def test_model_forward_matches_pytorch_restatement(variant):
         ref = _ref_forward(m, img)
     err = float((out.double() - ref).abs().max() / ref.abs().max())
     assert err < 1e-4, err
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("variant", ["1d", "1dpp"])
+def test_model_training_step_gradients(variant):
+    """Forward + backward through the autograd function of every oriented conv in the model
+    (stride-2 stems, identity-tap convs of 1D++, every stage size): gradients of all parameters
+    and of the input against float64 autograd through the PyTorch restatement."""
+    torch.manual_seed(1)
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    m = convnext1d.ConvNeXt1D(depths=(1, 1, 1, 1), dims=(32, 64, 96, 128), variant=variant, stem_dim1=16,
+                              layer_scale_init_value=0.5, num_classes=10).cuda().train()
+    for p in m.parameters():
+        if p.dim() > 1:
+            torch.nn.init.normal_(p, std=0.1)
+    img = torch.randn(2, 3, 64, 64, device="cuda", requires_grad=True)
+    target = torch.randn(2, 10, device="cuda")
+    (m(img) * target).sum().backward()
+    got = {k: p.grad.double().clone() for k, p in m.named_parameters() if p.grad is not None}
+    got_img = img.grad.double().clone()
+    assert not any(k.endswith("theta") for k in got)              # angles never receive a gradient
+    m.zero_grad(set_to_none=True)
+    img.grad = None
+    (_ref_forward(m, img) * target.double()).sum().backward()
+    for k, p in m.named_parameters():
+        if k.endswith("theta"):
+            continue
+        ref = p.grad.double()
+        err = float((got[k] - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+        assert err < 5e-4, (k, err)
+    err = float((got_img - img.grad.double()).abs().max() / img.grad.abs().max())
+    assert err < 5e-4, err
