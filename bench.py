@@ -442,40 +442,61 @@ def run_ours(args):
 
 
 def run_case(args):
-    """One kernel of the sweep on its own, a few launches: the command profiled with ncu.
-    Case names are the keys of the `kernels` table, e.g. fprop_f32_56x56x96."""
+    """One kernel on its own, a few launches: the command profiled with ncu.  Case names are
+    <op>_<f32|bf16>_<H>x<W>x<C>: the keys of the `kernels` table (fprop, dgrad, wgrad; stride 1,
+    K = 31), plus fprop2 / dgrad2 / wgrad2 (stride 2, H x W is the input size), ln (channels-last
+    LayerNorm), pw (stem projection from a 3-channel image to C channels) and tr (NHWC -> NCHW
+    transpose)."""
     import torch
 
     import oriented1d_b200 as o1d
 
     op, tag, shape = args.case.split("_")
-    hw, _, C = (int(v) for v in shape.split("x"))
+    H, W, C = (int(v) for v in shape.split("x"))
     dtype = torch.float32 if tag == "f32" else torch.bfloat16
+    es = 4 if dtype == torch.float32 else 2
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     g = torch.Generator(device="cpu").manual_seed(0)
     n = args.batch
-    plan = o1d.Plan(round_robin_angles(C) if args.angles == "rr" else block_angles(C), K)
-    w = (0.02 * torch.randn((C, 1, 1, K), generator=g)).to(dev)
-    sets = [(torch.randn((n, hw, hw, C), generator=g).to(dev).to(dtype),
-             torch.randn((n, hw, hw, C), generator=g).to(dev).to(dtype)) for _ in range(2)]
+    stride = 2 if op.endswith("2") else 1
+    P, Q = -(-H // stride), -(-W // stride)
+    if op == "pw":
+        sets = [(torch.randn((n, 3, H, W), generator=g).to(dev).to(dtype), None) for _ in range(2)]
+        w = torch.randn((C, 3), generator=g).to(dev)
+        bias = torch.randn((C,), generator=g).to(dev)
+        alg = n * H * W * (3 + C) * es
+    else:
+        plan = o1d.Plan(round_robin_angles(C) if args.angles == "rr" else block_angles(C), K)
+        w = (0.02 * torch.randn((C, 1, 1, K), generator=g)).to(dev)
+        bias = torch.randn((C,), generator=g).to(dev)
+        sets = [(torch.randn((n, H, W, C), generator=g).to(dev).to(dtype),
+                 torch.randn((n, P, Q, C), generator=g).to(dev).to(dtype)) for _ in range(2)]
+        alg = (n * H * W * C + n * P * Q * C) * es if op not in ("ln", "tr") else 2 * n * H * W * C * es
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     times = []
     for i in range(args.reps):
         x, dy = sets[i % 2]
         e0.record()
-        if op == "fprop":
-            o1d.fprop(x, w, None, plan, 1, True)
-        elif op == "dgrad":
-            o1d.dgrad(dy, w, plan, hw, hw, 1, True)
+        if op in ("fprop", "fprop2"):
+            o1d.fprop(x, w, None, plan, stride, True)
+        elif op in ("dgrad", "dgrad2"):
+            o1d.dgrad(dy, w, plan, H, W, stride, True)
+        elif op in ("wgrad", "wgrad2"):
+            o1d.wgrad(dy, x, plan, stride, True, True)
+        elif op == "ln":
+            o1d.ops.layer_norm_cl(x, bias, bias, 1e-6, False)
+        elif op == "pw":
+            o1d.ops.pointwise_in(x, w, bias)
+        elif op == "tr":
+            o1d.ops.nhwc_to_nchw(x)
         else:
-            o1d.wgrad(dy, x, plan, 1, True, True)
+            raise SystemExit("unknown case " + args.case)
         e1.record()
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1) * 1e3)
-    es = 4 if dtype == torch.float32 else 2
-    print(json.dumps({"case": args.case, "batch": n, "us": times, "alg_bytes": algorithmic_bytes(hw, C, es, n),
+    print(json.dumps({"case": args.case, "batch": n, "us": times, "alg_bytes": alg,
                       "device_status": o1d.ops.device_status()}))
 
 

@@ -15,7 +15,12 @@ import types
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-REF = os.environ.get("O1D_REFERENCE_ROOT", "/root/reference")
+sys.path.insert(0, ROOT)
+from oracle.build import reference_root  # noqa: E402
+
+REF = reference_root()
+if REF is None:
+    raise SystemExit("no reference checkout (set O1D_REFERENCE_ROOT)")
 sys.path.insert(0, ROOT)
 
 import oriented1d_b200  # noqa: E402
