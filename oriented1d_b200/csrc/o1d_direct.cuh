@@ -26,7 +26,8 @@
 
 namespace o1d {
 
-constexpr int kDirectThreads = 256;
+constexpr int kDirectThreads = 256;      // CTA size when two CTAs share an SM
+constexpr int kDirectThreadsMax = 512;   // CTA size when the tiles leave room for one CTA per SM only
 
 struct DirectParams {
     int N, H, W, C, K, stride, P, Q;
@@ -83,10 +84,10 @@ template <typename T, int IMM> __device__ __forceinline__ float ld_smem(uint32_t
 // (PLW = 32/CCs pixel lanes); a thread's NPX pixels are PLW apart, so their tile addresses
 // differ by the compile-time constant 32*sizeof(T)*STRIDE bytes and share one address add per
 // tap, while the lanes of every single load still cover 32 different banks.
-// MULTI: the launch holds several chunk ranges (parameters are then indexed by range at run
-// time, which costs registers; such launches use large tiles and one CTA per SM anyway).
+// MULTI: the launch holds several chunk ranges (parameters are then indexed by range at run time).
+// The CTA has 256 threads when two CTAs fit an SM and 512 when the tiles only leave room for one.
 template <typename T, int KT, int NPX, int STRIDE, bool MULTI>
-__global__ void __launch_bounds__(kDirectThreads, MULTI ? 1 : 2)
+__global__ void __launch_bounds__(kDirectThreadsMax, 1)
 direct_fprop_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMaps maps, const float *__restrict__ wgt,
                          const float *__restrict__ bias, const uint16_t *__restrict__ cls,
                          const int8_t *__restrict__ taps, T *__restrict__ y) {
@@ -102,7 +103,7 @@ direct_fprop_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMap
 
     const int tid = threadIdx.x;
     const int CCs = p.CCs;
-    const int lane = tid & 31, warp = tid >> 5;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (int)blockDim.x >> 5;
     const int cl = lane % CCs;                // channel within the chunk
     const int pl = lane / CCs;                // pixel lane within the warp
     const int PLW = 32 / CCs;                 // pixel lanes per warp
@@ -172,7 +173,7 @@ direct_fprop_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMap
         const int b = it & 1;
         if (!failed && !mbar_wait(&full[b], (it >> 1) & 1)) failed = true;
         const uint32_t tile_b = smem_u32(smem_raw) + b * p.buf_stride;    // shared address of the buffer
-        for (int u = warp; u < units; u += kDirectThreads / 32) {
+        for (int u = warp; u < units; u += nwarps) {
             const int img = p.div_thsq.div(u), r = u - img * (p.Th * p.segs_q);
             const int pr = p.div_sq.div(r), sq = r - pr * p.segs_q;
             const int pc0 = sq * (PLW * NPX) + pl;
@@ -212,7 +213,7 @@ constexpr int kDirectPartialStride = 32;   // floats per channel in a partial: u
 // direct_wgrad_final_kernel adds the partials of a chunk's CTAs in CTA order.  No atomics:
 // bit-reproducible.  (Reference: models/dwoconv1d/kernels/kernels.h:402-518, 31 atomicAdd per block.)
 template <typename T, int KT, int NPX, int STRIDE, bool MULTI>
-__global__ void __launch_bounds__(kDirectThreads, MULTI ? 1 : 2)
+__global__ void __launch_bounds__(kDirectThreadsMax, 1)
 direct_wgrad_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMaps maps,
                          const __grid_constant__ DirectMaps dym,
                          const uint16_t *__restrict__ cls, const int8_t *__restrict__ taps,
@@ -227,7 +228,7 @@ direct_wgrad_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMap
 
     const int tid = threadIdx.x;
     const int CCs = p.CCs;
-    const int lane = tid & 31, warp = tid >> 5;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (int)blockDim.x >> 5;
     const int cl = lane % CCs, pl = lane / CCs;
     const int PLW = 32 / CCs;
     constexpr int DELTA = 32 * (int)sizeof(T) * STRIDE;
@@ -264,7 +265,7 @@ direct_wgrad_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMap
     // The slack behind each input tile is read (times a zero dy) by the overrun pixels of the
     // last row segment: it must hold finite numbers.  TMA never writes there.
     for (int b = 0; b < 2; b++)
-        for (int i = p.tile_bytes / 4 + tid; i < p.tile_stride / 4; i += kDirectThreads)
+        for (int i = p.tile_bytes / 4 + tid; i < p.tile_stride / 4; i += (int)blockDim.x)
             reinterpret_cast<uint32_t *>(smem_raw + (size_t)b * p.buf_stride)[i] = 0u;
     __syncthreads();
 
@@ -298,7 +299,7 @@ direct_wgrad_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMap
         if (!failed && !mbar_wait(&full[b], (it >> 1) & 1)) failed = true;
         const uint32_t tile_b = smem_u32(smem_raw) + b * p.buf_stride;
         const uint32_t dy_b = tile_b + p.tile_stride;
-        for (int u = warp; u < units; u += kDirectThreads / 32) {
+        for (int u = warp; u < units; u += nwarps) {
             const int img = p.div_thsq.div(u), r = u - img * (p.Th * p.segs_q);
             const int pr = p.div_sq.div(r), sq = r - pr * p.segs_q;
             const int pc0 = sq * (PLW * NPX) + pl;
@@ -334,11 +335,11 @@ direct_wgrad_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMap
         r[kDirectPartialStride - 1] = acc_db;
     }
     __syncthreads();
-    for (int e = tid; e < CCs * kDirectPartialStride; e += kDirectThreads) {
+    for (int e = tid; e < CCs * kDirectPartialStride; e += (int)blockDim.x) {
         const int k = e % kDirectPartialStride;
         float sum = 0.f;
         if (k < KT || k == kDirectPartialStride - 1)
-            for (int w = 0; w < kDirectThreads / 32; w++) sum += red[w * CCs * kDirectPartialStride + e];
+            for (int w = 0; w < nwarps; w++) sum += red[w * CCs * kDirectPartialStride + e];
         partial[p.partial_off + (size_t)bid * CCs * kDirectPartialStride + e] = sum;
     }
 }
@@ -390,7 +391,7 @@ constexpr int kDgrad2Slots = 16;   // merged taps per parity class (a line of 31
 // Hx, Wx those of dx.  (Reference: models/dwoconv1d/kernels/kernels.h:312-399 tests `%` and `/`
 // by the stride for every tap of every pixel.)
 template <typename T, int NPX, bool MULTI>
-__global__ void __launch_bounds__(kDirectThreads, MULTI ? 1 : 2)
+__global__ void __launch_bounds__(kDirectThreadsMax, 1)
 direct_dgrad2_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMaps maps, const float *__restrict__ wgt,
                           const uint16_t *__restrict__ cls, const int8_t *__restrict__ taps,
                           T *__restrict__ dx, int Hx, int Wx) {
@@ -407,7 +408,7 @@ direct_dgrad2_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMa
 
     const int tid = threadIdx.x;
     const int CCs = p.CCs;
-    const int lane = tid & 31, warp = tid >> 5;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (int)blockDim.x >> 5;
     const int cl = lane % CCs, pl = lane / CCs;
     const int PLW = 32 / CCs;
     constexpr int DELTA = 32 * (int)sizeof(T);
@@ -486,7 +487,7 @@ direct_dgrad2_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMa
             for (int k = 0; k < KS; k++) { w[k] = s_w[(q * CCs + cl) * KS + k]; off[k] = s_off[(q * CCs + cl) * KS + k]; }
             auto pass = [&](auto nslots) {
                 constexpr int NS = decltype(nslots)::value;
-                for (int u = warp; u < units; u += kDirectThreads / 32) {
+                for (int u = warp; u < units; u += nwarps) {
                     const int img = p.div_thsq.div(u), r = u - img * (p.Th * p.segs_q);
                     const int pr = p.div_sq.div(r), sq = r - pr * p.segs_q;
                     const int pc0 = sq * (PLW * NPX) + pl;

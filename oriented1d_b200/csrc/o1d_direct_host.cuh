@@ -67,7 +67,7 @@ inline bool direct_configure_tiles(int N, int H, int W, int C, int K, int stride
     p.off_taps_bytes = 2 * p.buf_stride;
     p.off_bar_bytes = p.off_taps_bytes + tap_bytes;
     int smem = p.off_bar_bytes + 16;
-    const int red_bytes = (kDirectThreads / 32) * CCs * kDirectPartialStride * 4;   // reuses the tile buffers
+    const int red_bytes = (kDirectThreadsMax / 32) * CCs * kDirectPartialStride * 4;   // reuses the tile buffers
     if (wgrad && smem < red_bytes) smem = red_bytes;
     if (smem > smem_limit) return false;
     int ctas = (228 * 1024) / (smem + 1024);
@@ -213,7 +213,7 @@ enum : int { DIRECT_FPROP = 0, DIRECT_WGRAD = 1, DIRECT_DGRAD2 = 2 };
 struct DirectLaunchSet {
     int n;
     DirectConfig cfg[kMaxChunkRanges];
-    int kt, npx, smem_bytes, grid;
+    int kt, npx, smem_bytes, grid, threads;
     bool whole_image;
     size_t partial_floats;       // weight gradient: floats of partial sums over all ranges
 };
@@ -262,13 +262,17 @@ inline bool direct_plan_launches(const PlanHeader &ph, const void *plan_host, in
         DirectConfig &c = out->cfg[i];
         if (mode != DIRECT_DGRAD2) {     // the tap tables are sized by the common KT
             c.p.off_bar_bytes = c.p.off_taps_bytes + c.p.CCs * out->kt * 8;
-            const int red_bytes = (kDirectThreads / 32) * c.p.CCs * kDirectPartialStride * 4;
+            const int red_bytes = (kDirectThreadsMax / 32) * c.p.CCs * kDirectPartialStride * 4;
             c.smem_bytes = c.p.off_bar_bytes + 16;
             if (mode == DIRECT_WGRAD && c.smem_bytes < red_bytes) c.smem_bytes = red_bytes;
         }
         if (c.smem_bytes > out->smem_bytes) out->smem_bytes = c.smem_bytes;
     }
     if (out->smem_bytes > smem_limit) return false;
+    // one CTA per SM (large tiles): give it twice the warps
+    // (measured: weight gradient 28x28x192 121 -> 115 us; the stride-2 input gradient loses, 449 -> 541 us)
+    out->threads = ((228 * 1024) / (out->smem_bytes + 1024) >= 2 || mode == DIRECT_DGRAD2) ? kDirectThreads
+                                                                                          : kDirectThreadsMax;
     for (int i = 0; i < out->n; i++) {
         DirectConfig &c = out->cfg[i];
         DirectParams &p = c.p;
@@ -309,7 +313,7 @@ cudaError_t launch_direct_one(const DirectLaunchSet &ls, const DirectMulti &mp, 
                          : direct_fprop_nhwc_kernel<T, KT, NPX, STRIDE, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ls.smem_bytes);
     if (e != cudaSuccess) return e;
-    kern<<<ls.grid, kDirectThreads, ls.smem_bytes, st>>>(mp, maps, w, bias, pv.cls, pv.taps, (T *)y);
+    kern<<<ls.grid, ls.threads, ls.smem_bytes, st>>>(mp, maps, w, bias, pv.cls, pv.taps, (T *)y);
     return cudaGetLastError();
 }
 template <typename T, int KT, int NPX, int STRIDE>
@@ -319,7 +323,7 @@ cudaError_t launch_direct_wgrad_one(const DirectLaunchSet &ls, const DirectMulti
                          : direct_wgrad_nhwc_kernel<T, KT, NPX, STRIDE, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ls.smem_bytes);
     if (e != cudaSuccess) return e;
-    kern<<<ls.grid, kDirectThreads, ls.smem_bytes, st>>>(mp, maps, dym, pv.cls, pv.taps, partial);
+    kern<<<ls.grid, ls.threads, ls.smem_bytes, st>>>(mp, maps, dym, pv.cls, pv.taps, partial);
     return cudaGetLastError();
 }
 
@@ -365,7 +369,7 @@ cudaError_t launch_direct_dgrad2_one(const DirectLaunchSet &ls, const DirectMult
     auto kern = ls.n > 1 ? direct_dgrad2_nhwc_kernel<T, NPX, true> : direct_dgrad2_nhwc_kernel<T, NPX, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ls.smem_bytes);
     if (e != cudaSuccess) return e;
-    kern<<<ls.grid, kDirectThreads, ls.smem_bytes, st>>>(mp, maps, w, pv.cls, pv.taps, (T *)dx, Hx, Wx);
+    kern<<<ls.grid, ls.threads, ls.smem_bytes, st>>>(mp, maps, w, pv.cls, pv.taps, (T *)dx, Hx, Wx);
     return cudaGetLastError();
 }
 template <typename T>
