@@ -670,8 +670,9 @@ int dispatch_ln(const void *x, const float *gamma, const float *beta, void *y, i
                 int gelu, cudaStream_t st, const DeviceInfo &d) {
     const int nvec = C / (16 / (int)sizeof(T));
     if (nvec <= 8) return launch_ln<T, 8, 1>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
-    if (nvec <= 16) return launch_ln<T, 16, 1>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
-    if (nvec <= 32) return launch_ln<T, 32, 1>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
+    // two vectors per lane: fewer shuffle steps and more rows in flight per warp
+    if (nvec <= 16) return launch_ln<T, 8, 2>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
+    if (nvec <= 32) return launch_ln<T, 16, 2>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
     if (nvec <= 64) return launch_ln<T, 32, 2>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
     if (nvec <= 128) return launch_ln<T, 32, 4>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
     if (nvec <= 256) return launch_ln<T, 32, 8>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
@@ -701,8 +702,10 @@ int o1d_pointwise_in(const void *x, const float *w, const float *bias, void *y, 
         return O1D_ERR_INVALID;
     if (Cin > 4 || Cout % 8 != 0 || HW > 0x7fffffffLL || ((uintptr_t)y & 15)) return O1D_ERR_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
-    const long long npix = (long long)N * HW, total = npix * (Cout / 8);
-    const long long blocks = (total + kPointwiseThreads - 1) / kPointwiseThreads;
+    if (Cout / 8 > kPointwiseThreads) return O1D_ERR_UNSUPPORTED;
+    const long long npix = (long long)N * HW;
+    const long long per_block = (long long)(kPointwiseThreads / (Cout / 8)) * kPointwisePasses;
+    const long long blocks = (npix + per_block - 1) / per_block;
     if (blocks > 0x7fffffffLL) return O1D_ERR_UNSUPPORTED;
 #define O1D_PW(T, CIN)                                                                                     \
     pointwise_in_kernel<T, CIN><<<(unsigned)blocks, kPointwiseThreads, 0, st>>>((const T *)x, w, bias, (T *)y, npix, \
