@@ -181,11 +181,13 @@ class ConvNeXt1D(nn.Module):
 
     def __init__(self, in_chans=3, num_classes=1000, depths=(3, 3, 9, 3), dims=(96, 192, 384, 768),
                  drop_path_rate=0.0, layer_scale_init_value=1e-6, head_init_scale=1.0, variant="1d", N=8,
-                 stem_dim1=64, arbitrary_size=False):
+                 stem_dim1=64, arbitrary_size=False, block_kernels=None, stem_kernel=None):
         super().__init__()
         assert variant in ("1d", "1dpp")
         Block = Block1D if variant == "1d" else Block1DPP
-        self.downsample_layers = nn.ModuleList([Stem1D(in_chans, stem_dim1, dims[0], STEM_KERNEL[variant], 1,
+        block_kernels = BLOCK_KERNELS[variant] if block_kernels is None else block_kernels
+        stem_kernel = STEM_KERNEL[variant] if stem_kernel is None else stem_kernel
+        self.downsample_layers = nn.ModuleList([Stem1D(in_chans, stem_dim1, dims[0], stem_kernel, 1,
                                                        arbitrary_size)])
         for i in range(3):
             self.downsample_layers.append(Downsample(dims[i], dims[i + 1]))
@@ -194,7 +196,7 @@ class ConvNeXt1D(nn.Module):
         cur = 0
         for i in range(4):
             self.stages.append(nn.Sequential(*[
-                Block(dims[i], kernel_sizes=BLOCK_KERNELS[variant][i], N=N, drop_path=rates[cur + j],
+                Block(dims[i], kernel_sizes=block_kernels[i], N=N, drop_path=rates[cur + j],
                       layer_scale_init_value=layer_scale_init_value,
                       layer_offset=layer_wise_rotation_offset(j, 1), arbitrary_size=arbitrary_size)
                 for j in range(depths[i])]))
