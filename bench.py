@@ -209,7 +209,8 @@ def run_ours(args):
     layers32 = [Layer(hw, C, torch.float32) for hw, C in STAGES]
     launches = {"n": 0}
 
-    def step(layers):
+    def compute(layers):
+        """The 12 kernel calls of one step; returns the weight/bias gradients as one flat buffer."""
         grads = []
         for L in layers:
             x, dy = L.next()
@@ -219,9 +220,33 @@ def run_ours(args):
             grads += [dw.reshape(-1), db]
             launches["n"] += o1d.ops.KERNELS_PER_CALL["fprop"] + o1d.ops.KERNELS_PER_CALL["dgrad"] + \
                 o1d.ops.KERNELS_PER_CALL["wgrad"]
+        return torch.cat(grads) if world > 1 else None
+
+    def step(layers):
+        flat = compute(layers)
         if world > 1:   # data-parallel training sums the weight gradients across ranks
-            flat = torch.cat(grads)
             dist.all_reduce(flat)
+
+    def graphed_multi_gpu_step(layers, cycle):
+        """world > 1: one CUDA graph per step of the input rotation (kernels only); the NCCL
+        all-reduce of that step's gradient buffer follows each replay, outside the graph."""
+        for _ in range(3):
+            step(layers)
+        torch.cuda.synchronize()
+        graphs = []
+        for _ in range(cycle):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                flat = compute(layers)
+            graphs.append((g, flat))
+        state = {"i": 0}
+
+        def run():
+            g, flat = graphs[state["i"] % cycle]
+            state["i"] += 1
+            g.replay()
+            dist.all_reduce(flat)
+        return run
 
     def timed(fn, steps, warmup, graph_cycle=0, all_ranks=True):
         """Device time of `steps` calls of fn (CUDA events on the launching stream, barrier and
@@ -268,7 +293,10 @@ def run_ours(args):
         launches["n"] = 0
         step(layers32)
         per_step = launches["n"]
-        ms = timed(lambda: step(layers32), args.steps, warm, graph_cycle=cycle)
+        if world > 1 and not args.no_graph:
+            ms = timed(graphed_multi_gpu_step(layers32, max(L.nsets for L in layers32)), args.steps, warm)
+        else:
+            ms = timed(lambda: step(layers32), args.steps, warm, graph_cycle=cycle)
         n_launch = per_step * args.steps
         time.sleep(0.25)
     clocks = clk.summary()
@@ -428,7 +456,8 @@ def run_ours(args):
             "config": {"workload": "stage-sweep: (56,96),(28,192),(14,384),(7,768) x batch 128 per GPU, K=31, "
                                    "stride 1, NHWC, 8 orientations round-robin; fprop+dgrad+wgrad per shape",
                        "l2": "inputs rotate over sets totalling >4x L2, so every launch reads from HBM",
-                       "launch": "eager" if (args.no_graph or world > 1) else "CUDA graph of one full input rotation, replayed",
+                       "launch": ("eager" if args.no_graph else "CUDA graph of one full input rotation, replayed" if world == 1
+                                  else "one CUDA graph per step (kernels only), NCCL all-reduce after each replay"),
                        "parallelism": f"dp{world} (batch-sharded; weight-gradient all-reduce when >1)"},
             "roofline": roof, "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
