@@ -5,6 +5,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "o1d_tiled.cuh"
 
 namespace o1d {
@@ -67,10 +69,12 @@ inline int skew_stride(int v, int CC, int VE) {
 }
 inline int make_odd(int v) { return v | 1; }
 
-// Picks R, BR (band rows), CC (chunk channels) and the stage count; returns false when the
-// tiled kernels do not apply and the general kernels must be used.
-inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, int H, int W, int C, int K,
-                            int stride, int layout, int esize, int smem_limit, int sms, int op, TiledConfig *out) {
+// Picks BR (band rows), CC (chunk channels), the CTA size and the stage count for given line
+// pitches (0 = the default, smallest odd pitch); returns false when the tiled kernels do not apply
+// and the general kernels must be used.
+inline bool tiled_configure_pitch(const PlanHeader &ph, const void *plan_host, int N, int H, int W, int C, int K,
+                                  int stride, int layout, int esize, int smem_limit, int sms, int op, int want_pn,
+                                  int want_pt, TiledConfig *out) {
     if (stride != 1 || layout != O1D_NHWC || K > kMaxTaps || !ph.all_canon || ph.comps_off == 0) return false;
     if (H > 256 || W > 256 || (C * esize) % 16 != 0) return false;
     int R = 0;
@@ -80,7 +84,7 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
     const int VE = 16 / esize;
     const KindComp *comps = reinterpret_cast<const KindComp *>(static_cast<const char *>(plan_host) + ph.comps_off);
     const int G = (R == 8) ? 17 : 16;
-    const int pitch_n = make_odd(W + G), pitch_t = make_odd(H + G);
+    const int pitch_n = want_pn ? want_pn : make_odd(W + G), pitch_t = want_pt ? want_pt : make_odd(H + G);
     // R == 7 kernels surround every plane with kHaloLines zero lines (shared between neighbouring
     // planes) instead of bounds-checking lines; see tiled_nhwc_kernel.
     const int halo = (R == 7) ? kHaloLines : 0;
@@ -214,6 +218,136 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
         *out = best;
     }
     return found;
+}
+
+// Shared-memory wavefronts of the register-window loads of one band for one channel chunk: every
+// load instruction of a warp costs as many wavefronts as its worst bank is hit with different
+// addresses, and all window loads of a thread are at constant offsets from its segment origin,
+// so the degree of a warp follows from the origins alone.  Mirrors the thread -> (kind, channel,
+// segment) assignment and the origin arithmetic of tiled_nhwc_kernel.
+inline long tiled_window_wavefronts(const int8_t *ids, const TiledParams &p, int NT) {
+    const int CC = p.CC, R = p.R, BR = p.BR, W = p.W, H = p.H;
+    int sorted[kMaxCC], cnt[3] = {0, 0, 0}, n = 0;
+    for (int kd = 0; kd < 3; kd++)
+        for (int i = 0; i < CC; i++)
+            if (canon_kind(ids[i]) == kd) { sorted[n++] = i; cnt[kd]++; }
+    const int wd = W + R - 1;
+    const int slotsA = round32(cnt[0] * p.nseg_line), slotsS = round32(cnt[1] * p.nseg_line);
+    const int loads[3] = {R + 30, 11 * (R + 2), R + 20};      // window loads per segment: axis, slant, diagonal
+    long total = 0;
+    for (int w0 = 0; w0 < NT; w0 += 32) {
+        int origin[32], m = 0, kind = -1;
+        for (int tid = w0; tid < w0 + 32; tid++) {
+            int idx = tid, kd, ch, seg;
+            if (idx < slotsA) {
+                const int j = idx / p.nseg_line;
+                if (j >= cnt[0]) continue;
+                kd = KIND_AXIS; ch = sorted[j]; seg = idx - j * p.nseg_line;
+            } else if ((idx -= slotsA) < slotsS) {
+                const int j = idx / p.nseg_line;
+                if (j >= cnt[1]) continue;
+                kd = KIND_SLANT; ch = sorted[cnt[0] + j]; seg = idx - j * p.nseg_line;
+            } else {
+                idx -= slotsS;
+                const int j = idx / p.nseg_diag;
+                if (j >= cnt[2]) continue;
+                kd = KIND_DIAG; ch = sorted[cnt[0] + cnt[1] + j]; seg = idx - j * p.nseg_diag;
+            }
+            const int mode = canon_mode(ids[ch]);
+            const int pbase = p.plane_base + ch * p.plane_stride;
+            int a;
+            if (kd == KIND_DIAG) {
+                const int sub = seg / wd, qi = seg - sub * wd;
+                a = pbase + (sub * R + R - 1) * p.pitch_n + qi - (R - 1);
+            } else if (!(mode & MODE_T)) {
+                const int sg = seg / BR, rl = seg - sg * BR;
+                a = pbase + rl * p.pitch_n + sg * R;
+            } else {
+                const int sub = seg / W;
+                int l = seg - sub * W + 5;
+                if (l >= W) l -= W;
+                a = pbase + l * p.pitch_t + ((mode & MODE_FP) ? H - BR : 0) + sub * R;
+            }
+            origin[m++] = a;
+            kind = kd;
+        }
+        if (!m) continue;
+        int degree = 1;
+        for (int b = 0; b < 32; b++) {
+            int distinct = 0, seen[32];
+            for (int i = 0; i < m; i++) {
+                if (((origin[i] % 32) + 32) % 32 != b) continue;
+                bool dup = false;
+                for (int j = 0; j < distinct; j++) dup = dup || seen[j] == origin[i];
+                if (!dup) seen[distinct++] = origin[i];
+            }
+            if (distinct > degree) degree = distinct;
+        }
+        total += (long)degree * loads[kind];
+    }
+    return total;
+}
+
+// With segments of 7 the 7*k segments of a channel never fill whole warps, and with the default
+// pitches most warps straddle two line groups whose origins collide (28x28: 2.0 to 2.6
+// wavefronts per window load).  Shared memory has room at these sizes, so the line pitches are
+// searched for the fewest window-load wavefronts on a few sample chunks (28x28x192: 107 -> 97 us).
+// The result is cached per problem geometry; the search costs about 0.2 ms once.
+inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, int H, int W, int C, int K,
+                            int stride, int layout, int esize, int smem_limit, int sms, int op, TiledConfig *out) {
+    TiledConfig base;
+    if (!tiled_configure_pitch(ph, plan_host, N, H, W, C, K, stride, layout, esize, smem_limit, sms, op, 0, 0, &base))
+        return false;
+    *out = base;
+    if (base.p.R != 7 || ph.chan_off == 0) return true;
+    const int8_t *chan = reinterpret_cast<const int8_t *>(static_cast<const char *>(plan_host) + ph.chan_off);
+    const int CC = base.p.CC, nchunks = C / CC;
+    int sample[4], ns = 0;
+    for (int i = 0; i < 4; i++) {
+        const int ch = (int)((long long)i * (nchunks - 1) / 3);
+        if (ns == 0 || sample[ns - 1] != ch) sample[ns++] = ch;
+    }
+    uint64_t sig = 1469598103934665603ull;                     // FNV-1a over the sampled chunks' line ids
+    for (int i = 0; i < ns; i++)
+        for (int j = 0; j < CC; j++) sig = (sig ^ (uint8_t)chan[sample[i] * CC + j]) * 1099511628211ull;
+    struct Entry { int H, W, CC, BR, NT, esize, op; uint64_t sig; int pn, pt; };
+    static Entry cache[64];
+    static int cached = 0;
+    static std::mutex mu;
+    int pn = 0, pt = 0;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (int i = 0; i < cached; i++) {
+            const Entry &e = cache[i];
+            if (e.H == H && e.W == W && e.CC == CC && e.BR == base.p.BR && e.NT == base.threads && e.esize == esize &&
+                e.op == op && e.sig == sig) { pn = e.pn; pt = e.pt; }
+        }
+    }
+    if (!pn) {
+        long best = -1;
+        for (int dn = 0; dn < 16; dn++)
+            for (int dt = 0; dt < 16; dt += 2) {                // transposed planes keep an odd pitch
+                TiledConfig c;
+                const int cn = base.p.pitch_n + dn, ct = base.p.pitch_t + dt;
+                if (!tiled_configure_pitch(ph, plan_host, N, H, W, C, K, stride, layout, esize, smem_limit, sms, op, cn,
+                                           ct, &c))
+                    continue;
+                if (c.p.CC != CC || c.p.BR != base.p.BR || c.threads != base.threads || c.ctas_per_sm < base.ctas_per_sm)
+                    continue;
+                long cost = 0;
+                for (int i = 0; i < ns; i++) cost += tiled_window_wavefronts(chan + sample[i] * CC, c.p, c.threads);
+                if (best < 0 || cost < best) { best = cost; pn = cn; pt = ct; }
+            }
+        if (!pn) { pn = base.p.pitch_n; pt = base.p.pitch_t; }
+        std::lock_guard<std::mutex> lock(mu);
+        if (cached < 64) cache[cached++] = Entry{H, W, CC, base.p.BR, base.threads, esize, op, sig, pn, pt};
+    }
+    if (pn == base.p.pitch_n && pt == base.p.pitch_t) return true;
+    TiledConfig tuned;
+    if (tiled_configure_pitch(ph, plan_host, N, H, W, C, K, stride, layout, esize, smem_limit, sms, op, pn, pt, &tuned) &&
+        tuned.p.CC == CC && tuned.ctas_per_sm >= base.ctas_per_sm)
+        *out = tuned;
+    return true;
 }
 
 // 4-D tensor map over an NHWC tensor: dims (C, W, H, N), box (CC, W, BR, 1).
