@@ -1,7 +1,8 @@
-// "Direct" kernels: NHWC forward (any stride) and stride-1 input gradient for the cases where
-// a zero-haloed input tile of a 32-byte channel chunk fits shared memory: small feature maps
-// as whole images (several images per tile when they are tiny), large or strided ones (stems,
-// dense-prediction sizes) as row/column tiles.  Any per-channel angle, any K <= 31.
+// "Direct" kernels: NHWC forward (stride 1 or 2) and stride-1 input gradient, weight gradient
+// (stride 1 or 2) and stride-2 input gradient, all on zero-haloed input tiles of a 32-byte
+// channel chunk in shared memory: small feature maps as whole images (several images per tile
+// when they are tiny), large or strided ones (stems, dense-prediction sizes) as row/column
+// tiles.  Any per-channel angle, any K <= 31.
 //
 //   * TMA (cp.async.bulk.tensor.4d, no multicast) brings a box CCs x TWp x THp x NI of the NHWC
 //     tensor into one of two tile buffers; coordinates outside the image are zero-filled by the
@@ -18,7 +19,8 @@
 //
 // Compared with the tiled kernels (o1d_tiled.cuh) this spends one shared-memory load per FMA
 // instead of one per 3-7, but has no restage / band-buffer passes and almost no barriers,
-// which wins on small maps; at 56x56 the halo'd tile no longer fits and the tiled kernels run.
+// which wins on tiny maps, and they take every shape the tiled kernels do not (strides, sizes
+// that are not multiples of 7 or 8, arbitrary angles, layers whose chunks hold a single line kind).
 #pragma once
 
 #include "o1d_common.cuh"
