@@ -578,13 +578,12 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
 
         // band buffer <-> global: per-thread constants (index walk as in restage)
         int oa[VE], ostep[VE];
-        float bs[VE];
+        const float bias_v = (OP == OP_FPROP) ? bias_s[ch] : 0.f;      // accumulators start at the bias
 #pragma unroll
         for (int j = 0; j < VE; j++) {
             const int4 m = map_out[g_vec * VE + j];
             oa[j] = m.x * rl_first + m.y * col_first + m.z;
             ostep[j] = m.x * p.TR;
-            bs[j] = bias_s[g_vec * VE + j];
         }
         T *gbase = io + ((size_t)n * H * W) * C + c0 + g_vec * VE;
 
@@ -653,7 +652,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 if constexpr (OP == OP_FPROP) {
                     float acc[R];
 #pragma unroll
-                    for (int o = 0; o < R; o++) acc[o] = 0.f;
+                    for (int o = 0; o < R; o++) acc[o] = bias_v;
                     seg_line<OP_FPROP, KIND_AXIS, JH, R, false>(sm, at, pitch, nlines, p.off_zero, line, w, acc);
 #pragma unroll
                     for (int o = 0; o < R; o++) ob[o] = acc[o];
@@ -667,7 +666,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 if constexpr (OP == OP_FPROP) {
                     float acc[R];
 #pragma unroll
-                    for (int o = 0; o < R; o++) acc[o] = 0.f;
+                    for (int o = 0; o < R; o++) acc[o] = bias_v;
                     if (inside) seg_line<OP_FPROP, KIND_SLANT, JH, R, false>(sm, at, pitch, nlines, p.off_zero, line, w, acc);
                     else seg_line<OP_FPROP, KIND_SLANT, JH, R, true>(sm, at, pitch, nlines, p.off_zero, line, w, acc);
 #pragma unroll
@@ -684,7 +683,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 if constexpr (OP == OP_FPROP) {
                     float acc[R];
 #pragma unroll
-                    for (int o = 0; o < R; o++) acc[o] = 0.f;
+                    for (int o = 0; o < R; o++) acc[o] = bias_v;
                     if (inside) seg_diag<OP_FPROP, JH, R, false>(sm, at, pitch, nlines, p.off_zero, line, w, acc);
                     else seg_diag<OP_FPROP, JH, R, true>(sm, at, pitch, nlines, p.off_zero, line, w, acc);
 #pragma unroll
@@ -717,7 +716,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 for (int pix = mover ? pix_first : band_pixels; pix < band_pixels; pix += pix_step) {
                     float f[VE];
 #pragma unroll
-                    for (int j = 0; j < VE; j++) { f[j] = src[idx[j]] + bs[j]; idx[j] += ostep[j]; }
+                    for (int j = 0; j < VE; j++) { f[j] = src[idx[j]]; idx[j] += ostep[j]; }
                     *reinterpret_cast<uint4 *>(gdst + (size_t)pix * C) = Vec16<T>::pack(f);
                 }
             }
