@@ -382,7 +382,7 @@ int o1d_uses_tiled(const void *plan_host, int N, int H, int W, int C, int K, int
     if (tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, 232448, 148, OP_FPROP, &cfg)) return 1;
     DirectConfig dcfg;
     const ChunkRange all{0, C / (32 / esize), ph.max_dh, ph.max_dw};
-    return direct_configure(ph, plan_host, all, N, H, W, C, K, stride, layout, esize, 232448, 148, false, &dcfg) ? 1 : 0;
+    return direct_configure(ph, plan_host, all, N, H, W, C, K, stride, layout, esize, 232448, 148, false, false, &dcfg) ? 1 : 0;
 }
 
 int o1d_offsets(const float *theta_host, int C, int K, int8_t *dh, int8_t *dw) {

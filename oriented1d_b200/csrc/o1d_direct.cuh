@@ -87,8 +87,11 @@ template <typename T, int IMM> __device__ __forceinline__ float ld_smem(uint32_t
 // differ by the compile-time constant 32*sizeof(T)*STRIDE bytes and share one address add per
 // tap, while the lanes of every single load still cover 32 different banks.
 // MULTI: the launch holds several chunk ranges (parameters are then indexed by range at run time).
+// PAIR (2-byte elements whose even/odd channel neighbours share their line): a thread owns two
+// adjacent channels, loads them as one 32-bit word (half the shared-memory wavefronts of two
+// 16-bit loads), widens both halves and runs two FMAs; a warp is then 4 pixels x 8 channel pairs.
 // The CTA has 256 threads when two CTAs fit an SM and 512 when the tiles only leave room for one.
-template <typename T, int KT, int NPX, int STRIDE, bool MULTI>
+template <typename T, int KT, int NPX, int STRIDE, bool MULTI, bool PAIR>
 __global__ void __launch_bounds__(kDirectThreadsMax, 1)
 direct_fprop_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMaps maps, const float *__restrict__ wgt,
                          const float *__restrict__ bias, const uint16_t *__restrict__ cls,
@@ -106,10 +109,13 @@ direct_fprop_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMap
     const int tid = threadIdx.x;
     const int CCs = p.CCs;
     const int lane = tid & 31, warp = tid >> 5, nwarps = (int)blockDim.x >> 5;
-    const int cl = lane % CCs;                // channel within the chunk
-    const int pl = lane / CCs;                // pixel lane within the warp
-    const int PLW = 32 / CCs;                 // pixel lanes per warp
-    constexpr int DELTA = 32 * (int)sizeof(T) * STRIDE;   // bytes between a thread's pixels
+    static_assert(!PAIR || sizeof(T) == 2, "channel pairs are for 2-byte elements");
+    constexpr int CPT = PAIR ? 2 : 1;         // channels per thread
+    const int CL = CCs / CPT;                 // channel lanes per pixel
+    const int cl = (lane % CL) * CPT;         // (first) channel of this thread within the chunk
+    const int pl = lane / CL;                 // pixel lane within the warp
+    const int PLW = 32 / CL;                  // pixel lanes per warp
+    constexpr int DELTA = 32 * (int)sizeof(T) * CPT * STRIDE;   // bytes between a thread's pixels (PLW pixels)
     const int groups = gsz / p.nchunks;        // CTAs per chunk
     const int chunk = p.chunk0 + bid % p.nchunks;
     const int first = bid / p.nchunks;
@@ -141,11 +147,15 @@ direct_fprop_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMap
         for (; n < KT; n++) { s_w[tid * KT + n] = 0.f; s_off[tid * KT + n] = 0; }
     }
     __syncthreads();
-    float w[KT];
+    float w[KT], w2[PAIR ? KT : 1];
     int off[KT];
 #pragma unroll
-    for (int k = 0; k < KT; k++) { w[k] = s_w[cl * KT + k]; off[k] = s_off[cl * KT + k]; }
+    for (int k = 0; k < KT; k++) {
+        w[k] = s_w[cl * KT + k]; off[k] = s_off[cl * KT + k];
+        if constexpr (PAIR) w2[k] = s_w[(cl + 1) * KT + k];      // same line, hence the same kept taps and offsets
+    }
     const float bv = bias ? __ldg(bias + c0 + cl) : 0.f;
+    const float bv2 = (PAIR && bias) ? __ldg(bias + c0 + cl + 1) : 0.f;
 
     auto tile_coords = [&](int it, int &n0, int &p0, int &q0) {
         const int t = first + it * groups;
@@ -182,19 +192,35 @@ direct_fprop_nhwc_kernel(const DirectMulti mp, const __grid_constant__ DirectMap
             const int n = n0 + img, pp = p0 + pr;
             if (n >= p.N || pp >= p.P) continue;
             const uint32_t base = tile_b + (img * img_elems + ((pr * STRIDE + p.hh) * p.TWp + pc0 * STRIDE + p.hw) * CCs + cl) * (int)sizeof(T);
-            float acc[NPX];
+            float acc[NPX], acc2[PAIR ? NPX : 1];
 #pragma unroll
-            for (int j = 0; j < NPX; j++) acc[j] = bv;
+            for (int j = 0; j < NPX; j++) { acc[j] = bv; if constexpr (PAIR) acc2[j] = bv2; }
 #pragma unroll
             for (int k = 0; k < KT; k++) {
                 const uint32_t a = base + off[k];
-                static_for<0, NPX>([&](auto j) { acc[j] = fmaf(w[k], ld_smem<T, j * DELTA>(a), acc[j]); });
+                static_for<0, NPX>([&](auto j) {
+                    if constexpr (PAIR) {
+                        uint32_t word;
+                        asm volatile("ld.shared.b32 %0, [%1+%2];" : "=r"(word) : "r"(a), "n"(j * DELTA));
+                        acc[j] = fmaf(w[k], __uint_as_float(word << 16), acc[j]);
+                        acc2[j] = fmaf(w2[k], __uint_as_float(word & 0xffff0000u), acc2[j]);
+                    } else {
+                        acc[j] = fmaf(w[k], ld_smem<T, j * DELTA>(a), acc[j]);
+                    }
+                });
             }
             T *yrow = y + (((size_t)n * p.P + pp) * p.Q + q0) * p.C + c0 + cl;
 #pragma unroll
             for (int j = 0; j < NPX; j++) {
                 const int pc = pc0 + PLW * j;
-                if (pc < p.Tq && q0 + pc < p.Q) st(yrow + (size_t)pc * p.C, acc[j]);
+                if (pc < p.Tq && q0 + pc < p.Q) {
+                    if constexpr (PAIR) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(acc[j], acc2[j]);
+                        *reinterpret_cast<__nv_bfloat162 *>(yrow + (size_t)pc * p.C) = h;
+                    } else {
+                        st(yrow + (size_t)pc * p.C, acc[j]);
+                    }
+                }
             }
         }
         __syncthreads();                                   // everyone is done with buffer b

@@ -18,7 +18,7 @@ struct DirectConfig {
 // wgrad: also reserve room for the dy tiles and the end-of-kernel reduction scratch.
 inline bool direct_configure_tiles(int N, int H, int W, int C, int K, int stride, int esize, int smem_limit, int sms,
                                    bool wgrad, int hh, int hw, int kt, int tap_bytes, const ChunkRange &rg,
-                                   DirectConfig *out) {
+                                   bool pair, DirectConfig *out) {
     const int CCs = 32 / esize;
     DirectParams p{};
     p.N = N; p.H = H; p.W = W; p.C = C; p.K = K; p.stride = stride;
@@ -61,7 +61,7 @@ inline bool direct_configure_tiles(int N, int H, int W, int C, int K, int stride
     p.tile_stride = ((p.tile_bytes + 127) & ~127) + 16 * stride * CCs * esize;
     p.dy_bytes = wgrad ? Th * Tq * CCs * esize * NI : 0;
     p.buf_stride = p.tile_stride + (wgrad ? ((p.dy_bytes + 127) & ~127) + 16 * CCs * esize : 0);
-    const int plw = 32 / CCs;
+    const int plw = pair ? 4 : 32 / CCs;      // pixel lanes per warp
     const int npx = (Tq >= 3 * plw) ? 4 : (Tq > plw ? 2 : 1);
     p.segs_q = ceil_div(Tq, plw * npx);
     p.off_taps_bytes = 2 * p.buf_stride;
@@ -125,7 +125,7 @@ inline int direct_chunk_ranges(const PlanHeader &ph, const void *plan_host, int 
 // Forward / weight gradient: halo = the lines' reach clipped to the image, KT = longest clipped tap list.
 inline bool direct_configure(const PlanHeader &ph, const void *plan_host, const ChunkRange &rg, int N, int H, int W,
                              int C, int K, int stride, int layout, int esize, int smem_limit, int sms, bool wgrad,
-                             DirectConfig *out) {
+                             bool pair, DirectConfig *out) {
     if (layout != O1D_NHWC || K > kMaxTaps || (stride != 1 && stride != 2)) return false;
     const int CCs = 32 / esize;
     if (C % CCs != 0) return false;
@@ -143,7 +143,8 @@ inline bool direct_configure(const PlanHeader &ph, const void *plan_host, const 
         if (n > longest) longest = n;
     }
     const int kt = longest <= 15 ? 15 : longest <= 23 ? 23 : 31;
-    return direct_configure_tiles(N, H, W, C, K, stride, esize, smem_limit, sms, wgrad, hh, hw, kt, CCs * kt * 8, rg, out);
+    return direct_configure_tiles(N, H, W, C, K, stride, esize, smem_limit, sms, wgrad, hh, hw, kt, CCs * kt * 8, rg, pair,
+                                  out);
 }
 
 // Stride-2 input gradient: tiles of the dy grid (P x Q) with a halo of half the lines' reach.
@@ -170,7 +171,8 @@ inline bool direct_configure_dgrad2(const PlanHeader &ph, const void *plan_host,
     const int P = ceil_div(H, 2), Q = ceil_div(W, 2);
     const int hh = (rg.reach_h + 1) / 2, hw = (rg.reach_w + 1) / 2;
     const int tap_bytes = 4 * CCs * kDgrad2Slots * 8 + 4 * CCs * 4;
-    if (!direct_configure_tiles(N, P, Q, C, K, 1, esize, smem_limit, sms, false, hh, hw, kDgrad2Slots, tap_bytes, rg, out))
+    if (!direct_configure_tiles(N, P, Q, C, K, 1, esize, smem_limit, sms, false, hh, hw, kDgrad2Slots, tap_bytes, rg, false,
+                                out))
         return false;
     return true;
 }
@@ -215,17 +217,27 @@ struct DirectLaunchSet {
     DirectConfig cfg[kMaxChunkRanges];
     int kt, npx, smem_bytes, grid, threads;
     bool whole_image;
+    bool pair;                   // forward, 2-byte elements: every even/odd channel pair shares its line
     size_t partial_floats;       // weight gradient: floats of partial sums over all ranges
 };
 inline bool direct_plan_launches(const PlanHeader &ph, const void *plan_host, int N, int H, int W, int C, int K,
                                  int stride, int layout, int esize, int smem_limit, int sms, int mode,
                                  DirectLaunchSet *out) {
     if (layout != O1D_NHWC || K > kMaxTaps || C % (32 / esize) != 0) return false;
+    bool pair = false;
+    // measured with block-wise angles, bf16: 7x7 80 vs 88 us, 14x14 142 vs 153, 28x28 233 vs 270 at batch 256;
+    // stride 2 loses 6 % (two weight sets leave registers for two outputs per thread only)
+    if (mode == DIRECT_FPROP && esize == 2 && stride == 1) {
+        PlanView pv = plan_view(plan_host, ph);
+        pair = true;
+        for (int c = 0; c + 1 < C && pair; c += 2) pair = pv.cls[c] == pv.cls[c + 1];
+    }
+    out->pair = pair;
     auto configure = [&](const ChunkRange &rg, DirectConfig *cfg) {
         return mode == DIRECT_DGRAD2
                    ? direct_configure_dgrad2(ph, plan_host, rg, N, H, W, C, K, layout, esize, smem_limit, sms, cfg)
                    : direct_configure(ph, plan_host, rg, N, H, W, C, K, stride, layout, esize, smem_limit, sms,
-                                      mode == DIRECT_WGRAD, cfg);
+                                      mode == DIRECT_WGRAD, pair, cfg);
     };
     const ChunkRange all{0, C / (32 / esize), ph.max_dh, ph.max_dw};
     DirectConfig whole;
@@ -250,7 +262,7 @@ inline bool direct_plan_launches(const PlanHeader &ph, const void *plan_host, in
         else return false;
     }
     // common launch parameters; every range gets a share of the SMs in proportion to its chunks
-    const int plw = (32 / esize) == 8 ? 4 : 2;
+    const int plw = (esize == 4 || pair) ? 4 : 2;
     const int total_chunks = C / (32 / esize);
     out->kt = 0; out->npx = 4; out->smem_bytes = 0; out->grid = 0; out->partial_floats = 0;
     out->whole_image = out->cfg[0].whole_image;
@@ -258,6 +270,8 @@ inline bool direct_plan_launches(const PlanHeader &ph, const void *plan_host, in
         if (out->cfg[i].kt > out->kt) out->kt = out->cfg[i].kt;
         if (out->cfg[i].npx < out->npx) out->npx = out->cfg[i].npx;
     }
+    // two weight sets per thread: four outputs per thread would spill with the longest tap lists
+    if (pair && out->npx == 4 && out->kt > 15) out->npx = 2;
     for (int i = 0; i < out->n; i++) {
         DirectConfig &c = out->cfg[i];
         if (mode != DIRECT_DGRAD2) {     // the tap tables are sized by the common KT
@@ -309,8 +323,13 @@ inline void direct_fill_multi(const DirectLaunchSet &ls, DirectMulti *mp) {
 template <typename T, int KT, int NPX, int STRIDE>
 cudaError_t launch_direct_one(const DirectLaunchSet &ls, const DirectMulti &mp, const DirectMaps &maps, const float *w, const float *bias,
                               const PlanView &pv, void *y, cudaStream_t st) {
-    auto kern = ls.n > 1 ? direct_fprop_nhwc_kernel<T, KT, NPX, STRIDE, true>
-                         : direct_fprop_nhwc_kernel<T, KT, NPX, STRIDE, false>;
+    auto kern = ls.n > 1 ? direct_fprop_nhwc_kernel<T, KT, NPX, STRIDE, true, false>
+                         : direct_fprop_nhwc_kernel<T, KT, NPX, STRIDE, false, false>;
+    if constexpr (sizeof(T) == 2) {
+        if (ls.pair)
+            kern = ls.n > 1 ? direct_fprop_nhwc_kernel<T, KT, NPX, STRIDE, true, true>
+                            : direct_fprop_nhwc_kernel<T, KT, NPX, STRIDE, false, true>;
+    }
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ls.smem_bytes);
     if (e != cudaSuccess) return e;
     kern<<<ls.grid, ls.threads, ls.smem_bytes, st>>>(mp, maps, w, bias, pv.cls, pv.taps, (T *)y);
