@@ -11,6 +11,7 @@
 #include "o1d_generic.cuh"
 #include "o1d_tiled_host.cuh"
 #include "o1d_direct_host.cuh"
+#include "o1d_small.cuh"
 #include "o1d_layernorm.cuh"
 #include "o1d_transpose.cuh"
 #include "o1d_pointwise.cuh"
@@ -217,6 +218,26 @@ int try_direct(const void *x, const float *w, const float *bias, const PlanHeade
     return O1D_OK;
 }
 
+// Forward / stride-1 input gradient of 7x7 maps with one channel plane per thread.
+int try_small7(const void *x, const float *w, const float *bias, const PlanHeader &ph, const void *plan_dev, void *y,
+               int N, int H, int W, int C, int K, int stride, int layout, int dtype, int add_identity, int flip,
+               cudaStream_t st, const DeviceInfo &d) {
+    if (g_force_generic) return kNotTiled;
+    const int esize = dtype == O1D_F32 ? 4 : 2;
+    SmallConfig cfg;
+    if (!small7_configure(ph, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, &cfg)) return kNotTiled;
+    if (((uintptr_t)y & 15) != 0) return kNotTiled;
+    CUtensorMap map;
+    if (!make_small7_tensor_map(&map, x, N, C, esize, cfg.p.CCs)) return kNotTiled;
+    cfg.p.flip = flip;
+    cfg.p.add_identity = add_identity;
+    PlanView pv = plan_view(plan_dev, ph);
+    const cudaError_t e = dtype == O1D_F32 ? launch_small7<float>(cfg, map, w, bias, pv.chan, y, st)
+                                           : launch_small7<__nv_bfloat16>(cfg, map, w, bias, pv.chan, y, st);
+    if (e != cudaSuccess) return cuda_fail(e, "7x7 plane kernel launch");
+    return O1D_OK;
+}
+
 // Route of a forward-type call (flip = 1: stride-1 input gradient):
 //   1. direct kernels when one tile holds a whole image (small maps),
 //   2. tiled kernels (canonical lines, stride 1, sizes in multiples of 7/8),
@@ -226,6 +247,10 @@ int route_forward(const void *x, const float *w, const float *bias, const PlanHe
                   const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride, int layout,
                   int dtype, int add_identity, int flip, cudaStream_t st, const DeviceInfo &d) {
     int rc = kNotTiled;
+    if (g_prefer == 0) {       // 7x7 maps on canonical lines: a channel plane per thread
+        rc = try_small7(x, w, bias, ph, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity, flip, st, d);
+        if (rc != kNotTiled) return rc;
+    }
     // Layers whose chunks are all of one line kind (the models' block-wise angle assignment) can
     // leave half of a tiled CTA's threads without a segment; the direct kernels then win even
     // with row tiles (28x28x192 fp32, batch 128: 167 vs 250 us).

@@ -1,0 +1,211 @@
+// 7x7 maps (the last ConvNeXt stage): one thread holds a whole 49-pixel channel plane in
+// registers.  Forward and stride-1 input gradient, NHWC, canonical lines, K <= 31.
+//
+// A 31-tap line over a 7x7 map touches at most 13 pixels, so tiles with line halos (the
+// direct kernels: a 19x19 zero-filled tile per 7x7 image, one shared-memory load per FMA) or
+// planes with restage and band passes (the tiled kernels) are mostly overhead here.  Instead:
+//   * TMA brings a box [32 images][7][7][CCs channels] (50 KB) into one of two tile buffers;
+//   * the CTA re-lays it into one fp32 plane per channel, [channel][image][49 (+2 pad)], with
+//     strides chosen so that both the re-layout and the per-thread plane loads are free of bank
+//     conflicts;
+//   * thread (warp = channel, lane = image) loads its 49 inputs into registers and evaluates
+//     the 49 outputs with code unrolled for its channel's line: every tap that lands inside
+//     the map is one register-register FMA, every other tap does not exist (compile time);
+//     a warp works on one channel, so the eight unrolled line shapes never diverge;
+//   * outputs go back through the thread's own plane and leave as 128-bit NHWC stores.
+// About 17 instructions per output instead of about 50.
+#pragma once
+
+#include "o1d_common.cuh"
+#include "o1d_lines.cuh"
+#include "o1d_tiled_host.cuh"   // mbarrier / TMA primitives, static_for, Vec16, encode_tiled_fn
+
+namespace o1d {
+
+constexpr int kSmallImgs = 32;                    // images per tile = lanes of a warp
+constexpr int kSmallPix = 49;
+constexpr int kSmallImgPitch = 51;                // floats between the images of a plane (odd)
+constexpr int kSmallPlaneStride = kSmallImgs * kSmallImgPitch + 4;   // = 4 (mod 32): channel planes 4 banks apart
+
+struct SmallParams {
+    int N, C, K, CCs, nchunks, tiles_n;
+    int flip, add_identity;
+    int tile_bytes, off_planes_bytes, off_w_bytes, off_bar_bytes;
+};
+
+// y[p] = bias + sum over the taps of line O that land inside the 7x7 map.  w is indexed by the
+// canonical tap index (k - 15 = signed distance along the line); taps beyond K/2 carry weight 0.
+template <int O>
+__device__ __forceinline__ void small_plane(const float (&x)[kSmallPix], const float (&w)[kMaxTaps], float bias,
+                                            float *__restrict__ out) {
+    static_for<0, kSmallPix>([&](auto pi) {
+        constexpr int p = decltype(pi)::value, h = p / 7, q = p % 7;
+        float acc = bias;
+        static_for<0, kMaxTaps>([&](auto ki) {
+            constexpr int k = decltype(ki)::value;
+            constexpr int hh = h + kCanonDh[O][k], qq = q + kCanonDw[O][k];
+            if constexpr (hh >= 0 && hh < 7 && qq >= 0 && qq < 7) acc = fmaf(w[k], x[hh * 7 + qq], acc);
+        });
+        out[p] = acc;
+    });
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512, 1)
+small7_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restrict__ wgt,
+                    const float *__restrict__ bias, const int8_t *__restrict__ chan, T *__restrict__ y,
+                    const SmallParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float *planes = reinterpret_cast<float *>(smem_raw + p.off_planes_bytes);
+    float *s_w = reinterpret_cast<float *>(smem_raw + p.off_w_bytes);          // [CCs][32]
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + p.off_bar_bytes);
+    constexpr int VE = Vec16<T>::N;
+
+    const int tid = threadIdx.x, nt = blockDim.x;         // nt = 32 * CCs: one thread per (channel, image)
+    const int lane = tid & 31, ch = tid >> 5;
+    constexpr int CCs = 32 / (int)sizeof(T);              // channels per chunk: compile time, so that the
+                                                          // re-layout index arithmetic has no runtime divisions
+    // work items (chunk, tile of 32 images), chunk fastest, dealt round-robin to the CTAs
+    const int items = p.nchunks * p.tiles_n;
+    const int my_tiles = (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    auto item_of = [&](int it, int &chunk, int &n0) {
+        const int t = blockIdx.x + it * gridDim.x;
+        chunk = t % p.nchunks;
+        n0 = (t / p.nchunks) * kSmallImgs;
+    };
+
+    if (tid == 0) {
+        mbar_init(&full[0], 1);
+        mbar_init(&full[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    auto issue = [&](int it) {
+        int chunk, n0;
+        item_of(it, chunk, n0);
+        const int b = it & 1;
+        mbar_expect_tx(&full[b], p.tile_bytes);
+        tma_load_4d(smem_raw + (size_t)b * p.tile_bytes, &tmap, &full[b], chunk * CCs, 0, 0, n0);
+    };
+    if (tid == 0) {
+        if (my_tiles > 0) issue(0);
+        if (my_tiles > 1) issue(1);
+    }
+
+    float *mine = planes + ch * kSmallPlaneStride + lane * kSmallImgPitch;
+    constexpr int elems = kSmallImgs * kSmallPix * CCs;   // elements of a tile
+    bool failed = false;
+    for (int it = 0; it < my_tiles; it++) {
+        const int b = it & 1;
+        int chunk, n0;
+        item_of(it, chunk, n0);
+        const int c0 = chunk * CCs;
+        // weights of this chunk by canonical tap index, mirrored for the input gradient
+        for (int e = tid; e < CCs * 32; e += nt) {
+            const int i = e >> 5, k = e & 31;
+            float v = 0.f;
+            const int kk = k - kHalf + p.K / 2;
+            if (k < kMaxTaps && kk >= 0 && kk < p.K) {
+                const int src = p.flip ? p.K - 1 - kk : kk;
+                v = __ldg(wgt + (size_t)(c0 + i) * p.K + src);
+                if (p.add_identity && src == p.K / 2) v += 1.f;
+            }
+            s_w[e] = v;
+        }
+        const float bv = bias ? __ldg(bias + c0 + ch) : 0.f;
+        const int line = chan[c0 + ch];                    // canonical line of this warp's channel
+        if (!failed && !mbar_wait(&full[b], (it >> 1) & 1)) failed = true;
+        // ---- tile [image][pixel][channel] -> planes [channel][image][pixel] ----------------
+        const T *tile = reinterpret_cast<const T *>(smem_raw + (size_t)b * p.tile_bytes);
+        for (int e = tid; e < elems; e += nt) {
+            const int c = e % CCs, ip = e / CCs;          // ip = image * 49 + pixel
+            const int img = ip / kSmallPix, px = ip - img * kSmallPix;
+            planes[c * kSmallPlaneStride + img * kSmallImgPitch + px] = (float)tile[e];   // shared memory: a plain load
+        }
+        __syncthreads();                                   // planes complete; tile buffer b is free
+        if (tid == 0 && it + 2 < my_tiles) issue(it + 2);
+        // ---- one plane per thread -----------------------------------------------------------
+        float w[kMaxTaps];
+#pragma unroll
+        for (int k = 0; k < kMaxTaps; k++) w[k] = s_w[ch * 32 + k];
+        float x[kSmallPix];
+#pragma unroll
+        for (int i = 0; i < kSmallPix; i++) x[i] = mine[i];
+        switch (line) {                                    // warp-uniform
+            case 0: small_plane<0>(x, w, bv, mine); break;
+            case 1: small_plane<1>(x, w, bv, mine); break;
+            case 2: small_plane<2>(x, w, bv, mine); break;
+            case 3: small_plane<3>(x, w, bv, mine); break;
+            case 4: small_plane<4>(x, w, bv, mine); break;
+            case 5: small_plane<5>(x, w, bv, mine); break;
+            case 6: small_plane<6>(x, w, bv, mine); break;
+            default: small_plane<7>(x, w, bv, mine); break;
+        }
+        __syncthreads();                                   // output planes complete
+        // ---- planes -> NHWC, 16 bytes per store ---------------------------------------------
+        constexpr int GV = CCs / VE;                       // 16-byte vectors per pixel of the chunk
+        for (int e = tid; e < kSmallImgs * kSmallPix * GV; e += nt) {
+            const int g = e % GV, ip = e / GV;
+            const int img = ip / kSmallPix, px = ip - img * kSmallPix;
+            if (n0 + img >= p.N) continue;
+            float f[VE];
+#pragma unroll
+            for (int j = 0; j < VE; j++) f[j] = planes[(g * VE + j) * kSmallPlaneStride + img * kSmallImgPitch + px];
+            *reinterpret_cast<uint4 *>(y + ((size_t)(n0 + img) * kSmallPix + px) * p.C + c0 + g * VE) = Vec16<T>::pack(f);
+        }
+        __syncthreads();                                   // planes may be overwritten by the next tile
+    }
+}
+
+
+// ---- host side -------------------------------------------------------------------------
+struct SmallConfig { SmallParams p; int smem_bytes, grid, threads; };
+
+inline bool small7_configure(const PlanHeader &ph, int N, int H, int W, int C, int K, int stride, int layout, int esize,
+                             int smem_limit, int sms, SmallConfig *out) {
+    if (H != 7 || W != 7 || stride != 1 || layout != O1D_NHWC || K > kMaxTaps || !ph.all_canon || ph.chan_off == 0)
+        return false;
+    const int CCs = 32 / esize;
+    if (C % CCs != 0) return false;
+    SmallParams p{};
+    p.N = N; p.C = C; p.K = K; p.CCs = CCs; p.nchunks = C / CCs;
+    p.tiles_n = ceil_div(N, kSmallImgs);
+    p.tile_bytes = kSmallImgs * kSmallPix * CCs * esize;
+    p.off_planes_bytes = 2 * p.tile_bytes;
+    p.off_w_bytes = p.off_planes_bytes + CCs * kSmallPlaneStride * 4;
+    p.off_bar_bytes = p.off_w_bytes + CCs * 32 * 4;
+    out->smem_bytes = p.off_bar_bytes + 16;
+    if (out->smem_bytes > smem_limit) return false;
+    const int items = p.nchunks * p.tiles_n;
+    out->grid = items < sms ? items : sms;
+    out->threads = 32 * CCs;
+    out->p = p;
+    return true;
+}
+
+// 4-D tensor map over an NHWC tensor [N][7][7][C] with a box CCs x 7 x 7 x 32 images.
+inline bool make_small7_tensor_map(CUtensorMap *map, const void *base, int N, int C, int esize, int CCs) {
+    PFN_encodeTiled enc = encode_tiled_fn();
+    if (!enc || ((uintptr_t)base & 15) || (C * esize) % 16 != 0) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)C, 7, 7, (cuuint64_t)N};
+    cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)7 * C * esize, (cuuint64_t)49 * C * esize};
+    cuuint32_t box[4] = {(cuuint32_t)CCs, 7, 7, (cuuint32_t)kSmallImgs};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+               const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T>
+cudaError_t launch_small7(const SmallConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
+                          const int8_t *chan, void *y, cudaStream_t st) {
+    auto kern = small7_fprop_kernel<T>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
+    if (e != cudaSuccess) return e;
+    kern<<<cfg.grid, cfg.threads, cfg.smem_bytes, st>>>(map, w, bias, chan, (T *)y, cfg.p);
+    return cudaGetLastError();
+}
+
+}  // namespace o1d
