@@ -30,6 +30,7 @@ constexpr int kSmallPlaneStride = kSmallImgs * kSmallImgPitch + 4;   // = 4 (mod
 struct SmallParams {
     int N, C, K, CCs, nchunks, tiles_n;
     int flip, add_identity;
+    int nbuf;                     // tile buffers: 2 (one CTA per SM) or 1 (two CTAs per SM overlap each other)
     int tile_bytes, off_planes_bytes, off_w_bytes, off_bar_bytes;
 };
 
@@ -84,20 +85,18 @@ small7_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__res
     auto issue = [&](int it) {
         int chunk, n0;
         item_of(it, chunk, n0);
-        const int b = it & 1;
+        const int b = it % p.nbuf;
         mbar_expect_tx(&full[b], p.tile_bytes);
         tma_load_4d(smem_raw + (size_t)b * p.tile_bytes, &tmap, &full[b], chunk * CCs, 0, 0, n0);
     };
-    if (tid == 0) {
-        if (my_tiles > 0) issue(0);
-        if (my_tiles > 1) issue(1);
-    }
+    if (tid == 0)
+        for (int it = 0; it < p.nbuf && it < my_tiles; it++) issue(it);
 
     float *mine = planes + ch * kSmallPlaneStride + lane * kSmallImgPitch;
     constexpr int elems = kSmallImgs * kSmallPix * CCs;   // elements of a tile
     bool failed = false;
     for (int it = 0; it < my_tiles; it++) {
-        const int b = it & 1;
+        const int b = it % p.nbuf;
         int chunk, n0;
         item_of(it, chunk, n0);
         const int c0 = chunk * CCs;
@@ -115,16 +114,21 @@ small7_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__res
         }
         const float bv = bias ? __ldg(bias + c0 + ch) : 0.f;
         const int line = chan[c0 + ch];                    // canonical line of this warp's channel
-        if (!failed && !mbar_wait(&full[b], (it >> 1) & 1)) failed = true;
+        if (!failed && !mbar_wait(&full[b], (it / p.nbuf) & 1)) failed = true;
         // ---- tile [image][pixel][channel] -> planes [channel][image][pixel] ----------------
         const T *tile = reinterpret_cast<const T *>(smem_raw + (size_t)b * p.tile_bytes);
-        for (int e = tid; e < elems; e += nt) {
-            const int c = e % CCs, ip = e / CCs;          // ip = image * 49 + pixel
-            const int img = ip / kSmallPix, px = ip - img * kSmallPix;
-            planes[c * kSmallPlaneStride + img * kSmallImgPitch + px] = (float)tile[e];   // shared memory: a plain load
+        {   // thread -> channel tid % CCs and (image, pixel) tid / CCs, then 32 pixels further per trip
+            int img = (tid / CCs) / kSmallPix, px = (tid / CCs) % kSmallPix;
+            float *dst = planes + (tid % CCs) * kSmallPlaneStride;
+#pragma unroll 7
+            for (int i = 0; i < elems / (32 * CCs); i++) {
+                dst[img * kSmallImgPitch + px] = (float)tile[tid + i * 32 * CCs];   // shared memory: a plain load
+                px += 32;
+                if (px >= kSmallPix) { px -= kSmallPix; img++; }
+            }
         }
         __syncthreads();                                   // planes complete; tile buffer b is free
-        if (tid == 0 && it + 2 < my_tiles) issue(it + 2);
+        if (tid == 0 && it + p.nbuf < my_tiles) issue(it + p.nbuf);
         // ---- one plane per thread -----------------------------------------------------------
         float w[kMaxTaps];
 #pragma unroll
@@ -145,14 +149,20 @@ small7_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__res
         __syncthreads();                                   // output planes complete
         // ---- planes -> NHWC, 16 bytes per store ---------------------------------------------
         constexpr int GV = CCs / VE;                       // 16-byte vectors per pixel of the chunk
-        for (int e = tid; e < kSmallImgs * kSmallPix * GV; e += nt) {
-            const int g = e % GV, ip = e / GV;
-            const int img = ip / kSmallPix, px = ip - img * kSmallPix;
-            if (n0 + img >= p.N) continue;
-            float f[VE];
+        {
+            constexpr int STEP = 32 * CCs / GV, DI = STEP / kSmallPix, DP = STEP % kSmallPix;   // (image, pixel) per trip
+            const int g = tid % GV;
+            int img = (tid / GV) / kSmallPix, px = (tid / GV) % kSmallPix;
+            const float *src = planes + g * VE * kSmallPlaneStride;
+            T *dst = y + (size_t)n0 * kSmallPix * p.C + c0 + g * VE;
+            for (; img < kSmallImgs; img += DI, px += DP) {
+                if (px >= kSmallPix) { px -= kSmallPix; if (++img >= kSmallImgs) break; }
+                if (n0 + img >= p.N) break;                // images are visited in ascending order
+                float f[VE];
 #pragma unroll
-            for (int j = 0; j < VE; j++) f[j] = planes[(g * VE + j) * kSmallPlaneStride + img * kSmallImgPitch + px];
-            *reinterpret_cast<uint4 *>(y + ((size_t)(n0 + img) * kSmallPix + px) * p.C + c0 + g * VE) = Vec16<T>::pack(f);
+                for (int j = 0; j < VE; j++) f[j] = src[j * kSmallPlaneStride + img * kSmallImgPitch + px];
+                *reinterpret_cast<uint4 *>(dst + ((size_t)img * kSmallPix + px) * p.C) = Vec16<T>::pack(f);
+            }
         }
         __syncthreads();                                   // planes may be overwritten by the next tile
     }
@@ -172,13 +182,16 @@ inline bool small7_configure(const PlanHeader &ph, int N, int H, int W, int C, i
     p.N = N; p.C = C; p.K = K; p.CCs = CCs; p.nchunks = C / CCs;
     p.tiles_n = ceil_div(N, kSmallImgs);
     p.tile_bytes = kSmallImgs * kSmallPix * CCs * esize;
-    p.off_planes_bytes = 2 * p.tile_bytes;
+    // 4-byte elements: 256 threads per CTA; one tile buffer leaves room for two CTAs per SM
+    p.nbuf = (esize == 4) ? 1 : 2;
+    p.off_planes_bytes = p.nbuf * p.tile_bytes;
     p.off_w_bytes = p.off_planes_bytes + CCs * kSmallPlaneStride * 4;
     p.off_bar_bytes = p.off_w_bytes + CCs * 32 * 4;
     out->smem_bytes = p.off_bar_bytes + 16;
     if (out->smem_bytes > smem_limit) return false;
     const int items = p.nchunks * p.tiles_n;
-    out->grid = items < sms ? items : sms;
+    const int slots = sms * (p.nbuf == 1 ? 2 : 1);
+    out->grid = items < slots ? items : slots;
     out->threads = 32 * CCs;
     out->p = p;
     return true;
