@@ -238,6 +238,31 @@ int try_small7(const void *x, const float *w, const float *bias, const PlanHeade
     return O1D_OK;
 }
 
+// Weight gradient of 7x7 maps with one channel plane per thread.
+int try_small7_wgrad(const void *dy, const void *x, const PlanHeader &ph, const void *plan_dev, float *dw, float *db,
+                     void *workspace, size_t workspace_bytes, int N, int H, int W, int C, int K, int stride,
+                     int layout, int dtype, cudaStream_t st, const DeviceInfo &d) {
+    if (g_force_generic) return kNotTiled;
+    const int esize = dtype == O1D_F32 ? 4 : 2;
+    SmallConfig cfg;
+    if (!small7_wgrad_configure(ph, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, &cfg)) return kNotTiled;
+    if (((uintptr_t)workspace & 15) != 0) return kNotTiled;
+    if (workspace_bytes < small7_wgrad_partial_bytes(cfg)) return O1D_ERR_WORKSPACE;
+    CUtensorMap mx, mdy;
+    if (!make_small7_tensor_map(&mx, x, N, C, esize, cfg.p.CCs)) return kNotTiled;
+    if (!make_small7_tensor_map(&mdy, dy, N, C, esize, cfg.p.CCs)) return kNotTiled;
+    PlanView pv = plan_view(plan_dev, ph);
+    float *partial = (float *)workspace;
+    const cudaError_t e = dtype == O1D_F32 ? launch_small7_wgrad<float>(cfg, mx, mdy, pv.chan, partial, st)
+                                           : launch_small7_wgrad<__nv_bfloat16>(cfg, mx, mdy, pv.chan, partial, st);
+    if (e != cudaSuccess) return cuda_fail(e, "7x7 plane wgrad launch");
+    const int tot = C * (K + 1);
+    small7_wgrad_final_kernel<<<ceil_div(tot, 128), 128, 0, st>>>(partial, dw, db, C, K, cfg.p.CCs, cfg.p.nchunks,
+                                                                  cfg.p.tiles_n);
+    O1D_CUDA(cudaGetLastError());
+    return O1D_OK;
+}
+
 // Route of a forward-type call (flip = 1: stride-1 input gradient):
 //   1. direct kernels when one tile holds a whole image (small maps),
 //   2. tiled kernels (canonical lines, stride 1, sizes in multiples of 7/8),
@@ -583,6 +608,11 @@ int o1d_wgrad(const void *dy, const void *x, const void *plan_host, const void *
     // Small maps: the direct kernels first (measured at batch 128: fp32 28x28 120 vs 142 us, 14x14 75 vs
     // 84, 7x7 33 vs 59; bf16 only at 7x7, 40 vs 64, since every 2-byte load needs a widening shift).
     // Otherwise tiled, then direct (stems, dense-prediction maps, arbitrary angles), then general.
+    if (g_prefer == 0) {       // 7x7 maps on canonical lines: a channel plane per thread
+        rc = try_small7_wgrad(dy, x, ph, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K, stride, layout,
+                              dtype, st, d);
+        if (rc != kNotTiled && rc != O1D_ERR_WORKSPACE) return rc;
+    }
     const bool small_map = (dtype == O1D_F32) ? (H * W <= 32 * 32) : (H * W <= 10 * 10);
     bool weak_tiled = false;     // see route_forward
     if (g_prefer == 0 && !small_map) {

@@ -169,6 +169,129 @@ small7_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__res
 }
 
 
+// Weight gradient of one plane: acc[k] += sum over pixels p of x[p + offset_k] * dy[p] for the taps
+// that land inside the map (compile time); dy comes from the thread's plane, one pixel at a time.
+template <int O>
+__device__ __forceinline__ void small_plane_wgrad(const float (&x)[kSmallPix], const float *__restrict__ dyp,
+                                                  float (&acc)[kMaxTaps], float &db) {
+    static_for<0, kSmallPix>([&](auto pi) {
+        constexpr int p = decltype(pi)::value, h = p / 7, q = p % 7;
+        const float g = dyp[p];
+        db += g;
+        static_for<0, kMaxTaps>([&](auto ki) {
+            constexpr int k = decltype(ki)::value;
+            constexpr int hh = h + kCanonDh[O][k], qq = q + kCanonDw[O][k];
+            if constexpr (hh >= 0 && hh < 7 && qq >= 0 && qq < 7) acc[k] = fmaf(x[hh * 7 + qq], g, acc[k]);
+        });
+    });
+}
+
+// Weight gradient, same tiles and planes: x goes tile -> planes -> registers, then dy takes the
+// same tile buffer and the same planes.  The 32 images of a warp are added with shuffles; one
+// partial per (tile, channel); small7_wgrad_final_kernel adds the tiles of a chunk in order.
+template <typename T>
+__global__ void __launch_bounds__(512, 1)
+small7_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_dy,
+                    const int8_t *__restrict__ chan, float *__restrict__ partial, const SmallParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float *planes = reinterpret_cast<float *>(smem_raw + p.off_planes_bytes);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + p.off_bar_bytes);
+    constexpr int CCs = 32 / (int)sizeof(T);
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, ch = tid >> 5;
+    const int items = p.nchunks * p.tiles_n;
+    const int my_tiles = (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    auto item_of = [&](int it, int &chunk, int &n0) {
+        const int t = blockIdx.x + it * gridDim.x;
+        chunk = t % p.nchunks;
+        n0 = (t / p.nchunks) * kSmallImgs;
+    };
+    if (tid == 0) {
+        mbar_init(&full[0], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    auto issue = [&](const CUtensorMap *map, int it) {       // the single tile buffer
+        int chunk, n0;
+        item_of(it, chunk, n0);
+        mbar_expect_tx(&full[0], p.tile_bytes);
+        tma_load_4d(smem_raw, map, &full[0], chunk * CCs, 0, 0, n0);
+    };
+    auto relayout = [&]() {
+        const T *tile = reinterpret_cast<const T *>(smem_raw);
+        int img = (tid / CCs) / kSmallPix, px = (tid / CCs) % kSmallPix;
+        float *dst = planes + (tid % CCs) * kSmallPlaneStride;
+#pragma unroll 7
+        for (int i = 0; i < kSmallPix; i++) {
+            dst[img * kSmallImgPitch + px] = (float)tile[tid + i * 32 * CCs];
+            px += 32;
+            if (px >= kSmallPix) { px -= kSmallPix; img++; }
+        }
+    };
+    if (tid == 0 && my_tiles > 0) issue(&tmap_x, 0);
+    float *mine = planes + ch * kSmallPlaneStride + lane * kSmallImgPitch;
+    uint32_t uses = 0;
+    bool failed = false;
+    for (int it = 0; it < my_tiles; it++) {
+        int chunk, n0;
+        item_of(it, chunk, n0);
+        const int line = chan[chunk * CCs + ch];
+        if (!failed && !mbar_wait(&full[0], uses++ & 1)) failed = true;
+        relayout();                                        // x: tile -> planes
+        __syncthreads();
+        if (tid == 0) issue(&tmap_dy, it);                 // dy of the same item into the freed tile buffer
+        float x[kSmallPix];
+#pragma unroll
+        for (int i = 0; i < kSmallPix; i++) x[i] = mine[i];
+        __syncthreads();                                   // every thread holds its x plane in registers
+        if (!failed && !mbar_wait(&full[0], uses++ & 1)) failed = true;
+        relayout();                                        // dy: tile -> the same planes
+        __syncthreads();
+        if (tid == 0 && it + 1 < my_tiles) issue(&tmap_x, it + 1);
+        float acc[kMaxTaps], db = 0.f;
+#pragma unroll
+        for (int k = 0; k < kMaxTaps; k++) acc[k] = 0.f;
+        switch (line) {
+            case 0: small_plane_wgrad<0>(x, mine, acc, db); break;
+            case 1: small_plane_wgrad<1>(x, mine, acc, db); break;
+            case 2: small_plane_wgrad<2>(x, mine, acc, db); break;
+            case 3: small_plane_wgrad<3>(x, mine, acc, db); break;
+            case 4: small_plane_wgrad<4>(x, mine, acc, db); break;
+            case 5: small_plane_wgrad<5>(x, mine, acc, db); break;
+            case 6: small_plane_wgrad<6>(x, mine, acc, db); break;
+            default: small_plane_wgrad<7>(x, mine, acc, db); break;
+        }
+        // images beyond N are zero-filled tiles: they add nothing.  Sum over the warp's 32 images.
+#pragma unroll
+        for (int k = 0; k < kMaxTaps; k++)
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], d);
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) db += __shfl_xor_sync(0xffffffffu, db, d);
+        float *dst = partial + ((size_t)(blockIdx.x + it * gridDim.x) * CCs + ch) * 32;
+        float mineval = db;                                // lane k keeps tap k, lane 31 the bias gradient
+#pragma unroll
+        for (int k = 0; k < kMaxTaps; k++) if (lane == k) mineval = acc[k];
+        dst[lane] = mineval;
+        __syncthreads();                                   // planes are overwritten by the next item's x
+    }
+}
+
+// dw[c][kk] = sum over the tiles of c's chunk, in tile order, of the partial of canonical tap kk - K/2 + 15.
+__global__ void small7_wgrad_final_kernel(const float *__restrict__ partial, float *__restrict__ dw,
+                                          float *__restrict__ db, int C, int K, int CCs, int nchunks, int tiles_n) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= C * (K + 1)) return;
+    const int c = idx / (K + 1), kk = idx % (K + 1);
+    if (kk == K && db == nullptr) return;
+    const int chunk = c / CCs, cl = c % CCs;
+    const int slot = kk == K ? 31 : kk - K / 2 + kHalf;
+    float sum = 0.f;
+    for (int t = 0; t < tiles_n; t++) sum += partial[((size_t)(t * nchunks + chunk) * CCs + cl) * 32 + slot];
+    if (kk == K) db[c] = sum; else dw[(size_t)c * K + kk] = sum;
+}
+
 // ---- host side -------------------------------------------------------------------------
 struct SmallConfig { SmallParams p; int smem_bytes, grid, threads; };
 
@@ -218,6 +341,35 @@ cudaError_t launch_small7(const SmallConfig &cfg, const CUtensorMap &map, const 
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
     if (e != cudaSuccess) return e;
     kern<<<cfg.grid, cfg.threads, cfg.smem_bytes, st>>>(map, w, bias, chan, (T *)y, cfg.p);
+    return cudaGetLastError();
+}
+
+
+// Weight gradient: one tile buffer (x, then dy), one set of planes.
+inline bool small7_wgrad_configure(const PlanHeader &ph, int N, int H, int W, int C, int K, int stride, int layout,
+                                   int esize, int smem_limit, int sms, SmallConfig *out) {
+    if (!small7_configure(ph, N, H, W, C, K, stride, layout, esize, smem_limit, sms, out)) return false;
+    SmallParams &p = out->p;
+    p.nbuf = 1;
+    p.off_planes_bytes = p.tile_bytes;
+    p.off_w_bytes = p.off_planes_bytes + p.CCs * kSmallPlaneStride * 4;
+    p.off_bar_bytes = p.off_w_bytes;
+    out->smem_bytes = p.off_bar_bytes + 16;
+    const int items = p.nchunks * p.tiles_n;
+    const int slots = sms * ((228 * 1024) / (out->smem_bytes + 1024) >= 2 && out->threads <= 256 ? 2 : 1);
+    out->grid = items < slots ? items : slots;
+    return true;
+}
+inline size_t small7_wgrad_partial_bytes(const SmallConfig &cfg) {
+    return (size_t)cfg.p.nchunks * cfg.p.tiles_n * cfg.p.CCs * 32 * sizeof(float);
+}
+template <typename T>
+cudaError_t launch_small7_wgrad(const SmallConfig &cfg, const CUtensorMap &mx, const CUtensorMap &mdy,
+                                const int8_t *chan, float *partial, cudaStream_t st) {
+    auto kern = small7_wgrad_kernel<T>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
+    if (e != cudaSuccess) return e;
+    kern<<<cfg.grid, cfg.threads, cfg.smem_bytes, st>>>(mx, mdy, chan, partial, cfg.p);
     return cudaGetLastError();
 }
 
