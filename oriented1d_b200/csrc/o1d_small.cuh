@@ -34,11 +34,26 @@ struct SmallParams {
     int tile_bytes, off_planes_bytes, off_w_bytes, off_bar_bytes;
 };
 
-// y[p] = bias + sum over the taps of line O that land inside the 7x7 map.  w is indexed by the
-// canonical tap index (k - 15 = signed distance along the line); taps beyond K/2 carry weight 0.
+// The eight canonical lines reduce to three base shapes (axis, slant, diagonal: canonical lines
+// 0, 1, 2) when the plane is read transposed and/or mirrored and the weights possibly reversed
+// (o1d_lines.cuh).  A thread therefore loads and stores its plane through the index map
+// (l, p) -> A*l + B*p + C0 of its channel's mode and runs one of three unrolled bodies instead of
+// one of eight: the bodies are large, and eight of them at once overflow the instruction cache.
+struct PlaneMap { int A, B, C0; };
+__device__ __forceinline__ PlaneMap plane_map(int mode) {
+    PlaneMap m;
+    m.A = (mode & MODE_T) ? 1 : 7;
+    m.B = (mode & MODE_T) ? 7 : 1;
+    m.C0 = 0;
+    if (mode & MODE_FP) { m.C0 = 6 * m.B; m.B = -m.B; }
+    return m;
+}
+
+// y'[l,p] = bias + sum over the taps of base line O that land inside the 7x7 map, in stored
+// coordinates.  w is indexed by the stored tap index; taps beyond K/2 carry weight 0.
 template <int O>
 __device__ __forceinline__ void small_plane(const float (&x)[kSmallPix], const float (&w)[kMaxTaps], float bias,
-                                            float *__restrict__ out) {
+                                            float *__restrict__ out, const PlaneMap m) {
     static_for<0, kSmallPix>([&](auto pi) {
         constexpr int p = decltype(pi)::value, h = p / 7, q = p % 7;
         float acc = bias;
@@ -47,7 +62,7 @@ __device__ __forceinline__ void small_plane(const float (&x)[kSmallPix], const f
             constexpr int hh = h + kCanonDh[O][k], qq = q + kCanonDw[O][k];
             if constexpr (hh >= 0 && hh < 7 && qq >= 0 && qq < 7) acc = fmaf(w[k], x[hh * 7 + qq], acc);
         });
-        out[p] = acc;
+        out[m.A * h + m.B * q + m.C0] = acc;
     });
 }
 
@@ -130,22 +145,17 @@ small7_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__res
         __syncthreads();                                   // planes complete; tile buffer b is free
         if (tid == 0 && it + p.nbuf < my_tiles) issue(it + p.nbuf);
         // ---- one plane per thread -----------------------------------------------------------
+        const int mode = canon_mode(line), kind = canon_kind(line);     // warp-uniform
+        const PlaneMap pm = plane_map(mode);
         float w[kMaxTaps];
 #pragma unroll
-        for (int k = 0; k < kMaxTaps; k++) w[k] = s_w[ch * 32 + k];
+        for (int k = 0; k < kMaxTaps; k++) w[k] = s_w[ch * 32 + ((mode & MODE_REV) ? kMaxTaps - 1 - k : k)];
         float x[kSmallPix];
 #pragma unroll
-        for (int i = 0; i < kSmallPix; i++) x[i] = mine[i];
-        switch (line) {                                    // warp-uniform
-            case 0: small_plane<0>(x, w, bv, mine); break;
-            case 1: small_plane<1>(x, w, bv, mine); break;
-            case 2: small_plane<2>(x, w, bv, mine); break;
-            case 3: small_plane<3>(x, w, bv, mine); break;
-            case 4: small_plane<4>(x, w, bv, mine); break;
-            case 5: small_plane<5>(x, w, bv, mine); break;
-            case 6: small_plane<6>(x, w, bv, mine); break;
-            default: small_plane<7>(x, w, bv, mine); break;
-        }
+        for (int i = 0; i < kSmallPix; i++) x[i] = mine[pm.A * (i / 7) + pm.B * (i % 7) + pm.C0];
+        if (kind == KIND_AXIS) small_plane<0>(x, w, bv, mine, pm);
+        else if (kind == KIND_SLANT) small_plane<1>(x, w, bv, mine, pm);
+        else small_plane<2>(x, w, bv, mine, pm);
         __syncthreads();                                   // output planes complete
         // ---- planes -> NHWC, 16 bytes per store ---------------------------------------------
         constexpr int GV = CCs / VE;                       // 16-byte vectors per pixel of the chunk
@@ -173,10 +183,10 @@ small7_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__res
 // that land inside the map (compile time); dy comes from the thread's plane, one pixel at a time.
 template <int O>
 __device__ __forceinline__ void small_plane_wgrad(const float (&x)[kSmallPix], const float *__restrict__ dyp,
-                                                  float (&acc)[kMaxTaps], float &db) {
+                                                  float (&acc)[kMaxTaps], float &db, const PlaneMap m) {
     static_for<0, kSmallPix>([&](auto pi) {
         constexpr int p = decltype(pi)::value, h = p / 7, q = p % 7;
-        const float g = dyp[p];
+        const float g = dyp[m.A * h + m.B * q + m.C0];
         db += g;
         static_for<0, kMaxTaps>([&](auto ki) {
             constexpr int k = decltype(ki)::value;
@@ -241,9 +251,11 @@ small7_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         relayout();                                        // x: tile -> planes
         __syncthreads();
         if (tid == 0) issue(&tmap_dy, it);                 // dy of the same item into the freed tile buffer
+        const int mode = canon_mode(line), kind = canon_kind(line);     // warp-uniform
+        const PlaneMap pm = plane_map(mode);
         float x[kSmallPix];
 #pragma unroll
-        for (int i = 0; i < kSmallPix; i++) x[i] = mine[i];
+        for (int i = 0; i < kSmallPix; i++) x[i] = mine[pm.A * (i / 7) + pm.B * (i % 7) + pm.C0];
         __syncthreads();                                   // every thread holds its x plane in registers
         if (!failed && !mbar_wait(&full[0], uses++ & 1)) failed = true;
         relayout();                                        // dy: tile -> the same planes
@@ -252,16 +264,9 @@ small7_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         float acc[kMaxTaps], db = 0.f;
 #pragma unroll
         for (int k = 0; k < kMaxTaps; k++) acc[k] = 0.f;
-        switch (line) {
-            case 0: small_plane_wgrad<0>(x, mine, acc, db); break;
-            case 1: small_plane_wgrad<1>(x, mine, acc, db); break;
-            case 2: small_plane_wgrad<2>(x, mine, acc, db); break;
-            case 3: small_plane_wgrad<3>(x, mine, acc, db); break;
-            case 4: small_plane_wgrad<4>(x, mine, acc, db); break;
-            case 5: small_plane_wgrad<5>(x, mine, acc, db); break;
-            case 6: small_plane_wgrad<6>(x, mine, acc, db); break;
-            default: small_plane_wgrad<7>(x, mine, acc, db); break;
-        }
+        if (kind == KIND_AXIS) small_plane_wgrad<0>(x, mine, acc, db, pm);
+        else if (kind == KIND_SLANT) small_plane_wgrad<1>(x, mine, acc, db, pm);
+        else small_plane_wgrad<2>(x, mine, acc, db, pm);
         // images beyond N are zero-filled tiles: they add nothing.  Sum over the warp's 32 images.
 #pragma unroll
         for (int k = 0; k < kMaxTaps; k++)
@@ -270,9 +275,10 @@ small7_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) db += __shfl_xor_sync(0xffffffffu, db, d);
         float *dst = partial + ((size_t)(blockIdx.x + it * gridDim.x) * CCs + ch) * 32;
-        float mineval = db;                                // lane k keeps tap k, lane 31 the bias gradient
+        float mineval = db;                                // lane k keeps canonical tap k, lane 31 the bias gradient
+        const int stored = (mode & MODE_REV) ? kMaxTaps - 1 - lane : lane;    // stored tap that is canonical tap `lane`
 #pragma unroll
-        for (int k = 0; k < kMaxTaps; k++) if (lane == k) mineval = acc[k];
+        for (int k = 0; k < kMaxTaps; k++) if (stored == k) mineval = acc[k];
         dst[lane] = mineval;
         __syncthreads();                                   // planes are overwritten by the next item's x
     }
