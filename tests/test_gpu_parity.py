@@ -94,6 +94,7 @@ SHAPES = [
     (3, 192, 28, 28, 31, 1, "rr"),
     (3, 384, 14, 14, 31, 1, "model+"),
     (4, 768, 7, 7, 31, 1, "rr"),
+    (35, 64, 7, 7, 13, 1, "model+"),       # 7x7 plane kernels: short kernel, a partly filled second tile of 32 images
     (2, 64, 32, 48, 31, 2, "model"),       # stem-like: stride 2
     (2, 64, 32, 48, 15, 2, "model+"),
     (2, 16, 21, 27, 31, 2, "random"),      # stride 2, odd sizes, arbitrary angles
