@@ -61,11 +61,29 @@ const char *o1d_last_error(void);
  * environment variable at import time, models/convnext.py:16-23.) */
 int o1d_set_route(int route);
 
+/* Kernel family that served the calling thread's last successful o1d_fprop / o1d_dgrad /
+ * o1d_wgrad / o1d_wgrad_static call (O1D_ROUTE_NONE before the first one).  A diagnostic: a
+ * request that a fast family declines lands on the general kernels with the same results but
+ * several times the run time, and this is how a host or a test notices.  Per thread.  (No
+ * counterpart in the reference, whose module either is the specialised one or is not,
+ * models/convnext.py:16-23.) */
+enum {
+    O1D_ROUTE_NONE = -1,
+    O1D_ROUTE_GENERAL = 0,   /* gather kernels: any stride, layout, angle                      */
+    O1D_ROUTE_TILED = 1,     /* restaged channel planes with register windows                  */
+    O1D_ROUTE_DIRECT = 2,    /* TMA halo tiles, one tap list per thread                        */
+    O1D_ROUTE_PLANE7 = 3,    /* 7x7 maps, one channel plane per thread                         */
+    O1D_ROUTE_LINES = 4      /* whole lines per thread (round-robin angle assignment)          */
+};
+int o1d_last_route(void);
+
 /* Reads the device-side failure flag of the current device into *flag_out (0 = healthy,
  * 1 = a kernel gave up waiting for a TMA transfer and its output is invalid).  This call
  * SYNCHRONISES the device; it is a diagnostic, not part of the hot path.  (The reference
  * checks no launch or device errors at all, kernels.h:529,542,555.) */
 int o1d_device_status(int *flag_out);
+/* The same, and resets the flag to 0 afterwards (flag_out may be NULL). */
+int o1d_device_status_clear(int *flag_out);
 
 /* 1 if o1d_fprop would take one of the TMA-staged kernel families (tiled or direct) for this
  * request, 0 if the general kernels.  Lets a host decide whether converting an NCHW tensor
@@ -124,11 +142,14 @@ int o1d_wgrad(const void *dy, const void *x,
 /* Weight gradient without a workspace argument, for callers that are not able to allocate
  * device memory at the call site (plugin sandboxes and framework hooks that forbid it,
  * processes whose memory pool is fixed at start-up, code running under an allocator lock).
- * It has no counterpart in the reference.  Same arithmetic and same results as
- * o1d_wgrad(); the per-block partial sums go to an array of O1D_STATIC_SCRATCH_BYTES that
- * is compiled into the library (each GPU that loads the library keeps that much memory
- * until the process exits).  The call allocates nothing and frees nothing.
- *   - Shapes whose partial sums do not fit are refused with O1D_ERR_UNSUPPORTED and a
+ * It has no counterpart in the reference.  The per-block partial sums go to an array of
+ * O1D_STATIC_SCRATCH_BYTES that is compiled into the library (each GPU that loads the
+ * library keeps that much memory until the process exits).  The call allocates nothing
+ * and frees nothing.  It tries the kernel families in the same order as o1d_wgrad() and
+ * skips one whose partial sums exceed the array, so the result equals o1d_wgrad()'s bit
+ * for bit when both take the same family (o1d_last_route() tells) and otherwise agrees
+ * to rounding: the sums are then taken in a different order.
+ *   - Shapes whose partial sums fit no family are refused with O1D_ERR_UNSUPPORTED and a
  *     message in o1d_last_error(); use o1d_wgrad() with your own workspace for those.
  *   - The first call on each device looks up the array's device address; make that first
  *     call outside of any CUDA stream capture.

@@ -22,7 +22,9 @@ SIGNATURES = {
     "o1d_strerror": (ctypes.c_char_p, [_c_int]),
     "o1d_last_error": (ctypes.c_char_p, []),
     "o1d_set_route": (_c_int, [_c_int]),
+    "o1d_last_route": (_c_int, []),
     "o1d_device_status": (_c_int, [ctypes.POINTER(_c_int)]),
+    "o1d_device_status_clear": (_c_int, [ctypes.POINTER(_c_int)]),
     "o1d_uses_tiled": (_c_int, [_c_void_p] + [_c_int] * 8),
     "o1d_offsets": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p]),
     "o1d_plan_bytes": (_c_size_t, [_c_int, _c_int]),
@@ -53,11 +55,11 @@ def _load() -> ctypes.CDLL:
     if _build.stale():
         try:
             _build.build()
-        except Exception as e:  # no CPU path exists: fail loudly
-            if not os.path.exists(path):
-                raise RuntimeError(
-                    f"libo1d.so is missing and could not be built ({e}); "
-                    "run `python -m oriented1d_b200.build`") from e
+        except Exception as e:  # no CPU path exists, and kernels older than csrc/ must not run
+            what = "is missing" if not os.path.exists(path) else "was built from other sources than csrc/"
+            raise RuntimeError(
+                f"libo1d.so {what} and could not be rebuilt ({e}); "
+                "run `python -m oriented1d_b200.build`") from e
     lib = ctypes.CDLL(path)
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)          # AttributeError if the library lacks a symbol

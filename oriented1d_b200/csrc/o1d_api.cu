@@ -5,6 +5,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <vector>
 
 #include "o1d_common.cuh"
@@ -21,6 +22,7 @@ using namespace o1d;
 namespace {
 
 thread_local char g_err[256] = "";
+thread_local int g_last_route = O1D_ROUTE_NONE;   // kernel family of this thread's last operator call
 int g_force_generic = 0;   // o1d_set_route(): 1 = general kernels only (testing aid)
 int g_prefer = 0;          // o1d_set_route(): 2 = prefer the tiled kernels, 3 = prefer the direct kernels
 
@@ -28,29 +30,45 @@ int cuda_fail(cudaError_t e, const char *what) {
     snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
     return O1D_ERR_CUDA;
 }
+// A tensor map the driver refused although the request passed every documented check.
+int map_fail(const char *what) {
+    snprintf(g_err, sizeof(g_err), "%s: cuTensorMapEncodeTiled failed (CUresult %d)", what, last_encode_result());
+    return O1D_ERR_CUDA;
+}
+// `expr` yields MAP_OK / MAP_NA / MAP_FAIL.
+#define O1D_MAP(expr, what)                         \
+    do {                                            \
+        const int m_ = (expr);                      \
+        if (m_ == MAP_NA) return kNotTiled;         \
+        if (m_ == MAP_FAIL) return map_fail(what);  \
+    } while (0)
+
 #define O1D_CUDA(call)                                              \
     do {                                                            \
         cudaError_t e_ = (call);                                    \
         if (e_ != cudaSuccess) return cuda_fail(e_, #call);         \
     } while (0)
 
+constexpr int kNotTiled = -1;          // "this kernel family does not take the request"
+
 struct DeviceInfo { int sms; int smem_optin; };
 
 // Attributes of the current device, queried once per device.
 int device_info(DeviceInfo *out) {
-    static DeviceInfo cache[64];
-    static bool have[64];
+    static std::atomic<uint64_t> cache[64];      // (sms << 32) | smem_optin; 0 = not yet queried
     int dev = 0;
     O1D_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return O1D_ERR_UNSUPPORTED;
-    if (!have[dev]) {
-        DeviceInfo d;
-        O1D_CUDA(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev));
-        O1D_CUDA(cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-        cache[dev] = d;
-        have[dev] = true;
+    uint64_t v = cache[dev].load(std::memory_order_acquire);
+    if (!v) {
+        int sms = 0, smem = 0;
+        O1D_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        O1D_CUDA(cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        v = ((uint64_t)(uint32_t)sms << 32) | (uint32_t)smem;
+        cache[dev].store(v, std::memory_order_release);
     }
-    *out = cache[dev];
+    out->sms = (int)(v >> 32);
+    out->smem_optin = (int)(v & 0xffffffffu);
     return O1D_OK;
 }
 
@@ -105,6 +123,7 @@ int launch_generic_fprop(const void *x, const float *w, const float *bias, const
             kern<<<grid, kGenericThreads, smem, st>>>((const T *)x, w, bias, pv.cls, pv.taps, ph.ncls, w_staged,
                                                        (T *)y, N, H, W, C, K, stride, P, Q, add_identity);
             O1D_CUDA(cudaGetLastError());
+            g_last_route = O1D_ROUTE_GENERAL;
             return O1D_OK;
         }
     }
@@ -115,6 +134,7 @@ int launch_generic_fprop(const void *x, const float *w, const float *bias, const
         (const T *)x, w, bias, pv.cls, pv.taps, ph.ncls, staged, (T *)y, N, H, W, C, K, stride, P, Q,
         add_identity);
     O1D_CUDA(cudaGetLastError());
+    g_last_route = O1D_ROUTE_GENERAL;
     return O1D_OK;
 }
 
@@ -131,6 +151,7 @@ int launch_generic_dgrad(const void *dy, const float *w, const PlanHeader &ph, c
         (const T *)dy, w, pv.cls, pv.taps, ph.ncls, staged, (T *)dx, N, H, W, C, K, stride, P, Q,
         add_identity);
     O1D_CUDA(cudaGetLastError());
+    g_last_route = O1D_ROUTE_GENERAL;
     return O1D_OK;
 }
 
@@ -162,10 +183,10 @@ int launch_generic_wgrad(const void *dy, const void *x, const PlanHeader &ph, co
     const int tot = C * (K + 1);
     wgrad_final_kernel<<<ceil_div(tot, 256), 256, 0, st>>>(partial, dw, db, C, K, slices);
     O1D_CUDA(cudaGetLastError());
+    g_last_route = O1D_ROUTE_GENERAL;
     return O1D_OK;
 }
 
-constexpr int kNotTiled = -1;
 constexpr int kMaxTiledCtas = 256;   // upper bound on SMs (grid of the persistent kernels)
 
 // Forward / stride-1 input gradient through the tiled kernels; kNotTiled when they do not apply.
@@ -179,12 +200,13 @@ int try_tiled(const void *x, const float *w, const float *bias, const PlanHeader
         return kNotTiled;
     if (((uintptr_t)y & 15) != 0) return kNotTiled;
     CUtensorMap map;
-    if (!make_nhwc_tensor_map(&map, x, N, H, W, C, esize, cfg.p.CC, cfg.p.BR)) return kNotTiled;
+    O1D_MAP(make_nhwc_tensor_map(&map, x, N, H, W, C, esize, cfg.p.CC, cfg.p.BR), "tiled fprop");
     cfg.p.flip = flip;
     cfg.p.add_identity = add_identity;
     PlanView pv = plan_view(plan_dev, ph);
     cudaError_t e = launch_tiled<OP_FPROP>(cfg, dtype, map, w, bias, pv, y, nullptr, st);
     if (e != cudaSuccess) return cuda_fail(e, "tiled fprop launch");
+    g_last_route = O1D_ROUTE_TILED;
     return O1D_OK;
 }
 
@@ -210,11 +232,12 @@ int try_direct(const void *x, const float *w, const float *bias, const PlanHeade
     DirectMaps maps;
     direct_fill_multi(ls, &mp);
     for (int i = 0; i < ls.n; i++)
-        if (!make_direct_tensor_map(&maps.map[i], x, N, H, W, C, esize, ls.cfg[i].p)) return kNotTiled;
+        O1D_MAP(make_direct_tensor_map(&maps.map[i], x, N, H, W, C, esize, ls.cfg[i].p), "direct fprop");
     PlanView pv = plan_view(plan_dev, ph);
     const cudaError_t e = dtype == O1D_F32 ? launch_direct<float>(ls, mp, maps, w, bias, pv, y, st)
                                            : launch_direct<__nv_bfloat16>(ls, mp, maps, w, bias, pv, y, st);
     if (e != cudaSuccess) return cuda_fail(e, "direct fprop launch");
+    g_last_route = O1D_ROUTE_DIRECT;
     return O1D_OK;
 }
 
@@ -228,13 +251,14 @@ int try_small7(const void *x, const float *w, const float *bias, const PlanHeade
     if (!small7_configure(ph, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, &cfg)) return kNotTiled;
     if (((uintptr_t)y & 15) != 0) return kNotTiled;
     CUtensorMap map;
-    if (!make_small7_tensor_map(&map, x, N, C, esize, cfg.p.CCs)) return kNotTiled;
+    O1D_MAP(make_small7_tensor_map(&map, x, N, C, esize, cfg.p.CCs), "7x7 plane fprop");
     cfg.p.flip = flip;
     cfg.p.add_identity = add_identity;
     PlanView pv = plan_view(plan_dev, ph);
     const cudaError_t e = dtype == O1D_F32 ? launch_small7<float>(cfg, map, w, bias, pv.chan, y, st)
                                            : launch_small7<__nv_bfloat16>(cfg, map, w, bias, pv.chan, y, st);
     if (e != cudaSuccess) return cuda_fail(e, "7x7 plane kernel launch");
+    g_last_route = O1D_ROUTE_PLANE7;
     return O1D_OK;
 }
 
@@ -249,8 +273,8 @@ int try_small7_wgrad(const void *dy, const void *x, const PlanHeader &ph, const 
     if (((uintptr_t)workspace & 15) != 0) return kNotTiled;
     if (workspace_bytes < small7_wgrad_partial_bytes(cfg)) return O1D_ERR_WORKSPACE;
     CUtensorMap mx, mdy;
-    if (!make_small7_tensor_map(&mx, x, N, C, esize, cfg.p.CCs)) return kNotTiled;
-    if (!make_small7_tensor_map(&mdy, dy, N, C, esize, cfg.p.CCs)) return kNotTiled;
+    O1D_MAP(make_small7_tensor_map(&mx, x, N, C, esize, cfg.p.CCs), "7x7 plane wgrad (x)");
+    O1D_MAP(make_small7_tensor_map(&mdy, dy, N, C, esize, cfg.p.CCs), "7x7 plane wgrad (dy)");
     PlanView pv = plan_view(plan_dev, ph);
     float *partial = (float *)workspace;
     const cudaError_t e = dtype == O1D_F32 ? launch_small7_wgrad<float>(cfg, mx, mdy, pv.chan, partial, st)
@@ -260,6 +284,7 @@ int try_small7_wgrad(const void *dy, const void *x, const PlanHeader &ph, const 
     small7_wgrad_final_kernel<<<ceil_div(tot, 128), 128, 0, st>>>(partial, dw, db, C, K, cfg.p.CCs, cfg.p.nchunks,
                                                                   cfg.p.tiles_n);
     O1D_CUDA(cudaGetLastError());
+    g_last_route = O1D_ROUTE_PLANE7;
     return O1D_OK;
 }
 
@@ -313,7 +338,7 @@ int try_tiled_wgrad(const void *dy, const void *x, const PlanHeader &ph, const v
     if (((uintptr_t)dy & 15) != 0 || ((uintptr_t)workspace & 15) != 0) return kNotTiled;
     if (workspace_bytes < need) return O1D_ERR_WORKSPACE;
     CUtensorMap map;
-    if (!make_nhwc_tensor_map(&map, x, N, H, W, C, esize, cfg.p.CC, cfg.p.BR)) return kNotTiled;
+    O1D_MAP(make_nhwc_tensor_map(&map, x, N, H, W, C, esize, cfg.p.CC, cfg.p.BR), "tiled wgrad");
     PlanView pv = plan_view(plan_dev, ph);
     float *partial = (float *)workspace;
     cudaError_t e = launch_tiled<OP_WGRAD>(cfg, dtype, map, nullptr, nullptr, pv, const_cast<void *>(dy), partial, st);
@@ -323,6 +348,7 @@ int try_tiled_wgrad(const void *dy, const void *x, const PlanHeader &ph, const v
     tiled_wgrad_final_kernel<<<ceil_div(tot, 128), 128, 0, st>>>(partial, pv.chan, dw, db, C, K, cfg.p.CC, N,
                                                                  cfg.p.total_items, cfg.grid, cfg.p.max_visits, cfg.p.order, mt);
     O1D_CUDA(cudaGetLastError());
+    g_last_route = O1D_ROUTE_TILED;
     return O1D_OK;
 }
 
@@ -341,12 +367,13 @@ int try_direct_dgrad2(const void *dy, const float *w, const PlanHeader &ph, cons
     DirectMaps maps;
     direct_fill_multi(ls, &mp);
     for (int i = 0; i < ls.n; i++)
-        if (!make_direct_tensor_map(&maps.map[i], dy, N, ls.cfg[i].p.H, ls.cfg[i].p.W, C, esize, ls.cfg[i].p))
-            return kNotTiled;
+        O1D_MAP(make_direct_tensor_map(&maps.map[i], dy, N, ls.cfg[i].p.H, ls.cfg[i].p.W, C, esize, ls.cfg[i].p),
+                "direct stride-2 dgrad");
     PlanView pv = plan_view(plan_dev, ph);
     const cudaError_t e = dtype == O1D_F32 ? launch_direct_dgrad2<float>(ls, mp, maps, w, pv, dx, H, W, st)
                                            : launch_direct_dgrad2<__nv_bfloat16>(ls, mp, maps, w, pv, dx, H, W, st);
     if (e != cudaSuccess) return cuda_fail(e, "direct stride-2 dgrad launch");
+    g_last_route = O1D_ROUTE_DIRECT;
     return O1D_OK;
 }
 
@@ -369,8 +396,8 @@ int try_direct_wgrad(const void *dy, const void *x, const PlanHeader &ph, const 
     direct_fill_multi(ls, &mp);
     for (int i = 0; i < ls.n; i++) {
         const DirectParams &p = ls.cfg[i].p;
-        if (!make_direct_tensor_map(&maps.map[i], x, N, H, W, C, esize, p)) return kNotTiled;
-        if (!make_direct_dy_tensor_map(&dym.map[i], dy, N, p.P, p.Q, C, esize, p)) return kNotTiled;
+        O1D_MAP(make_direct_tensor_map(&maps.map[i], x, N, H, W, C, esize, p), "direct wgrad (x)");
+        O1D_MAP(make_direct_dy_tensor_map(&dym.map[i], dy, N, p.P, p.Q, C, esize, p), "direct wgrad (dy)");
     }
     PlanView pv = plan_view(plan_dev, ph);
     float *partial = (float *)workspace;
@@ -380,6 +407,7 @@ int try_direct_wgrad(const void *dy, const void *x, const PlanHeader &ph, const 
     const int tot = C * (K + 1);
     direct_wgrad_final_kernel<<<ceil_div(tot, 128), 128, 0, st>>>(mp, partial, pv.cls, pv.taps, dw, db, C, K);
     O1D_CUDA(cudaGetLastError());
+    g_last_route = O1D_ROUTE_DIRECT;
     return O1D_OK;
 }
 
@@ -409,6 +437,8 @@ const char *o1d_strerror(int status) {
 
 const char *o1d_last_error(void) { return g_err; }
 
+int o1d_last_route(void) { return g_last_route; }
+
 int o1d_set_route(int route) {
     if (route < 0 || route > 3) return O1D_ERR_INVALID;
     g_force_generic = (route == 1);
@@ -419,6 +449,17 @@ int o1d_set_route(int route) {
 int o1d_device_status(int *flag_out) {
     if (!flag_out) return O1D_ERR_INVALID;
     O1D_CUDA(cudaMemcpyFromSymbol(flag_out, g_o1d_device_error, sizeof(int)));
+    return O1D_OK;
+}
+
+int o1d_device_status_clear(int *flag_out) {
+    int flag = 0;
+    O1D_CUDA(cudaMemcpyFromSymbol(&flag, g_o1d_device_error, sizeof(int)));
+    if (flag) {
+        const int zero = 0;
+        O1D_CUDA(cudaMemcpyToSymbol(g_o1d_device_error, &zero, sizeof(int)));
+    }
+    if (flag_out) *flag_out = flag;
     return O1D_OK;
 }
 
@@ -586,28 +627,29 @@ int o1d_dgrad(const void *dy, const float *w, const void *plan_host, const void 
 size_t o1d_wgrad_workspace_bytes(int N, int H, int W, int C, int K, int stride, int layout, int dtype) {
     if (bad_common(N, H, W, C, K, stride, layout, dtype)) return 0;
     const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
-    // Large enough for either route: the general kernels' slices, and (an upper bound that
-    // needs no plan) one partial per tiled CTA and chunk visit.
+    // Large enough for every kernel family, without needing the plan: the general kernels' slices;
+    // one partial per persistent CTA and chunk visit (tiled and direct kernels, an upper bound);
+    // one partial per (channel, tile of 32 images) for the 7x7 plane kernels.
     const size_t general = (size_t)generic_wgrad_slices(N, P, Q, C, layout) * C * (K + 1) * sizeof(float);
     const size_t tiled = (size_t)kMaxTiledCtas * 4 * kMaxCC * kPartialStride * sizeof(float);
-    return general > tiled ? general : tiled;
+    const size_t plane7 = (H == 7 && W == 7) ? (size_t)C * ceil_div(N, kSmallImgs) * 32 * sizeof(float) : 0;
+    size_t need = general > tiled ? general : tiled;
+    if (plane7 > need) need = plane7;
+    return need;
 }
 
-int o1d_wgrad(const void *dy, const void *x, const void *plan_host, const void *plan_dev, float *dw,
-              float *db, void *workspace, size_t workspace_bytes, int N, int H, int W, int C, int K,
-              int stride, int layout, int dtype, void *stream) {
-    if (!dy || !x || !dw || !plan_dev || bad_common(N, H, W, C, K, stride, layout, dtype)) return O1D_ERR_INVALID;
-    PlanHeader ph;
-    int rc = check_plan(plan_host, C, K, &ph);
-    if (rc) return rc;
-    if (!workspace || workspace_bytes < o1d_wgrad_workspace_bytes(N, H, W, C, K, stride, layout, dtype))
-        return O1D_ERR_WORKSPACE;
-    cudaStream_t st = (cudaStream_t)stream;
-    DeviceInfo d;
-    if ((rc = device_info(&d))) return rc;
-    // Small maps: the direct kernels first (measured at batch 128: fp32 28x28 120 vs 142 us, 14x14 75 vs
-    // 84, 7x7 33 vs 59; bf16 only at 7x7, 40 vs 64, since every 2-byte load needs a widening shift).
-    // Otherwise tiled, then direct (stems, dense-prediction maps, arbitrary angles), then general.
+}  // extern "C"
+
+namespace {
+// Weight gradient with `workspace_bytes` of scratch at `workspace`: each kernel family in the order
+// of preference, skipping a family whose partial sums do not fit.  Small maps: the direct kernels
+// first (measured at batch 128: fp32 28x28 120 vs 142 us, 14x14 75 vs 84, 7x7 33 vs 59; bf16 only at
+// 7x7, 40 vs 64, since every 2-byte load needs a widening shift).  Otherwise tiled, then direct
+// (stems, dense-prediction maps, arbitrary angles), then general.
+int wgrad_dispatch(const void *dy, const void *x, const PlanHeader &ph, const void *plan_host, const void *plan_dev,
+                   float *dw, float *db, void *workspace, size_t workspace_bytes, int N, int H, int W, int C, int K,
+                   int stride, int layout, int dtype, cudaStream_t st, const DeviceInfo &d) {
+    int rc;
     if (g_prefer == 0) {       // 7x7 maps on canonical lines: a channel plane per thread
         rc = try_small7_wgrad(dy, x, ph, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K, stride, layout,
                               dtype, st, d);
@@ -635,8 +677,33 @@ int o1d_wgrad(const void *dy, const void *x, const void *plan_host, const void *
                               stride, layout, dtype, st, d, nullptr);
         if (rc != kNotTiled && rc != O1D_ERR_WORKSPACE) return rc;
     }
+    const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
+    const size_t need = (size_t)generic_wgrad_slices(N, P, Q, C, layout) * C * (K + 1) * sizeof(float);
+    if (need > workspace_bytes) {
+        snprintf(g_err, sizeof(g_err), "weight gradient needs %zu bytes of scratch, %zu are available", need,
+                 workspace_bytes);
+        return O1D_ERR_WORKSPACE;
+    }
     return O1D_DISPATCH(launch_generic_wgrad, dy, x, ph, plan_dev, dw, db, (float *)workspace, N, H, W,
                         C, K, stride, st);
+}
+}  // namespace
+
+extern "C" {
+
+int o1d_wgrad(const void *dy, const void *x, const void *plan_host, const void *plan_dev, float *dw,
+              float *db, void *workspace, size_t workspace_bytes, int N, int H, int W, int C, int K,
+              int stride, int layout, int dtype, void *stream) {
+    if (!dy || !x || !dw || !plan_dev || bad_common(N, H, W, C, K, stride, layout, dtype)) return O1D_ERR_INVALID;
+    PlanHeader ph;
+    int rc = check_plan(plan_host, C, K, &ph);
+    if (rc) return rc;
+    if (!workspace || workspace_bytes < o1d_wgrad_workspace_bytes(N, H, W, C, K, stride, layout, dtype))
+        return O1D_ERR_WORKSPACE;
+    DeviceInfo d;
+    if ((rc = device_info(&d))) return rc;
+    return wgrad_dispatch(dy, x, ph, plan_host, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K, stride,
+                          layout, dtype, (cudaStream_t)stream, d);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -656,23 +723,28 @@ int o1d_wgrad(const void *dy, const void *x, const void *plan_host, const void *
 // ---------------------------------------------------------------------------------------
 static __device__ __align__(256) unsigned char g_wgrad_static_scratch[O1D_STATIC_SCRATCH_BYTES];
 
+}  // extern "C"
+
 namespace {
-// Device address of the static scratch on the current device; resolved on first use.
+// Device address of the static scratch on the current device; resolved on first use.  Threads
+// that race on a device's first use each look the address up and publish the same value.
 int static_scratch_ptr(void **out) {
-    static void *cache[64];
+    static std::atomic<void *> cache[64];
     int dev = 0;
     O1D_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return O1D_ERR_UNSUPPORTED;
-    if (!cache[dev]) {
-        void *ptr = nullptr;
+    void *ptr = cache[dev].load(std::memory_order_acquire);
+    if (!ptr) {
         O1D_CUDA(cudaGetSymbolAddress(&ptr, g_wgrad_static_scratch));
         if (!ptr) return O1D_ERR_CUDA;
-        cache[dev] = ptr;
+        cache[dev].store(ptr, std::memory_order_release);
     }
-    *out = cache[dev];
+    *out = ptr;
     return O1D_OK;
 }
 }  // namespace
+
+extern "C" {
 
 int o1d_wgrad_static(const void *dy, const void *x, const void *plan_host, const void *plan_dev, float *dw,
                      float *db, int N, int H, int W, int C, int K, int stride, int layout, int dtype,
@@ -685,26 +757,16 @@ int o1d_wgrad_static(const void *dy, const void *x, const void *plan_host, const
     if ((rc = device_info(&d))) return rc;
     void *scratch = nullptr;
     if ((rc = static_scratch_ptr(&scratch))) return rc;
-    cudaStream_t st = (cudaStream_t)stream;
-    // tiled route, if it applies and its partials fit
-    size_t need = 0;
-    rc = try_tiled_wgrad(dy, x, ph, plan_host, plan_dev, dw, db, nullptr, 0, N, H, W, C, K, stride, layout, dtype,
-                         st, d, &need);
-    if (rc == O1D_OK && need <= (size_t)O1D_STATIC_SCRATCH_BYTES) {
-        rc = try_tiled_wgrad(dy, x, ph, plan_host, plan_dev, dw, db, scratch, O1D_STATIC_SCRATCH_BYTES, N, H, W, C,
-                             K, stride, layout, dtype, st, d, nullptr);
-        if (rc != kNotTiled) return rc;
-    }
-    // general route
-    const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
-    need = (size_t)generic_wgrad_slices(N, P, Q, C, layout) * C * (K + 1) * sizeof(float);
-    if (need > (size_t)O1D_STATIC_SCRATCH_BYTES) {
-        snprintf(g_err, sizeof(g_err), "o1d_wgrad_static: needs %zu bytes of scratch, the built-in array holds %d",
-                 need, O1D_STATIC_SCRATCH_BYTES);
+    // Same order of kernel families as o1d_wgrad(); a family whose partial sums exceed the array
+    // is skipped, and when even the general kernels' do not fit the request is refused.
+    rc = wgrad_dispatch(dy, x, ph, plan_host, plan_dev, dw, db, scratch, O1D_STATIC_SCRATCH_BYTES, N, H, W, C, K,
+                        stride, layout, dtype, (cudaStream_t)stream, d);
+    if (rc == O1D_ERR_WORKSPACE) {
+        snprintf(g_err, sizeof(g_err), "o1d_wgrad_static: the partial sums of this shape do not fit the built-in "
+                 "array of %d bytes; use o1d_wgrad() with a workspace", O1D_STATIC_SCRATCH_BYTES);
         return O1D_ERR_UNSUPPORTED;
     }
-    return O1D_DISPATCH(launch_generic_wgrad, dy, x, ph, plan_dev, dw, db, (float *)scratch, N, H, W, C, K, stride,
-                        st);
+    return rc;
 }
 
 }  // extern "C"

@@ -178,33 +178,21 @@ inline bool direct_configure_dgrad2(const PlanHeader &ph, const void *plan_host,
 }
 
 // 4-D tensor map over an NHWC tensor with a box CCs x TWp x THp x NI.
-inline bool make_direct_tensor_map(CUtensorMap *map, const void *base, int N, int H, int W, int C, int esize,
-                                   const DirectParams &p) {
-    PFN_encodeTiled enc = encode_tiled_fn();
-    if (!enc || ((uintptr_t)base & 15) || (C * esize) % 16 != 0) return false;
-    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
-    cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)W * C * esize, (cuuint64_t)H * W * C * esize};
-    cuuint32_t box[4] = {(cuuint32_t)p.CCs, (cuuint32_t)p.TWp, (cuuint32_t)p.THp, (cuuint32_t)p.NI};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    return enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
-               const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+inline int make_direct_tensor_map(CUtensorMap *map, const void *base, int N, int H, int W, int C, int esize,
+                                  const DirectParams &p) {
+    const cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    const cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)W * C * esize, (cuuint64_t)H * W * C * esize};
+    const cuuint32_t box[4] = {(cuuint32_t)p.CCs, (cuuint32_t)p.TWp, (cuuint32_t)p.THp, (cuuint32_t)p.NI};
+    return encode_map4(map, base, esize, dims, strides, box);
 }
 
 // 4-D tensor map over dy [N][P][Q][C] with a box CCs x Tq x Th x NI.
-inline bool make_direct_dy_tensor_map(CUtensorMap *map, const void *base, int N, int P, int Q, int C, int esize,
-                                      const DirectParams &p) {
-    PFN_encodeTiled enc = encode_tiled_fn();
-    if (!enc || ((uintptr_t)base & 15) || (C * esize) % 16 != 0) return false;
-    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)Q, (cuuint64_t)P, (cuuint64_t)N};
-    cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)Q * C * esize, (cuuint64_t)P * Q * C * esize};
-    cuuint32_t box[4] = {(cuuint32_t)p.CCs, (cuuint32_t)p.Tq, (cuuint32_t)p.Th, (cuuint32_t)p.NI};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    return enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
-               const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+inline int make_direct_dy_tensor_map(CUtensorMap *map, const void *base, int N, int P, int Q, int C, int esize,
+                                     const DirectParams &p) {
+    const cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)Q, (cuuint64_t)P, (cuuint64_t)N};
+    const cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)Q * C * esize, (cuuint64_t)P * Q * C * esize};
+    const cuuint32_t box[4] = {(cuuint32_t)p.CCs, (cuuint32_t)p.Tq, (cuuint32_t)p.Th, (cuuint32_t)p.NI};
+    return encode_map4(map, base, esize, dims, strides, box);
 }
 
 // The launches of one call: a single range over all chunks when one tile then holds a whole image

@@ -327,17 +327,11 @@ inline bool small7_configure(const PlanHeader &ph, int N, int H, int W, int C, i
 }
 
 // 4-D tensor map over an NHWC tensor [N][7][7][C] with a box CCs x 7 x 7 x 32 images.
-inline bool make_small7_tensor_map(CUtensorMap *map, const void *base, int N, int C, int esize, int CCs) {
-    PFN_encodeTiled enc = encode_tiled_fn();
-    if (!enc || ((uintptr_t)base & 15) || (C * esize) % 16 != 0) return false;
-    cuuint64_t dims[4] = {(cuuint64_t)C, 7, 7, (cuuint64_t)N};
-    cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)7 * C * esize, (cuuint64_t)49 * C * esize};
-    cuuint32_t box[4] = {(cuuint32_t)CCs, 7, 7, (cuuint32_t)kSmallImgs};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    return enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
-               const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+inline int make_small7_tensor_map(CUtensorMap *map, const void *base, int N, int C, int esize, int CCs) {
+    const cuuint64_t dims[4] = {(cuuint64_t)C, 7, 7, (cuuint64_t)N};
+    const cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)7 * C * esize, (cuuint64_t)49 * C * esize};
+    const cuuint32_t box[4] = {(cuuint32_t)CCs, 7, 7, (cuuint32_t)kSmallImgs};
+    return encode_map4(map, base, esize, dims, strides, box);
 }
 
 template <typename T>

@@ -350,20 +350,61 @@ inline bool tiled_configure(const PlanHeader &ph, const void *plan_host, int N, 
     return true;
 }
 
-// 4-D tensor map over an NHWC tensor: dims (C, W, H, N), box (CC, W, BR, 1).
-inline bool make_nhwc_tensor_map(CUtensorMap *map, const void *base, int N, int H, int W, int C, int esize,
-                                 int CC, int BR) {
+// Outcome of building a tensor map: it was built, the request is outside what a tiled copy can
+// describe (the caller moves on to the next kernel family), or the driver refused a request that
+// should have been valid (reported to the caller as O1D_ERR_CUDA, never as a silent fallback).
+enum : int { MAP_OK = 0, MAP_NA = 1, MAP_FAIL = 2 };
+
+// CUresult of the last failed encode on this thread (-1: the driver entry point was not found).
+inline int &last_encode_result() {
+    thread_local int r = 0;
+    return r;
+}
+
+__global__ void context_probe_kernel() {}
+
+// Makes the device's primary context current on the calling thread.  The encode below is a driver
+// API call; on a thread that has only ever made runtime calls which need no context (a framework's
+// backward worker, for instance) it can run before any context is bound.  Querying a kernel's
+// attributes forces the runtime to bind one, is not a stream operation and is legal during capture.
+inline void bind_primary_context() {
+    cudaFuncAttributes a;
+    (void)cudaFuncGetAttributes(&a, context_probe_kernel);
+}
+
+// 4-D tiled tensor map, dims/box innermost first, strides in bytes for dims 1..3.
+inline int encode_map4(CUtensorMap *map, const void *base, int esize, const cuuint64_t (&dims)[4],
+                       const cuuint64_t (&strides)[3], const cuuint32_t (&box)[4]) {
+    if ((uintptr_t)base & 15) return MAP_NA;
+    for (int i = 0; i < 4; i++)
+        if (box[i] == 0 || box[i] > 256 || dims[i] == 0 || dims[i] > 0xffffffffull) return MAP_NA;
+    for (int i = 0; i < 3; i++)
+        if (strides[i] % 16 != 0 || strides[i] >= (1ull << 40)) return MAP_NA;
+    if ((box[0] * (cuuint64_t)esize) % 16 != 0) return MAP_NA;
+    thread_local bool bound = false;
+    if (!bound) { bind_primary_context(); bound = true; }
     PFN_encodeTiled enc = encode_tiled_fn();
-    if (!enc || ((uintptr_t)base & 15)) return false;
-    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
-    cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)W * C * esize, (cuuint64_t)H * W * C * esize};
-    cuuint32_t box[4] = {(cuuint32_t)CC, (cuuint32_t)W, (cuuint32_t)BR, 1};
+    if (!enc) { last_encode_result() = -1; return MAP_FAIL; }
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
-                     const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    CUresult r = CUDA_SUCCESS;
+    for (int attempt = 0; attempt < 2; attempt++) {
+        r = enc(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r == CUDA_SUCCESS) return MAP_OK;
+        bind_primary_context();
+    }
+    last_encode_result() = (int)r;
+    return MAP_FAIL;
+}
+
+// 4-D tensor map over an NHWC tensor: dims (C, W, H, N), box (CC, W, BR, 1).
+inline int make_nhwc_tensor_map(CUtensorMap *map, const void *base, int N, int H, int W, int C, int esize,
+                                int CC, int BR) {
+    const cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    const cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)W * C * esize, (cuuint64_t)H * W * C * esize};
+    const cuuint32_t box[4] = {(cuuint32_t)CC, (cuuint32_t)W, (cuuint32_t)BR, 1};
+    return encode_map4(map, base, esize, dims, strides, box);
 }
 
 template <typename T, int R, int JH, int OP>

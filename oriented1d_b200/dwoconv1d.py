@@ -123,14 +123,18 @@ class DepthwiseOrientedConv1d(nn.Conv2d):
         self._angles_fp32 = self.theta.detach().clone().reshape(-1)
         self._plan = None
         self._plan_key = None
+        self._plan_src = None
         if arbitrary_size:
             self.forward = self.forward_safe
 
     # -- plan cache -------------------------------------------------------------------
     def _get_plan(self) -> ops.Plan:
         th = self.theta
+        # the key holds the tensor that backs the parameter: a new tensor swapped in through
+        # `theta.data = ...` can then never reuse the old one's address while the plan lives
         key = (th._version, th.data_ptr(), th.dtype)
-        if self._plan is None or key != self._plan_key:
+        if self._plan is None or key != self._plan_key or self._plan_src is not th.data.untyped_storage():
+            self._plan_src = th.data.untyped_storage()
             if th.dtype == torch.float32:
                 angles = th.detach().reshape(-1)
             else:
@@ -172,12 +176,17 @@ class _KernelModule:
         self._plans: dict = {}
 
     def _plan(self, theta) -> ops.Plan:
+        """Plan of these angles.  A cache entry keeps the storage of the tensor it was built from
+        alive, so the allocator cannot hand that address to a later tensor with other angles;
+        a hit therefore means the same memory at the same version, i.e. the same values."""
         key = (theta.data_ptr(), theta._version, theta.numel())
-        p = self._plans.get(key)
-        if p is None:
-            if len(self._plans) > 64:
-                self._plans.clear()
-            p = self._plans[key] = ops.Plan(theta, self.K)
+        hit = self._plans.get(key)
+        if hit is not None:
+            return hit[1]
+        if len(self._plans) > 64:
+            self._plans.clear()
+        p = ops.Plan(theta, self.K)
+        self._plans[key] = (theta.detach().untyped_storage(), p)
         return p
 
     def fprop(self, x, w, theta):

@@ -79,12 +79,23 @@ def _dims(t: torch.Tensor, nhwc: bool):
     return n, c, h, w
 
 
+def _check_params(plan: Plan, C: int, w=None, bias=None) -> None:
+    """The kernels index w as [C, K] and bias as [C]: a shorter buffer would be read past its end."""
+    if plan.C != C:
+        raise ValueError(f"plan was built for {plan.C} channels, tensor has {C}")
+    if w is not None and w.numel() != C * plan.K:
+        raise ValueError(f"weight has {w.numel()} elements, expected C*K = {C * plan.K}")
+    if bias is not None and bias.numel() != C:
+        raise ValueError(f"bias has {bias.numel()} elements, expected C = {C}")
+
+
 def fprop(x, w, bias, plan: Plan, stride: int = 1, nhwc: bool = False, add_identity: bool = False):
     """y = oriented conv of x.  x: [N,C,H,W] (or [N,H,W,C] if nhwc), contiguous."""
-    _need_cuda(x, w, bias)
-    x = x.contiguous()
     N, C, H, W = _dims(x, nhwc)
     K = plan.K
+    _check_params(plan, C, w, bias)
+    _need_cuda(x, w, bias)
+    x = x.contiguous()
     w32 = w.detach().reshape(C, K).to(torch.float32).contiguous()
     b32 = bias.detach().to(torch.float32).contiguous() if bias is not None else None
     P, Q = -(-H // stride), -(-W // stride)
@@ -100,12 +111,13 @@ def fprop(x, w, bias, plan: Plan, stride: int = 1, nhwc: bool = False, add_ident
 def dgrad(dy, w, plan: Plan, H: int, W: int, stride: int = 1, nhwc: bool = False,
           add_identity: bool = False):
     """dx [.., H, W ..] from dy [.., ceil(H/s), ceil(W/s) ..]."""
-    _need_cuda(dy, w)
-    dy = dy.contiguous()
     N, C, P, Q = _dims(dy, nhwc)
     if P != -(-H // stride) or Q != -(-W // stride):
         raise ValueError("dy extents do not match ceil(H/stride) x ceil(W/stride)")
     K = plan.K
+    _check_params(plan, C, w)
+    _need_cuda(dy, w)
+    dy = dy.contiguous()
     w32 = w.detach().reshape(C, K).to(torch.float32).contiguous()
     dx = torch.empty((N, H, W, C) if nhwc else (N, C, H, W), dtype=dy.dtype, device=dy.device)
     with torch.cuda.device(dy.device):
@@ -117,12 +129,17 @@ def dgrad(dy, w, plan: Plan, H: int, W: int, stride: int = 1, nhwc: bool = False
 
 def wgrad(dy, x, plan: Plan, stride: int = 1, nhwc: bool = False, with_bias: bool = False):
     """(dw [C,1,1,K] fp32, db [C] fp32 or None).  Deterministic."""
-    _need_cuda(dy, x)
-    dy, x = dy.contiguous(), x.contiguous()
     if dy.dtype != x.dtype:
         raise TypeError("dy and x must have the same dtype")
     N, C, H, W = _dims(x, nhwc)
     K = plan.K
+    _check_params(plan, C)
+    P, Q = -(-H // stride), -(-W // stride)
+    if tuple(dy.shape) != ((N, P, Q, C) if nhwc else (N, C, P, Q)):
+        raise ValueError(f"dy has shape {tuple(dy.shape)}, expected the output shape of x "
+                         f"({(N, P, Q, C) if nhwc else (N, C, P, Q)})")
+    _need_cuda(dy, x)
+    dy, x = dy.contiguous(), x.contiguous()
     code = _dtype_code(x)
     dw = torch.empty((C, 1, 1, K), dtype=torch.float32, device=x.device)
     db = torch.empty((C,), dtype=torch.float32, device=x.device) if with_bias else None
@@ -205,10 +222,21 @@ def set_route(route) -> None:
     check(lib.o1d_set_route(int(route)), "o1d_set_route")
 
 
-def device_status(device=None) -> int:
-    """Device-side failure flag (0 = healthy).  Synchronises the device."""
+ROUTE_NAMES = {-1: "none", 0: "general", 1: "tiled", 2: "direct", 3: "plane7", 4: "lines"}
+
+
+def last_route() -> str:
+    """Kernel family that served this thread's last fprop / dgrad / wgrad call."""
+    return ROUTE_NAMES[lib.o1d_last_route()]
+
+
+def device_status(device=None, clear: bool = False) -> int:
+    """Device-side failure flag (0 = healthy).  Synchronises the device.  ``clear`` resets it."""
     import ctypes
     flag = ctypes.c_int(0)
     with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
-        check(lib.o1d_device_status(ctypes.byref(flag)), "o1d_device_status")
+        if clear:
+            check(lib.o1d_device_status_clear(ctypes.byref(flag)), "o1d_device_status_clear")
+        else:
+            check(lib.o1d_device_status(ctypes.byref(flag)), "o1d_device_status")
     return flag.value

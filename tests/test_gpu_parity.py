@@ -149,8 +149,18 @@ def _pad_for_stride(dy, x, s):
     return dy, xp
 
 
-@pytest.mark.parametrize("shape", [SHAPES[0], SHAPES[2], SHAPES[4], SHAPES[5], SHAPES[8]],
-                         ids=lambda s: "x".join(map(str, s[:6])) + s[6])
+BF16_SHAPES = [SHAPES[0], SHAPES[2], SHAPES[4], SHAPES[5], SHAPES[8],
+               SHAPES[1],                              # 56x56, block-wise angles
+               (3, 384, 14, 14, 31, 1, "model+"),
+               (3, 384, 14, 14, 31, 1, "rr"),
+               (3, 192, 28, 28, 31, 1, "model"),
+               (2, 768, 7, 7, 31, 1, "model+"),
+               (1, 96, 50, 80, 27, 1, "model+"),       # dense-prediction map (row/column tiles)
+               (2, 64, 32, 48, 31, 2, "model"),        # stem: stride 2, even/odd channel pairs share a line
+               (2, 64, 32, 48, 15, 2, "model+")]
+
+
+@pytest.mark.parametrize("shape", BF16_SHAPES, ids=lambda s: "x".join(map(str, s[:6])) + s[6])
 @pytest.mark.parametrize("nhwc", [False, True], ids=["nchw", "nhwc"])
 def test_bf16_parity(oracle, shape, nhwc):
     N, C, H, W, K, s, mode = shape
@@ -240,10 +250,11 @@ def test_module_arbitrary_size_and_bf16_theta(oracle):
 
 
 @pytest.mark.parametrize("hw,C", [(56, 96), (28, 192), (14, 384), (7, 768)])
-def test_full_size_properties(hw, C):
+def test_full_size_properties(oracle, hw, C):
     """Batch-128 stage shapes, where the CPU oracle would take minutes: size-independent
     properties instead — linearity in x, exact adjointness identities between the three
-    kernels, and agreement of a sampled sub-batch with the rest."""
+    kernels, agreement of a sampled sub-batch with the rest — and the oracle itself on two
+    images cut out of the full-batch results."""
     N, K = 128, 31
     g = torch.Generator(device="cpu").manual_seed(hw)
     plan = o1d.Plan(angle_list("rr", C), K)
@@ -267,6 +278,17 @@ def test_full_size_properties(hw, C):
     # the batch is independent per image: a 2-image slice reproduces its part bit for bit
     ys = o1d.fprop(x1[5:7].contiguous(), w, None, plan, 1, True)
     assert torch.equal(ys, y1[5:7])
+    # ... and those two images of the full-batch run are what the oracle computes
+    th = angle_list("rr", C)
+    xs, dys, wn = (_to_nchw(t, True) for t in (x1[5:7], dy[5:7])) + (w.cpu().numpy(),)
+    assert rel_err(_to_nchw(y1[5:7], True), oracle.fprop(xs, wn, th, 1)) <= TOL_FPROP
+    assert rel_err(_to_nchw(dx[5:7], True), oracle.dgrad(dys, wn, th, 1)) <= TOL_DGRAD
+    dws, _ = o1d.wgrad(dy[5:7].contiguous(), x1[5:7].contiguous(), plan, 1, True, True)
+    assert rel_err(dws.cpu().numpy(), oracle.wgrad_f64(dys, xs, th, K, 1)) <= TOL_WGRAD
+    # the full-batch weight gradient is the sum over images: two slices of 64 add up to it
+    dwa, _ = o1d.wgrad(dy[:64].contiguous(), x1[:64].contiguous(), plan, 1, True, True)
+    dwb, _ = o1d.wgrad(dy[64:].contiguous(), x1[64:].contiguous(), plan, 1, True, True)
+    assert float((dw - (dwa + dwb)).abs().max()) <= 1e-5 * float(dw.abs().max())
 
 
 @pytest.mark.parametrize("hw,C,mode", [(56, 96, "rr"), (56, 96, "model"), (28, 192, "rr"), (28, 192, "model+"),
@@ -286,15 +308,23 @@ def test_tiled_route_equals_general_route(hw, C, mode, dtype):
     try:
         o1d.ops.set_route(True)
         y_ref = o1d.fprop(x, w, bias, plan, 1, True, True).float()
+        assert o1d.ops.last_route() == "general"
         dx_ref = o1d.dgrad(x, w, plan, hw, hw, 1, True, False).float()
+        assert o1d.ops.last_route() == "general"
         dw_ref, db_ref = o1d.wgrad(dy, x, plan, 1, True, True)
+        assert o1d.ops.last_route() == "general"
     finally:
         o1d.ops.set_route(False)
+    # which family must answer: a fast path that declines would otherwise compare the general
+    # kernels with themselves
+    want = {2: ("tiled",), 3: ("direct",), 0: ("tiled", "direct", "plane7", "lines")}
     for route in (2, 3, 0):          # tiled preferred, direct preferred, automatic
         try:
             o1d.ops.set_route(route)
             y = o1d.fprop(x, w, bias, plan, 1, True, True).float()
+            assert o1d.ops.last_route() in want[route], (route, o1d.ops.last_route())
             dx = o1d.dgrad(x, w, plan, hw, hw, 1, True, False).float()
+            assert o1d.ops.last_route() in want[route], (route, o1d.ops.last_route())
         finally:
             o1d.ops.set_route(0)
         assert o1d.ops.device_status() == 0
@@ -308,6 +338,7 @@ def test_tiled_route_equals_general_route(hw, C, mode, dtype):
         try:
             o1d.ops.set_route(route)
             dw, db = o1d.wgrad(dy, x, plan, 1, True, True)
+            assert o1d.ops.last_route() in want[route], (route, o1d.ops.last_route())
             dw2, db2 = o1d.wgrad(dy, x, plan, 1, True, True)
         finally:
             o1d.ops.set_route(0)
@@ -362,6 +393,41 @@ def test_nchw_module_takes_the_tiled_route(oracle):
     assert rel_err(xd.grad.cpu().numpy(), rdx) <= TOL_DGRAD
     assert rel_err(m.weight.grad.cpu().numpy(), oracle.wgrad_f64(dy, x, th, K, 1)) <= TOL_WGRAD
     assert rel_err(m.bias.grad.cpu().numpy(), rdb) <= TOL_WGRAD
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_module_forward_and_backward_stay_on_fast_kernels(dtype):
+    """Forward and backward of the nn.Module at a stage shape: every one of the three kernels
+    must come from a fast family.  Backward runs on autograd's own worker thread, so the route
+    is recorded from inside a tensor hook on that thread."""
+    N, C, hw, K = 2, 96, 56, 31
+    m = o1d.DepthwiseOrientedConv1d(C, C, K, groups=C, padding=K // 2, nhwc=True,
+                                    angle=[float(a) for a in angle_list("rr", C)]).to(DEV)
+    x = torch.randn((N, hw, hw, C), device=DEV).to(dtype).requires_grad_(True)
+    seen = {}
+    orig_dgrad, orig_wgrad = o1d.ops.dgrad, o1d.ops.wgrad
+
+    def dgrad(*a, **k):
+        out = orig_dgrad(*a, **k)
+        seen["dgrad"] = o1d.ops.last_route()
+        return out
+
+    def wgrad(*a, **k):
+        out = orig_wgrad(*a, **k)
+        seen["wgrad"] = o1d.ops.last_route()
+        return out
+
+    o1d.ops.dgrad, o1d.ops.wgrad = dgrad, wgrad
+    try:
+        y = m(x)
+        seen["fprop"] = o1d.ops.last_route()
+        y.backward(torch.randn_like(y))
+        torch.cuda.synchronize()
+    finally:
+        o1d.ops.dgrad, o1d.ops.wgrad = orig_dgrad, orig_wgrad
+    assert set(seen) == {"fprop", "dgrad", "wgrad"}
+    assert all(v in ("tiled", "lines") for v in seen.values()), seen
+    assert o1d.ops.device_status() == 0
 
 
 DENSE = [

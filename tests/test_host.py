@@ -142,6 +142,68 @@ def test_module_surface_matches_reference():
     assert torch.equal(m4.theta, m.theta)
 
 
+def test_shape_mismatches_raise_before_any_launch():
+    """A dy, weight or bias that does not match x would be read past its end on the device."""
+    plan = o1d.Plan(np.zeros(8, np.float32), 7)
+    x = torch.zeros(2, 8, 6, 6)
+    w = torch.zeros(8, 1, 1, 7)
+    with pytest.raises(ValueError, match="dy has shape"):
+        o1d.wgrad(torch.zeros(2, 8, 6, 5), x, plan)
+    with pytest.raises(ValueError, match="dy has shape"):
+        o1d.wgrad(torch.zeros(1, 8, 6, 6), x, plan)
+    with pytest.raises(ValueError, match="bias"):
+        o1d.fprop(x, w, torch.zeros(7), plan)
+    with pytest.raises(ValueError, match="weight"):
+        o1d.fprop(x, torch.zeros(8, 1, 1, 5), None, plan)
+    with pytest.raises(ValueError, match="channels"):
+        o1d.fprop(torch.zeros(2, 4, 6, 6), w, None, plan)
+    with pytest.raises(ValueError, match="dy extents"):
+        o1d.dgrad(torch.zeros(2, 8, 3, 3), w, plan, 6, 6, 1)
+    m = o1d.get_dwoconv1d_kernel("float", 7, 1, 3)
+    with pytest.raises(ValueError, match="dy has shape"):
+        m.wgrad(torch.zeros(2, 8, 6, 5), x, torch.zeros(8))
+
+
+def test_plan_cache_does_not_outlive_its_angles():
+    """The 5-callable module caches plans per theta tensor.  A second tensor with other angles
+    must get its own plan even if the allocator reuses the first one's address."""
+    m = o1d.get_dwoconv1d_kernel("float", 31, 1, 15)
+    seen = []
+    for angle in (0.0, np.pi / 4, np.pi / 2):
+        th = torch.full((16,), angle, dtype=torch.float32)
+        plan = m._plan(th)
+        dh, dw = o1d.offsets(th.numpy(), 31)
+        hdr = plan.host[:64].view(torch.int32).tolist()
+        taps = plan.host[hdr[8]:hdr[8] + 31 * 2].view(torch.int8).numpy().reshape(31, 2)
+        assert np.array_equal(taps[:, 0], dh[0]) and np.array_equal(taps[:, 1], dw[0]), angle
+        assert m._plan(th) is plan                      # same tensor, same version: cached
+        seen.append(th.data_ptr())
+        del th
+    # in-place change of the same tensor: version moves, the plan follows
+    th = torch.zeros(16)
+    p0 = m._plan(th)
+    th.fill_(np.pi / 2)
+    p1 = m._plan(th)
+    assert p1 is not p0
+    hdr = p1.host[:64].view(torch.int32).tolist()
+    assert hdr[4] == 15 and hdr[5] == 0                   # vertical line: max |dh| 15, max |dw| 0
+    # the nn.Module: swapping theta.data rebuilds the plan
+    mod = o1d.DepthwiseOrientedConv1d(8, 8, 31, groups=8, padding=15, angle=[0.0] * 8)
+    a = mod._get_plan()
+    mod.theta.data = torch.full((8,), float(np.pi / 2))
+    b = mod._get_plan()
+    assert b is not a and b.host[:64].view(torch.int32).tolist()[4] == 15
+
+
+def test_last_route_starts_unset():
+    import threading
+    out = []
+    t = threading.Thread(target=lambda: out.append(_lib.lib.o1d_last_route()))
+    t.start(); t.join()
+    assert out == [-1]                                    # per thread, no call made yet
+    assert o1d.ops.ROUTE_NAMES[-1] == "none"
+
+
 def test_cpu_tensors_are_refused():
     m = o1d.DepthwiseOrientedConv1d(8, 8, 7, groups=8, padding=3, angle=0.0)
     with pytest.raises(RuntimeError, match="CUDA"):
