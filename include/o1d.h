@@ -56,7 +56,8 @@ const char *o1d_strerror(int status);
 const char *o1d_last_error(void);
 
 /* Kernel routing, for tests and A/B timing: 0 = automatic, 1 = general kernels only,
- * 2 = prefer the tiled kernels, 3 = prefer the direct kernels.  Process-wide.  (No counterpart in
+ * 2 = prefer the tiled kernels, 3 = prefer the direct kernels, 4 = prefer the whole-line
+ * kernels.  Process-wide.  (No counterpart in
  * the reference, which picks general vs specialised kernels with the SPECIALIZED
  * environment variable at import time, models/convnext.py:16-23.) */
 int o1d_set_route(int route);

@@ -1,8 +1,8 @@
 """In-tree build of libo1d.so (sm_100a only).
 
-``python -m oriented1d_b200.build`` compiles ``csrc/o1d_api.cu`` with nvcc into
-``oriented1d_b200/libo1d.so``.  nvcc cross-compiles, so this works on a machine
-without a GPU.  The library has no dependency on torch or Python.
+``python -m oriented1d_b200.build`` compiles every ``csrc/*.cu`` with nvcc (one object per
+file, in parallel) and links them into ``oriented1d_b200/libo1d.so``.  nvcc cross-compiles,
+so this works on a machine without a GPU.  The library has no dependency on torch or Python.
 """
 from __future__ import annotations
 
@@ -16,10 +16,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libo1d.so")
 
+OBJ_DIR = os.path.join(HERE, "_obj")
+
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC",
 ]
 
 
@@ -55,14 +57,46 @@ def stale() -> bool:
         return f.read().strip() != source_digest()
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not (force or stale()):
-        return LIB
-    cmd = [nvcc(), *NVCC_FLAGS, "-o", LIB, *sources()]
+def _file_digest(src: str) -> str:
+    """Hash of one source file together with every header it could include."""
+    import hashlib
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    deps = [src] + sorted(glob.glob(os.path.join(CSRC, "*.cuh"))) + sorted(glob.glob(os.path.join(CSRC, "*.h")))
+    deps.append(os.path.join(HERE, "..", "include", "o1d.h"))
+    for d in deps:
+        h.update(os.path.basename(d).encode())
+        with open(d, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def _compile_one(src: str, force: bool, verbose: bool) -> str:
+    obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
+    tag = obj + ".digest"
+    digest = _file_digest(src)
+    if not force and os.path.exists(obj) and os.path.exists(tag):
+        with open(tag) as f:
+            if f.read().strip() == digest:
+                return obj
+    cmd = [nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
         print(" ".join(cmd))
     subprocess.run(cmd, check=True)
+    with open(tag, "w") as f:
+        f.write(digest)
+    return obj
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not (force or stale()):
+        return LIB
+    from concurrent.futures import ThreadPoolExecutor
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    srcs = sources()
+    with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 1)) as pool:
+        objs = list(pool.map(lambda s: _compile_one(s, force, verbose), srcs))
+    subprocess.run([nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs], check=True)
     with open(LIB + ".digest", "w") as f:
         f.write(source_digest())
     return LIB

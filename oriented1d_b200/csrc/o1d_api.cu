@@ -16,6 +16,7 @@
 #include "o1d_layernorm.cuh"
 #include "o1d_transpose.cuh"
 #include "o1d_pointwise.cuh"
+#include "o1d_wline.h"
 
 using namespace o1d;
 
@@ -24,7 +25,7 @@ namespace {
 thread_local char g_err[256] = "";
 thread_local int g_last_route = O1D_ROUTE_NONE;   // kernel family of this thread's last operator call
 int g_force_generic = 0;   // o1d_set_route(): 1 = general kernels only (testing aid)
-int g_prefer = 0;          // o1d_set_route(): 2 = prefer the tiled kernels, 3 = prefer the direct kernels
+int g_prefer = 0;          // o1d_set_route(): 2 = prefer the tiled kernels, 3 = direct, 4 = whole-line
 
 int cuda_fail(cudaError_t e, const char *what) {
     snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
@@ -288,6 +289,48 @@ int try_small7_wgrad(const void *dy, const void *x, const PlanHeader &ph, const 
     return O1D_OK;
 }
 
+// Device address of the failure flag on the current device (kernels of other translation units
+// receive it as a pointer); resolved on first use.
+int device_flag_ptr(int **out) {
+    static std::atomic<int *> cache[64];
+    int dev = 0;
+    O1D_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return O1D_ERR_UNSUPPORTED;
+    int *ptr = cache[dev].load(std::memory_order_acquire);
+    if (!ptr) {
+        O1D_CUDA(cudaGetSymbolAddress((void **)&ptr, g_o1d_device_error));
+        if (!ptr) return O1D_ERR_CUDA;
+        cache[dev].store(ptr, std::memory_order_release);
+    }
+    *out = ptr;
+    return O1D_OK;
+}
+
+// Forward / stride-1 input gradient through the whole-line kernels (square stage maps, canonical
+// lines, fp32); kNotTiled when they do not apply.
+int try_wline(const void *x, const float *w, const float *bias, const PlanHeader &ph, const void *plan_host,
+              const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride, int layout, int dtype,
+              int add_identity, int flip, cudaStream_t st, const DeviceInfo &d, bool need_two_ctas) {
+    if (g_force_generic || !ph.all_canon || ph.chan_off == 0) return kNotTiled;
+    const int esize = dtype == O1D_F32 ? 4 : 2;
+    const int8_t *chan_host = reinterpret_cast<const int8_t *>(static_cast<const char *>(plan_host) + ph.chan_off);
+    WlConfig cfg;
+    if (!wline_configure(chan_host, N, H, W, C, K, stride, layout, esize, 228 * 1024, d.smem_optin, d.sms, &cfg))
+        return kNotTiled;
+    if (need_two_ctas && cfg.ctas_per_sm < 2) return kNotTiled;
+    if (((uintptr_t)y & 15) != 0) return kNotTiled;
+    CUtensorMap map;
+    O1D_MAP(make_nhwc_tensor_map(&map, x, N, H, W, C, esize, cfg.box_c, cfg.box_rows), "whole-line fprop");
+    int *flag = nullptr;
+    int rc = device_flag_ptr(&flag);
+    if (rc) return rc;
+    PlanView pv = plan_view(plan_dev, ph);
+    const cudaError_t e = wline_launch_fprop(cfg, map, w, bias, pv.chan, (float *)y, flip, add_identity, flag, st);
+    if (e != cudaSuccess) return cuda_fail(e, "whole-line fprop launch");
+    g_last_route = O1D_ROUTE_LINES;
+    return O1D_OK;
+}
+
 // Route of a forward-type call (flip = 1: stride-1 input gradient):
 //   1. direct kernels when one tile holds a whole image (small maps),
 //   2. tiled kernels (canonical lines, stride 1, sizes in multiples of 7/8),
@@ -297,6 +340,11 @@ int route_forward(const void *x, const float *w, const float *bias, const PlanHe
                   const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride, int layout,
                   int dtype, int add_identity, int flip, cudaStream_t st, const DeviceInfo &d) {
     int rc = kNotTiled;
+    if (g_prefer == 0 || g_prefer == 4) {   // stage maps with whole lines per thread
+        rc = try_wline(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
+                       flip, st, d, /*need_two_ctas=*/g_prefer == 0);
+        if (rc != kNotTiled) return rc;
+    }
     if (g_prefer == 0) {       // 7x7 maps on canonical lines: a channel plane per thread
         rc = try_small7(x, w, bias, ph, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity, flip, st, d);
         if (rc != kNotTiled) return rc;
@@ -440,7 +488,7 @@ const char *o1d_last_error(void) { return g_err; }
 int o1d_last_route(void) { return g_last_route; }
 
 int o1d_set_route(int route) {
-    if (route < 0 || route > 3) return O1D_ERR_INVALID;
+    if (route < 0 || route > 4) return O1D_ERR_INVALID;
     g_force_generic = (route == 1);
     g_prefer = (route >= 2) ? route : 0;
     return O1D_OK;

@@ -81,4 +81,4 @@ def test_static_scratch_refuses_what_does_not_fit():
     db = torch.empty((C,), device=dev)
     rc = _call_static(x, x, plan, dw, db, N, H, W, C, K, 1, True, _lib.F32)
     assert rc == 2
-    assert b"scratch" in _lib.lib.o1d_last_error()
+    assert b"built-in array" in _lib.lib.o1d_last_error()
