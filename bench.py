@@ -570,7 +570,7 @@ def run_case(args):
 
 
 def run_model(args):
-    """ConvNeXt-T-1D inference (BASELINE.json configs[2]): depths 3/3/9/3, dims 96..768, K=31
+    """ConvNeXt-T-1D full-model inference: depths 3/3/9/3, dims 96..768, K=31
     oriented convs in every block and in the stem, 1000 classes, random init, bf16, batch 256
     per GPU of synthetic N(0,1) 224x224 images, batch-sharded over the GPUs with no collective."""
     import torch

@@ -6,8 +6,8 @@ Two artefacts, both kept out of version control:
 * ``oracle/_ref/libo1d_ref.so`` — the reference's own CPU operator
   (models/dwoconv1d_reference/kernels/kernels.cpp), compiled where it lies in the
   reference checkout through ``ref_shim.cpp``.  Only built when a reference checkout
-  is present (``O1D_REFERENCE_ROOT`` or the default location); elsewhere the
-  prebuilt file is used as is.
+  is present (``O1D_REFERENCE_ROOT``, or a directory named ``reference`` beside this
+  repository); elsewhere the prebuilt file is used as is.
 
 Run ``python oracle/build.py`` to (re)build both.
 """
@@ -25,8 +25,14 @@ REF_SO = os.path.join(REF_DIR, "libo1d_ref.so")
 REF_SUBDIR = os.path.join("models", "dwoconv1d_reference", "kernels")
 
 
+def _checkout() -> str:
+    """Where a reference checkout would be: O1D_REFERENCE_ROOT, else `reference` beside this repository."""
+    beside = os.path.normpath(os.path.join(HERE, os.pardir, os.pardir, "reference"))
+    return os.environ.get("O1D_REFERENCE_ROOT", beside)
+
+
 def reference_root() -> str | None:
-    root = os.environ.get("O1D_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+    root = _checkout()
     return root if os.path.isfile(os.path.join(root, REF_SUBDIR, "kernels.cpp")) else None
 
 
@@ -81,8 +87,7 @@ def build_refgpu(force: bool = False) -> str | None:
     """Compile the reference's specialised CUDA kernels (kernels.h, nhwc_utils.h) for sm_100a
     through refgpu_shim.cu; None if there is no checkout.  Several minutes: the reference
     fully unrolls its kernels per shape."""
-    root = os.environ.get("O1D_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
-    src_dir = os.path.join(root, REFGPU_SUBDIR)
+    src_dir = os.path.join(_checkout(), REFGPU_SUBDIR)
     if not os.path.isfile(os.path.join(src_dir, "kernels.h")):
         return REFGPU_SO if os.path.exists(REFGPU_SO) else None
     shim = os.path.join(HERE, "refgpu_shim.cu")

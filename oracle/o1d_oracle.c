@@ -18,7 +18,7 @@
  * single fp32 accumulator in the reference carries ~1e-5 relative error of its own.
  *
  * Parity status: pinned.  tests/golden/ holds outputs of the reference's own
- * kernels.cpp (compiled by oracle/build_ref.py) and tests/test_oracle.py checks this
+ * kernels.cpp (compiled by oracle/build.py) and tests/test_oracle.py checks this
  * file against them bit for bit.
  */
 #include <math.h>

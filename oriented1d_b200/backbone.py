@@ -31,9 +31,11 @@ from .dwoconv1d import DepthwiseOrientedConv1d
 __all__ = ["ConvNeXt1DBackbone", "backbone_tiny", "backbone_base", "convert_classifier_state_dict",
            "BACKBONE_BLOCK_KERNELS", "BACKBONE_STEM_KERNEL"]
 
-BACKBONE_BLOCK_KERNELS = {"1d": [[31], [31], [27], [13]],                       # backbone/convnext.py:316-321
+BACKBONE_BLOCK_KERNELS = {"2d": [[7], [7], [7], [7]],                           # backbone/convnext.py:315-320
+                          "2dpp": [[7, 31], [7, 31], [7, 27], [7, 13]],
+                          "1d": [[31], [31], [27], [13]],
                           "1dpp": [[15, 31], [15, 31], [15, 27], [13, 13]]}
-BACKBONE_STEM_KERNEL = {"1d": 31, "1dpp": 15}                                   # backbone/convnext.py:322-327
+BACKBONE_STEM_KERNEL = {"2d": 4, "2dpp": 4, "1d": 31, "1dpp": 15}               # backbone/convnext.py:321-326
 
 
 class ConvWrapper(nn.Module):
@@ -56,7 +58,7 @@ def _wrap_convs(module):
 
 
 class ConvNeXt1DBackbone(ConvNeXt1D):
-    """backbone/convnext.py:329-447 for variant in {"1d", "1dpp"}: images [N,3,H,W] of any size
+    """backbone/convnext.py:329-447, every variant: images [N,3,H,W] of any size
     -> tuple of normalised stage maps [N,C_i,ceil(H/4/2^i),ceil(W/4/2^i)] for i in out_indices."""
 
     def __init__(self, in_chans=3, depths=(3, 3, 9, 3), dims=(96, 192, 384, 768), drop_path_rate=0.0,
@@ -116,6 +118,9 @@ def convert_classifier_state_dict(state_dict, variant="1d"):
             continue
         new_key = f"{m.group(1)}.conv.{m.group(3)}"
         s = _STAGE_KEY.match(key)
+        if val.dim() == 4 and val.shape[2] != 1:          # a 7x7 depthwise conv of the 2D / 2D++ blocks: not wrapped
+            out[key] = val
+            continue
         if s and val.dim() == 4 and val.shape[2] == 1:
             want = kernels[int(s.group(1))][1 if s.group(2) == "dwconv2" else 0]
             have = val.shape[-1]

@@ -1,9 +1,9 @@
-"""ConvNeXt-1D / ConvNeXt-1D++ built on the oriented 1D depthwise convolution.
+"""ConvNeXt-1D / 1D++ / 2D++ (and plain 2D) built on the oriented 1D depthwise convolution.
 
 The caller side of the hot path: a timm-free restatement of the reference model
 (``models/convnext.py``: angle helpers :60-77, ``get_convolution_1d`` :80-128, ``Stem1D``
-:132-191, ``Block1D`` :255-319, ``Block1DPP`` :322-399, ``ConvNeXt`` :495-610, factories
-:613-644) with the same module tree and therefore the same state-dict keys and shapes
+:132-191, ``Block2D`` :195-252, ``Block1D`` :255-319, ``Block1DPP`` :322-399, ``Block2DPP``
+:402-475, ``ConvNeXt`` :495-610, factories :613-644) with the same module tree and therefore the same state-dict keys and shapes
 (``downsample_layers.0.dw1.weight [64,1,1,31]``, ``stages.0.0.dwconv.theta [96]`` ...), so
 reference checkpoints load with ``load_state_dict``.
 
@@ -29,8 +29,8 @@ from .dwoconv1d import DepthwiseOrientedConv1d
 
 __all__ = ["ConvNeXt1D", "convnext_tiny", "convnext_base", "get_convolution_1d"]
 
-BLOCK_KERNELS = {"1d": [[31]] * 4, "1dpp": [[15, 31]] * 4}     # convnext.py:483-488
-STEM_KERNEL = {"1d": 31, "1dpp": 15}                           # convnext.py:490
+BLOCK_KERNELS = {"2d": [[7]] * 4, "2dpp": [[7, 31]] * 4, "1d": [[31]] * 4, "1dpp": [[15, 31]] * 4}   # convnext.py:483-488
+STEM_KERNEL = {"2d": 4, "2dpp": 4, "1d": 31, "1dpp": 15}                                             # convnext.py:490
 
 
 def channel_cycle_offset(c, C, N):
@@ -154,6 +154,62 @@ class Block1DPP(Block1D):
         return self._residual(x, y)
 
 
+class Block2D(Block1D):
+    """convnext.py:195-252: the plain ConvNeXt block (7x7 depthwise conv); channels-last in and out.
+    The library conv runs on the NCHW view of the same memory (channels_last strides, no copy)."""
+
+    def __init__(self, dim, kernel_sizes=(7,), N=0, drop_path=0.0, layer_scale_init_value=1e-6, layer_offset=0,
+                 arbitrary_size=False):
+        nn.Module.__init__(self)
+        self.dwconv = nn.Conv2d(dim, dim, kernel_size=kernel_sizes[0], padding=kernel_sizes[0] // 2, groups=dim)
+        self.norm = LayerNorm(dim)
+        self.pwconv1 = nn.Linear(dim, 4 * dim)
+        self.pwconv2 = nn.Linear(4 * dim, dim)
+        self.gamma = (nn.Parameter(layer_scale_init_value * torch.ones(dim)) if layer_scale_init_value > 0 else None)
+        self.drop_path = drop_path
+
+    def _dw2d(self, conv, x):
+        return conv(x.permute(0, 3, 1, 2)).permute(0, 2, 3, 1)
+
+    def forward(self, x):
+        y = self.pwconv2(self._mlp_in(self._dw2d(self.dwconv, x)))
+        return self._residual(x, y)
+
+
+class Block2DPP(Block2D):
+    """convnext.py:402-475: 7x7 depthwise conv, then the oriented conv (K=31, identity tap, NHWC) on
+    the 4*dim hidden tensor."""
+
+    def __init__(self, dim, kernel_sizes=(7, 31), N=8, drop_path=0.0, layer_scale_init_value=1e-6,
+                 layer_offset=0, arbitrary_size=False):
+        assert len(kernel_sizes) == 2
+        super().__init__(dim, kernel_sizes[:1], N, drop_path, layer_scale_init_value, layer_offset, arbitrary_size)
+        self.dwconv1 = self.dwconv                     # reference names: dwconv1, dwconv2
+        del self.dwconv
+        self.dwconv2 = get_convolution_1d(4 * dim, kernel_size=kernel_sizes[1], padding=kernel_sizes[1] // 2,
+                                          nhwc=True, resid=True, N=N, layer_offset=layer_offset,
+                                          arbitrary_size=arbitrary_size)
+
+    def forward(self, x):
+        y = self._mlp_in(self._dw2d(self.dwconv1, x)).contiguous()
+        return self._residual(x, self.pwconv2(self.dwconv2(y)))
+
+
+class Stem2D(nn.Sequential):
+    """convnext.py:525-529: 4x4 stride-4 patchify conv + LayerNorm; image [N,3,H,W] in, channels-last out."""
+
+    def __init__(self, cin, cout):
+        super().__init__(nn.Conv2d(cin, cout, kernel_size=4, stride=4), LayerNorm(cout, data_format="channels_first"))
+
+    def forward(self, x, nchw_input=True):
+        if not nchw_input:
+            x = x.permute(0, 3, 1, 2)
+        return self[1](self[0](x).permute(0, 2, 3, 1).contiguous())
+
+
+BLOCKS = {"2d": Block2D, "2dpp": Block2DPP, "1d": Block1D, "1dpp": Block1DPP}      # convnext.py:477-482
+
+
 def _drop_path(y, rate, training):
     """Stochastic depth per sample (timm DropPath semantics, as used at convnext.py:292)."""
     if rate == 0.0 or not training:
@@ -177,18 +233,20 @@ class Downsample(nn.Sequential):
 
 
 class ConvNeXt1D(nn.Module):
-    """convnext.py:495-610 for variant in {"1d", "1dpp"}."""
+    """convnext.py:495-610, all four variants ("2d", "2dpp", "1d", "1dpp")."""
 
     def __init__(self, in_chans=3, num_classes=1000, depths=(3, 3, 9, 3), dims=(96, 192, 384, 768),
                  drop_path_rate=0.0, layer_scale_init_value=1e-6, head_init_scale=1.0, variant="1d", N=8,
                  stem_dim1=64, arbitrary_size=False, block_kernels=None, stem_kernel=None):
         super().__init__()
-        assert variant in ("1d", "1dpp")
-        Block = Block1D if variant == "1d" else Block1DPP
+        assert variant in BLOCKS
+        Block = BLOCKS[variant]
         block_kernels = BLOCK_KERNELS[variant] if block_kernels is None else block_kernels
         stem_kernel = STEM_KERNEL[variant] if stem_kernel is None else stem_kernel
-        self.downsample_layers = nn.ModuleList([Stem1D(in_chans, stem_dim1, dims[0], stem_kernel, 1,
-                                                       arbitrary_size)])
+        cycle = int(variant != "2d")                   # enable_layer_cycle, convnext.py:523
+        stem = (Stem2D(in_chans, dims[0]) if variant in ("2d", "2dpp")
+                else Stem1D(in_chans, stem_dim1, dims[0], stem_kernel, cycle, arbitrary_size))
+        self.downsample_layers = nn.ModuleList([stem])
         for i in range(3):
             self.downsample_layers.append(Downsample(dims[i], dims[i + 1]))
         rates = torch.linspace(0, drop_path_rate, sum(depths)).tolist()
@@ -198,7 +256,7 @@ class ConvNeXt1D(nn.Module):
             self.stages.append(nn.Sequential(*[
                 Block(dims[i], kernel_sizes=block_kernels[i], N=N, drop_path=rates[cur + j],
                       layer_scale_init_value=layer_scale_init_value,
-                      layer_offset=layer_wise_rotation_offset(j, 1), arbitrary_size=arbitrary_size)
+                      layer_offset=layer_wise_rotation_offset(j, cycle), arbitrary_size=arbitrary_size)
                 for j in range(depths[i])]))
             cur += depths[i]
         self.norm = nn.LayerNorm(dims[-1], eps=1e-6)

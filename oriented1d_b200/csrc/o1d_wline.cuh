@@ -167,7 +167,7 @@ __device__ __forceinline__ ChanMap make_map(int o, int off, int halo, int hi, in
 
 __device__ __forceinline__ int map_addr(const ChanMap &m, int hb, int wb, int Lside) {
     int a = m.a * hb + m.b * wb + m.c;
-    if (4 * hb + m.tb * wb + m.tc >= Lside) a += m.wrapfix;
+    if (m.wrapfix != 0 && 4 * hb + m.tb * wb + m.tc >= Lside) a += m.wrapfix;     // wrapped diagonals only
     return a;
 }
 
@@ -193,63 +193,73 @@ __device__ __forceinline__ void merge_weights(float (&w)[kMaxTaps]) {
 }
 
 // ---- compute bodies --------------------------------------------------------------------------------
-// AXIS: out[o] = sum_j w[j+15] * x[o+j] along one storage row of length L, in place.
-template <int L, int JH>
-__device__ __forceinline__ void axis_row(float *__restrict__ sm, int rb, const float (&w)[kMaxTaps]) {
-    float x[L];
+// Every body evaluates HALF of its outputs and is run twice: the second half is the first half of
+// the mirrored problem (positions counted from the far end of the row, rows from the far end of the
+// plane), which for these odd-symmetric lines is the same arithmetic with the weights read in
+// reverse order.  That halves the unrolled code (the instruction cache is what limits these
+// kernels' size) while a tap that would fall off the near end of a row still vanishes at compile
+// time and the far end needs no test.
+
+// Reversed copy of the 31 original weights (tap k <-> tap 30-k).
+__device__ __forceinline__ void reverse_weights(const float (&w)[kMaxTaps], float (&wr)[kMaxTaps]) {
 #pragma unroll
-    for (int i = 0; i < L; i++) x[i] = sm[rb + i];
-    constexpr int CH = 8;
-    static_for<0, L / CH>([&](auto ci) {
-        constexpr int o0 = decltype(ci)::value * CH;
-        float acc[CH];
-#pragma unroll
-        for (int o = 0; o < CH; o++) acc[o] = 0.f;
-        static_for<0, 2 * JH + 1>([&](auto ji) {
-            constexpr int j = decltype(ji)::value - JH;
-#pragma unroll
-            for (int o = 0; o < CH; o++)
-                if (o0 + o + j >= 0 && o0 + o + j < L) acc[o] = fmaf(w[j + kHalf], x[o0 + o + j], acc[o]);
-        });
-#pragma unroll
-        for (int o = 0; o < CH; o++) sm[rb + o0 + o] = acc[o];
-    });
+    for (int k = 0; k < kMaxTaps; k++) wr[k] = w[kMaxTaps - 1 - k];
 }
 
-// DIAG: the same along a wrapped diagonal row of length L + kGap whose columns rho+1 .. rho+kGap
-// are the gap (kept zero: results there are not written back).
-template <int L, int JH>
-__device__ __forceinline__ void diag_row(float *__restrict__ sm, int rb, int rho, const float (&w)[kMaxTaps]) {
-    using P = LP<KIND_DIAG, JH>;
-    constexpr int LD = Geo<L>::LD;
-    float x[LD];
+// AXIS / DIAG: 1-D convolution along storage rows of length ROW, in place.  A lane works through
+// `nrows` rows (row0, row0 + row_step, ..) x 2 halves.  Each half loads a window of ROW/2 + reach
+// inputs once, and holds its ROW/2 results back until the next window has been read, because the
+// next window may overlap the columns they overwrite.  KIND_DIAG rows hold two diagonals separated
+// by kGap zeros at columns rho+1 .. rho+kGap; results there are not written, so the gap stays zero.
+template <int KIND, int JH, int ROW>
+__device__ __forceinline__ void rows_in_place(float *__restrict__ sm, const RowBase &rb, int row0, int row_step,
+                                              int nrows, const float (&w)[kMaxTaps], const float (&wr)[kMaxTaps]) {
+    using P = LP<KIND, JH>;
+    constexpr int HALF = ROW / 2;
+    constexpr int REACH = (KIND == KIND_DIAG) ? kGap : JH;
+    constexpr int WN = (HALF + REACH < ROW) ? HALF + REACH : ROW;
+    static_assert(ROW % 2 == 0, "rows are processed in two halves");
+    float pend[HALF];
+    int pend_at = 0, pend_dir = 0, pend_c0 = 0, pend_rho = 0;
+#pragma unroll 1
+    for (int it = 0; it < 2 * nrows; it++) {
+        const int rho = row0 + (it >> 1) * row_step;
+        const bool mirror = (it & 1) != 0;
+        const int c0 = mirror ? ROW - 1 : 0, dir = mirror ? -1 : 1;
+        const int at = rb(rho) + c0;
+        float x[WN];
 #pragma unroll
-    for (int i = 0; i < LD; i++) x[i] = sm[rb + i];
-    constexpr int CH = 6;
-    static_assert(LD % CH == 0 || true, "");
-    static_for<0, (LD + CH - 1) / CH>([&](auto ci) {
-        constexpr int o0 = decltype(ci)::value * CH;
-        constexpr int n = (LD - o0 < CH) ? LD - o0 : CH;
-        float acc[CH];
+        for (int i = 0; i < WN; i++) x[i] = sm[at + dir * i];
+        if (it > 0) {
 #pragma unroll
-        for (int o = 0; o < CH; o++) acc[o] = 0.f;
+            for (int o = 0; o < HALF; o++) {
+                const int col = pend_c0 + pend_dir * o;
+                if (KIND != KIND_DIAG || col <= pend_rho || col > pend_rho + kGap) sm[pend_at + pend_dir * o] = pend[o];
+            }
+        }
+        float wv[kMaxTaps];
+#pragma unroll
+        for (int k = 0; k < kMaxTaps; k++) wv[k] = mirror ? wr[k] : w[k];
+#pragma unroll
+        for (int o = 0; o < HALF; o++) pend[o] = 0.f;
         static_for<0, P::p.ntaps>([&](auto ti) {
             constexpr int t = decltype(ti)::value;
             constexpr int dp = P::p.tap_dp[t], k = P::p.tap_k[t];
 #pragma unroll
-            for (int o = 0; o < n; o++)
-                if (o0 + o + dp >= 0 && o0 + o + dp < LD) acc[o] = fmaf(w[k], x[o0 + o + dp], acc[o]);
+            for (int o = 0; o < HALF; o++)
+                if (o + dp >= 0 && o + dp < WN) pend[o] = fmaf(wv[k], x[o + dp], pend[o]);
         });
+        pend_at = at; pend_dir = dir; pend_c0 = c0; pend_rho = rho;
+    }
 #pragma unroll
-        for (int o = 0; o < n; o++) {
-            const int col = o0 + o;
-            if (col <= rho || col > rho + kGap) sm[rb + col] = acc[o];
-        }
-    });
+    for (int o = 0; o < HALF; o++) {
+        const int col = pend_c0 + pend_dir * o;
+        if (KIND != KIND_DIAG || col <= pend_rho || col > pend_rho + kGap) sm[pend_at + pend_dir * o] = pend[o];
+    }
 }
 
-// SLANT.  Window of storage row (2*rp + e) needed by the outputs (rows 2*rp + m, m = 0, 1, columns
-// C0 .. C0+R-1): the union over m of the taps with line offset d = e - m.
+// SLANT.  Window of (mirrored) storage row 2*rp + e needed by the outputs of rows 2*rp + m, m = 0, 1,
+// columns 0 .. R-1: the union over m of the taps with line offset d = e - m, clipped to the row.
 struct SlWin { int lo, hi; };
 constexpr int slant_find_row(const LinePlan &p, int d) {
     for (int r = 0; r < p.nrows; r++)
@@ -257,64 +267,76 @@ constexpr int slant_find_row(const LinePlan &p, int d) {
     return -1;
 }
 template <int JH>
-constexpr SlWin slant_window(int e, int C0, int R, int L) {
+constexpr SlWin slant_window(int e, int R, int L) {
     const LinePlan &p = LP<KIND_SLANT, JH>::p;
     int lo = 1 << 20, hi = -(1 << 20);
     for (int m = 0; m < 2; m++) {
         const int r = slant_find_row(p, e - m);
         if (r < 0) continue;
-        if (C0 + p.row_lo[r] < lo) lo = C0 + p.row_lo[r];
-        if (C0 + R - 1 + p.row_hi[r] > hi) hi = C0 + R - 1 + p.row_hi[r];
+        if (p.row_lo[r] < lo) lo = p.row_lo[r];
+        if (R - 1 + p.row_hi[r] > hi) hi = R - 1 + p.row_hi[r];
     }
     if (lo < 0) lo = 0;
     if (hi > L - 1) hi = L - 1;
     return SlWin{lo, hi};
 }
 
-// Outputs (2*rp + m, C0 + o), m = 0..1, o = 0..R-1, of a slanted channel.  `in` addresses the input
-// plane (kHaloRows zero rows above and below the image rows), `out` the result plane.
-template <int L, int JH, int C0, int R>
-__device__ __forceinline__ void slant_pass(const float *__restrict__ sm, float *__restrict__ smo, const RowBase &in,
-                                           const RowBase &out, int rp, const float (&w)[kMaxTaps]) {
+// Slanted channel: a lane owns the row pair rp and evaluates, per pass, the outputs of its two rows
+// in the columns 0 .. L/2-1 of the plain (pass 0) or mirrored (pass 1) plane, so that every loaded
+// row segment serves both rows.  `in` addresses the input plane (kHaloRows zero rows above and below
+// the image rows), `out` the result plane (no halo).
+template <int L, int JH>
+__device__ __forceinline__ void slant_rows(const float *__restrict__ sm, float *__restrict__ smo, const RowBase &in,
+                                           const RowBase &out, int rp, const float (&w)[kMaxTaps],
+                                           const float (&wr)[kMaxTaps]) {
     using P = LP<KIND_SLANT, JH>;
-    constexpr int MD = P::p.max_d;
-    float acc[2][R];
+    constexpr int MD = P::p.max_d, R = L / 2;
+#pragma unroll 1
+    for (int pass = 0; pass < 2; pass++) {
+        const bool mirror = pass != 0;
+        const int rs = mirror ? -1 : 1, r0 = mirror ? L - 1 : 0;        // image row = rs * (mirrored row) + r0
+        const int cs = rs, cb = r0;                                     // same for columns
+        float wv[kMaxTaps];
 #pragma unroll
-    for (int m = 0; m < 2; m++)
+        for (int k = 0; k < kMaxTaps; k++) wv[k] = mirror ? wr[k] : w[k];
+        float acc[2][R];
 #pragma unroll
-        for (int o = 0; o < R; o++) acc[m][o] = 0.f;
-    static_for<0, 2 * MD + 2>([&](auto ei) {
-        constexpr int e = decltype(ei)::value - MD;
-        constexpr SlWin wn = slant_window<JH>(e, C0, R, L);
-        if constexpr (wn.hi >= wn.lo) {
-            constexpr int WN = wn.hi - wn.lo + 1;
-            const int base = in(2 * rp + e + kHaloRows) + wn.lo;
-            float win[WN];
+        for (int m = 0; m < 2; m++)
 #pragma unroll
-            for (int i = 0; i < WN; i++) win[i] = sm[base + i];
-            static_for<0, 2>([&](auto mi) {
-                constexpr int m = decltype(mi)::value;
-                constexpr int r = slant_find_row(P::p, e - m);
-                if constexpr (r >= 0) {
-                    static_for<0, P::p.ntaps>([&](auto ti) {
-                        constexpr int t = decltype(ti)::value;
-                        if constexpr (P::p.tap_row[t] == r) {
-                            constexpr int dp = P::p.tap_dp[t], k = P::p.tap_k[t];
+            for (int o = 0; o < R; o++) acc[m][o] = 0.f;
+        static_for<0, 2 * MD + 2>([&](auto ei) {
+            constexpr int e = decltype(ei)::value - MD;
+            constexpr SlWin wn = slant_window<JH>(e, R, L);
+            if constexpr (wn.hi >= wn.lo) {
+                constexpr int WN = wn.hi - wn.lo + 1;
+                const int base = in(rs * (2 * rp + e) + r0 + kHaloRows) + cb + cs * wn.lo;
+                float win[WN];
 #pragma unroll
-                            for (int o = 0; o < R; o++)
-                                if (C0 + o + dp >= 0 && C0 + o + dp < L)
-                                    acc[m][o] = fmaf(w[k], win[C0 + o + dp - wn.lo], acc[m][o]);
-                        }
-                    });
-                }
-            });
+                for (int i = 0; i < WN; i++) win[i] = sm[base + cs * i];
+                static_for<0, 2>([&](auto mi) {
+                    constexpr int m = decltype(mi)::value;
+                    constexpr int r = slant_find_row(P::p, e - m);
+                    if constexpr (r >= 0) {
+                        static_for<0, P::p.ntaps>([&](auto ti) {
+                            constexpr int t = decltype(ti)::value;
+                            if constexpr (P::p.tap_row[t] == r) {
+                                constexpr int dp = P::p.tap_dp[t], k = P::p.tap_k[t];
+#pragma unroll
+                                for (int o = 0; o < R; o++)
+                                    if (o + dp >= wn.lo && o + dp <= wn.hi)
+                                        acc[m][o] = fmaf(wv[k], win[o + dp - wn.lo], acc[m][o]);
+                            }
+                        });
+                    }
+                });
+            }
+        });
+#pragma unroll
+        for (int m = 0; m < 2; m++) {
+            const int ob = out(rs * (2 * rp + m) + r0) + cb;
+#pragma unroll
+            for (int o = 0; o < R; o++) smo[ob + cs * o] = acc[m][o];
         }
-    });
-#pragma unroll
-    for (int m = 0; m < 2; m++) {
-        const int ob = out(2 * rp + m) + C0;
-#pragma unroll
-        for (int o = 0; o < R; o++) smo[ob + o] = acc[m][o];
     }
 }
 
@@ -427,9 +449,11 @@ wline_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__rest
             const int o = o_all[0] * (warp == 0) + o_all[1] * (warp == 1) + o_all[2] * (warp == 2) + o_all[3] * (warp == 3);
             const int in_off = p.in_off[0] * (warp == 0) + p.in_off[1] * (warp == 1) + p.in_off[2] * (warp == 2) +
                                p.in_off[3] * (warp == 3);
-            const int out_off = p.out_off[0] * (warp == 0) + p.out_off[1] * (warp == 1) + p.out_off[2] * (warp == 2) +
-                                p.out_off[3] * (warp == 3);
             const int kind = canon_kind(o);
+            // results of a slanted channel go to its second plane; the other kinds work in place
+            const int out_off = kind != KIND_SLANT ? in_off
+                                                   : p.out_off[0] * (warp == 0) + p.out_off[1] * (warp == 1) +
+                                                         p.out_off[2] * (warp == 2) + p.out_off[3] * (warp == 3);
             float w[kMaxTaps];
             {
                 const float4 *wp = reinterpret_cast<const float4 *>(wts + warp * 32);
@@ -441,18 +465,21 @@ wline_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__rest
                 }
             }
             if (lane < L / 2) {
+                float wr[kMaxTaps];
+                reverse_weights(w, wr);
                 if (kind == KIND_AXIS) {
                     const RowBase rb = row_base_of<L>(o, in_off);
-                    for (int q = 0; q < 2; q++) axis_row<L, JH>(sm, rb(lane + q * (L / 2)), w);
+                    rows_in_place<KIND_AXIS, JH, L>(sm, rb, lane, L / 2, 2, w, wr);
                 } else if (kind == KIND_DIAG) {
                     merge_weights<KIND_DIAG, JH>(w);
+                    merge_weights<KIND_DIAG, JH>(wr);
                     const RowBase rb = row_base_of<L>(o, in_off);
-                    for (int q = 0; q < 2; q++) diag_row<L, JH>(sm, rb(lane + q * (L / 2)), lane + q * (L / 2), w);
+                    rows_in_place<KIND_DIAG, JH, G::LD>(sm, rb, lane, L / 2, 2, w, wr);
                 } else {
                     merge_weights<KIND_SLANT, JH>(w);
+                    merge_weights<KIND_SLANT, JH>(wr);
                     const RowBase in = row_base_of<L>(o, in_off), out = row_base_of<L>(o, out_off);
-                    slant_pass<L, JH, 0, L / 2>(sm, sm, in, out, lane, w);
-                    slant_pass<L, JH, L / 2, L / 2>(sm, sm, in, out, lane, w);
+                    slant_rows<L, JH>(sm, sm, in, out, lane, w, wr);
                 }
             }
         }
@@ -464,7 +491,7 @@ wline_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__rest
             float bv[kCC];
 #pragma unroll
             for (int j = 0; j < kCC; j++) {
-                dmap[j] = make_map<L>(o_all[j], p.out_off[j], 0, hi, wi);
+                dmap[j] = make_map<L>(o_all[j], canon_kind(o_all[j]) == KIND_SLANT ? p.out_off[j] : p.in_off[j], 0, hi, wi);
                 bv[j] = bias ? __ldg(bias + c0 + j) : 0.f;
             }
             float *ybase = y + ((size_t)n * L * L) * p.C + c0;

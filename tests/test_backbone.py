@@ -1,9 +1,35 @@
 """Dense-prediction backbone (cropped kernels, `.conv.` keys, per-stage norms) and the
 classifier -> backbone checkpoint conversion."""
+import json
+import os
+
+import numpy as np
 import pytest
 import torch
 
 from oriented1d_b200 import backbone, convnext1d
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BB_KEYS = json.load(open(os.path.join(ROOT, "tests", "golden", "backbone_keys.json")))
+
+
+@pytest.mark.parametrize("name,factory,variant", [("tiny_1d", backbone.backbone_tiny, "1d"),
+                                                  ("tiny_1dpp", backbone.backbone_tiny, "1dpp"),
+                                                  ("tiny_2dpp", backbone.backbone_tiny, "2dpp"),
+                                                  ("base_1dpp", backbone.backbone_base, "1dpp")])
+def test_backbone_state_dict_matches_reference_file(name, factory, variant):
+    """Keys, shapes, parameter count and angles of the reference's own backbone class
+    (semantic_segmentation/backbone/convnext.py), from the fixture tests/golden/make_model_keys.py
+    wrote by importing that file."""
+    m = factory(variant=variant)
+    mine = {k: list(v.shape) for k, v in m.state_dict().items()}
+    ref = BB_KEYS[name]
+    assert set(mine) == set(ref), sorted(set(mine) ^ set(ref))[:10]
+    assert all(mine[k] == ref[k] for k in ref)
+    assert sum(p.numel() for p in m.parameters()) == BB_KEYS[name + "_params"]
+    sd = m.state_dict()
+    for k, vals in BB_KEYS[name + "_theta_sample"].items():
+        assert np.array_equal(sd[k].flatten()[:16].numpy(), np.array(vals, np.float32)), k
 
 
 def _small(variant, cls):

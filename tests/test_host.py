@@ -227,3 +227,44 @@ def test_bare_module_names_resolve():
         assert len(dwoconv1d.oriented_dwconv1d_get_module_from_params("float", 31, 1, 15, Sb=1)) == 5
     finally:
         sys.path.remove(o1d.compat_path())
+
+
+def test_reference_model_file_runs_on_this_operator():
+    """The reference's own models/convnext.py, unmodified, builds its 1D / 1D++ / 2D++ models with
+    this package answering `import dwoconv1d` — the drop-in claim, exercised where a checkout of
+    the reference exists (skipped elsewhere)."""
+    import sys
+    import types
+    from oracle.build import reference_root
+    from oriented1d_b200 import convnext1d
+    ref = reference_root()
+    if ref is None:
+        pytest.skip("no reference checkout")
+    saved_path, saved_mods = list(sys.path), dict(sys.modules)
+    try:
+        layers = types.ModuleType("timm.models.layers")
+        layers.trunc_normal_ = torch.nn.init.trunc_normal_
+        layers.DropPath = lambda p=0.0: torch.nn.Identity()
+        registry = types.ModuleType("timm.models.registry")
+        registry.register_model = lambda f: f
+        sys.modules.update({"timm": types.ModuleType("timm"), "timm.models": types.ModuleType("timm.models"),
+                            "timm.models.layers": layers, "timm.models.registry": registry})
+        sys.path.insert(0, o1d.compat_path())
+        sys.path.insert(0, ref)
+        for k in [k for k in sys.modules if k == "models" or k.startswith("models.")]:
+            del sys.modules[k]
+        from models import convnext as refmod
+        assert refmod.DepthwiseOrientedConv1d is o1d.DepthwiseOrientedConv1d
+        for variant in ("1d", "1dpp", "2dpp"):
+            m = refmod.ConvNeXt(depths=[1, 1, 1, 1], dims=[16, 32, 48, 64], variant=variant, stem_dim1=8)
+            mine = convnext1d.ConvNeXt1D(depths=(1, 1, 1, 1), dims=(16, 32, 48, 64), variant=variant, stem_dim1=8)
+            assert {k: tuple(v.shape) for k, v in m.state_dict().items()} == \
+                   {k: tuple(v.shape) for k, v in mine.state_dict().items()}
+            mine.load_state_dict(m.state_dict())           # a reference checkpoint loads as is
+            convs = [x for x in m.modules() if isinstance(x, o1d.DepthwiseOrientedConv1d)]
+            assert convs and all(c.kernel_size[1] in (15, 31) for c in convs)
+    finally:
+        sys.path[:] = saved_path
+        for k in list(sys.modules):
+            if k not in saved_mods:
+                del sys.modules[k]

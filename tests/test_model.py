@@ -18,7 +18,9 @@ KEYS = json.load(open(os.path.join(ROOT, "tests", "golden", "convnext_keys.json"
 
 @pytest.mark.parametrize("name,factory,variant", [("tiny_1d", convnext1d.convnext_tiny, "1d"),
                                                   ("tiny_1dpp", convnext1d.convnext_tiny, "1dpp"),
-                                                  ("base_1dpp", convnext1d.convnext_base, "1dpp")])
+                                                  ("base_1dpp", convnext1d.convnext_base, "1dpp"),
+                                                  ("tiny_2dpp", convnext1d.convnext_tiny, "2dpp"),
+                                                  ("tiny_2d", convnext1d.convnext_tiny, "2d")])
 def test_state_dict_layout_matches_reference(name, factory, variant):
     m = factory(variant=variant)
     mine = {k: list(v.shape) for k, v in m.state_dict().items()}
@@ -52,6 +54,10 @@ def _dense_kernel(conv):
 
 
 def _ref_conv(conv, x_nhwc):
+    if not isinstance(conv, o1d.DepthwiseOrientedConv1d):        # the 7x7 depthwise conv of the 2D / 2D++ blocks
+        y = F.conv2d(x_nhwc.permute(0, 3, 1, 2), conv.weight.double(), conv.bias.double(), conv.stride,
+                     conv.padding, 1, conv.groups)
+        return y.permute(0, 2, 3, 1)
     k2d, pad = _dense_kernel(conv)
     y = F.conv2d(x_nhwc.permute(0, 3, 1, 2), k2d, conv.bias.double(), conv.stride, pad, 1,
                  conv.weight.shape[0])
@@ -66,7 +72,10 @@ def _ref_forward(m, img):
     x = img.double().permute(0, 2, 3, 1)
     for i in range(4):
         ds = m.downsample_layers[i]
-        if i == 0:
+        if i == 0 and not hasattr(ds, "pw1"):                    # 4x4 patchify stem (convnext.py:525-529)
+            x = F.conv2d(x.permute(0, 3, 1, 2), d(ds[0].weight), d(ds[0].bias), 4).permute(0, 2, 3, 1)
+            x = ln(ds[1], x)
+        elif i == 0:
             x = lin(ds.pw1, x)
             x = F.gelu(ln(ds.norm1, _ref_conv(ds.dw1, x)))
             x = F.gelu(ln(ds.norm2, _ref_conv(ds.dw2, x)))
@@ -86,7 +95,7 @@ def _ref_forward(m, img):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("variant", ["1d", "1dpp"])
+@pytest.mark.parametrize("variant", ["1d", "1dpp", "2dpp"])
 def test_model_forward_matches_pytorch_restatement(variant):
     torch.manual_seed(0)
     torch.backends.cudnn.allow_tf32 = False        # the 2x2 downsampling convs would run in TF32
@@ -105,7 +114,7 @@ def test_model_forward_matches_pytorch_restatement(variant):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("variant", ["1d", "1dpp"])
+@pytest.mark.parametrize("variant", ["1d", "1dpp", "2dpp"])
 def test_model_training_step_gradients(variant):
     """Forward + backward through the autograd function of every oriented conv in the model
     (stride-2 stems, identity-tap convs of 1D++, every stage size): gradients of all parameters
