@@ -12,25 +12,22 @@ bool configure_side(const int8_t *chan, int N, int C, int K, int smem_per_sm, in
                     WlConfig *cfg) {
     using G = wl::Geo<L>;
     const int nchunks = C / wl::kCC;
-    int in_size[wl::kCC] = {0, 0, 0, 0};
-    bool slant[wl::kCC] = {false, false, false, false};
-    for (int c = 0; c < C; c++) {
-        const int o = chan[c];
-        if (o < 0 || o > 7) return false;
-        const int j = c % wl::kCC, kind = canon_kind(o);
-        const int need = kind == KIND_AXIS ? G::kAxisFloats : kind == KIND_DIAG ? G::kDiagFloats : G::kSlantFloats;
-        if (need > in_size[j]) in_size[j] = need;
-        if (kind == KIND_SLANT) slant[j] = true;
-    }
     int off = 0;
-    for (int j = 0; j < wl::kCC; j++) { cfg->in_off[j] = off; off += in_size[j]; }
-    for (int j = 0; j < wl::kCC; j++) {
-        cfg->out_off[j] = slant[j] ? off : -1;
-        if (slant[j]) off += G::kOutFloats;
+    for (int c0 = 0; c0 < C; c0 += wl::kCC) {
+        int kind[wl::kCC];
+        for (int j = 0; j < wl::kCC; j++) {
+            const int o = chan[c0 + j];
+            if (o < 0 || o > 7) return false;
+            kind[j] = canon_kind(o);
+        }
+        bool ok = true;
+        const int need = wl::chunk_plane_floats<L>(kind, &ok);
+        if (!ok) return false;                 // slanted channels are evaluated in pairs
+        if (need > off) off = need;
     }
     cfg->plane_floats = off;
     cfg->off_wts = (off + 3) & ~3;
-    const int fixed = (((cfg->off_wts + wl::kCC * 32) * 4) + 127) & ~127;
+    const int fixed = (((cfg->off_wts + wl::kCC * 32 + wl::kMapInts + wl::kMaxStages) * 4) + 127) & ~127;
     // two CTAs per SM when they fit with at least two stages; the ring grows into what is left
     int ctas = 0, nstg = 0;
     for (int t = 2; t >= 1 && !ctas; t--) {
@@ -60,9 +57,9 @@ cudaError_t launch_side(const WlConfig &cfg, const CUtensorMap &map, const float
     wl::WlParams p{};
     p.N = cfg.N; p.C = cfg.C; p.K = cfg.K; p.nchunks = cfg.nchunks; p.total_items = cfg.N * cfg.nchunks;
     p.flip = flip; p.add_identity = add_identity;
-    for (int j = 0; j < wl::kCC; j++) { p.in_off[j] = cfg.in_off[j]; p.out_off[j] = cfg.out_off[j]; }
     p.plane_floats = cfg.plane_floats; p.off_wts = cfg.off_wts;
     p.off_stage_bytes = cfg.off_stage_bytes; p.nstg = cfg.nstg; p.off_bar_bytes = cfg.off_bar_bytes;
+    p.step_n = cfg.grid / cfg.nchunks; p.step_chunk = cfg.grid % cfg.nchunks;
     auto kern = wl::wline_fprop_kernel<L, kHalf>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
     if (e != cudaSuccess) return e;

@@ -1,33 +1,41 @@
 // Whole-line kernels: stride 1, K <= 31, every channel on one of the eight canonical lines,
 // NHWC, square maps whose side L is a compile-time constant (the ConvNeXt stage maps).
 //
-// A work item is (image n, 4 consecutive channels) = 16 bytes per pixel in fp32.  A CTA of four
-// warps owns one item at a time, one warp per channel, and two CTAs share an SM so that one
-// CTA's arithmetic overlaps the other's data movement.  Per item:
+// A work item is (image n, 8 consecutive channels) = 32 bytes per pixel in fp32, one DRAM sector:
+// narrower items were measured to cap a plain strided copy of the tensor at 40 % of the HBM rate
+// (16-byte pieces) against 68 % for 32-byte pieces.  A CTA of eight warps owns one item at a time.
+// Per item:
 //
-//   1. TMA (cp.async.bulk.tensor, 4-D box 4 x L x 8 x 1) streams the item's row bands into a small
-//      ring; the producer runs ahead across item boundaries.
-//   2. restage: every band is scattered into one fp32 plane per channel in (line, position)
-//      coordinates (o1d_lines.cuh): rows for horizontal lines, columns for vertical ones,
-//      anti-diagonals (wrapped, with a gap of zeros between the two pieces that share a storage
-//      row) for the 45-degree lines.  After this step every line of an axis or diagonal channel
-//      is one contiguous storage row.
-//   3. compute: a lane owns whole storage rows.  It loads a row into registers ONCE (one
-//      shared-memory load per output instead of one per tap or per window) and evaluates all
-//      outputs of the row with compile-time tap offsets; taps that fall off the row do not
-//      exist at compile time, so there are no bounds tests and no halo columns.  Axis and
-//      diagonal rows are private to their lane and are overwritten in place.  Slanted lines
-//      (22.5 degrees: 29 taps spread over 11 rows) are evaluated for two adjacent rows and half
-//      a row of outputs at a time, so that each loaded row segment serves both output rows;
-//      their results go to a second plane.
+//   1. TMA (cp.async.bulk.tensor, 4-D box 8 x L x 8 x 1) streams the item's row bands into a small
+//      ring; the producer runs ahead across item boundaries, and the warp that finishes a band
+//      last refills its slot (no CTA-wide barrier per band).
+//   2. restage: every band is scattered into fp32 planes in (line, position) coordinates
+//      (o1d_lines.cuh): rows for horizontal lines, columns for vertical ones, anti-diagonals
+//      (wrapped, with a gap of zeros between the two pieces that share a storage row) for the
+//      45-degree lines.  After this step every line of an axis or diagonal channel is one
+//      contiguous storage row.
+//   3. compute: a lane owns whole storage rows and slides each of them through a register window,
+//      so every input is loaded from shared memory ONCE (not once per tap or per window) and no tap
+//      needs a bounds test.  Axis and diagonal rows are private to their lane and are overwritten
+//      in place.  Slanted lines (22.5 degrees: 29 taps spread over 11 rows) are evaluated for two
+//      adjacent rows at a time, so that each loaded row segment serves both; their results go to
+//      a second plane.
 //   4. destage: planes are gathered back to NHWC 16-byte vectors, bias added, and stored.
 //
-// Shared-memory plane layouts are chosen so that every phase is free of bank conflicts:
-// a storage row r starts at (r >> 2) * G4 + (r & 3) * Q4 (planes whose rows are image rows) or at
-// (r >> 3) * G8 + (r & 7) * Q8 (planes whose rows are image columns), with G = 1 (mod 32) and
-// Q chosen so that the 4 (8) rows of a group start 8 (4) banks apart.  The movers work on tiles
-// of 8 pixels x 4 rows per warp, which then hit 32 different banks in either plane type, and the
-// compute lanes (consecutive rows, or every second row) do too.
+// Everything is stored and computed in PAIRS (two floats side by side, one 64-bit shared-memory
+// access, one packed fma.rn.f32x2): the two halves are two adjacent storage rows of one channel
+// (axis, diagonal) or the same pixel of two slanted channels of the item.  The arithmetic is bound
+// by instruction issue, and the pairing halves its instruction count.
+//
+// The instruction cache shapes the compute bodies: straight-line code that four warps run through
+// at different places stops fitting at roughly 2 K instructions in total, after which the kernel
+// waits for instruction fetches.  Every body is therefore a short unrolled block inside a rolled
+// loop over chunks of outputs.
+//
+// Plane layouts are chosen so that every phase is (nearly) free of bank conflicts: a storage row
+// (pair) starts at group * G + member * Q with G = 2 (mod 32) and Q a multiple of 8 chosen per
+// plane type, so that the rows a mover tile of 8 pixels x 4 rows touches, and the rows consecutive
+// compute lanes own, start in different banks.
 //
 // The reference kernels (models/dwoconv1d_specialized/kernels/kernels.h:201-291) give each block
 // one (n, c) plane band, re-read the halo rows per band and redo sincosf + float->int + four
@@ -44,12 +52,13 @@
 namespace o1d {
 namespace wl {
 
-constexpr int kThreads = 128;            // four warps, one per channel of the item
-constexpr int kCC = 4;                   // channels per item
+constexpr int kCC = 8;                   // channels per item: 32 bytes of every pixel, one DRAM sector
+constexpr int kWarps = kCC;              // one warp per channel
+constexpr int kThreads = 32 * kWarps;
 constexpr int kBR = 8;                   // rows per TMA band
 constexpr int kMaxStages = 4;
 constexpr int kGap = 10;                 // zeros between the two diagonal pieces of a storage row (largest |dp|)
-constexpr int kHaloRows = 8;             // zero rows above a slanted-line plane (largest |dl| is 5; 8 keeps groups aligned)
+constexpr int kHaloRows = 8;             // zero rows above and below a slanted-line plane (largest |dl| is 5, +1 for the row pair)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 constexpr int next_mod(int v, int m, int r) {
@@ -57,32 +66,53 @@ constexpr int next_mod(int v, int m, int r) {
     while (x % m != r) x++;
     return x;
 }
+constexpr int cmax(int a, int b) { return a > b ? a : b; }
 
+// Plane geometry for side L.  All sizes in floats; every plane holds pairs, so a position is 2 floats.
 template <int L>
 struct Geo {
     static_assert(L % 8 == 0 && L / 2 <= 32 && L >= 16, "side must be a multiple of 8 with L/2 lanes");
-    static constexpr int Q4 = next_mod(L, 16, 8), G4 = 4 * Q4 + 1;              // rows are image rows
-    static constexpr int Q8 = next_mod(L, 8, 4), G8 = 8 * Q8 + 1;               // rows are image columns
-    static constexpr int LD = L + kGap;                                         // wrapped diagonal row
-    static constexpr int QD = next_mod(LD, 16, 8), GD = 4 * QD + 1;
-    static constexpr int SR = L + 2 * kHaloRows;                                // rows of a slanted-line plane
-    static constexpr int cmax(int a, int b) { return a > b ? a : b; }
-    static constexpr int kAxisFloats = cmax((L / 4) * G4, (L / 8) * G8);
-    static constexpr int kSlantFloats = cmax((SR / 4) * G4, (SR / 8) * G8);
+    // axis, rows are image rows: row r at (r>>2)*G2 + ((r>>1)&1)*Q2, its pair half r&1
+    static constexpr int Q2 = next_mod(2 * L, 32, 16), G2 = 2 * Q2 + 2;
+    // axis, rows are image columns: row pair q = r>>1 at (q>>2)*G8 + (q&3)*Q8
+    static constexpr int Q8 = next_mod(2 * L, 16, 8), G8 = 4 * Q8 + 2;
+    // diagonals (wrapped rows of L + kGap positions), paired like Q2/G2
+    static constexpr int LD = L + kGap;
+    static constexpr int QD = next_mod(2 * LD, 32, 16), GD = 2 * QD + 2;
+    // slanted channel pair: row r at (r>>2)*GS + (r&3)*QS, pair half = channel of the pair
+    static constexpr int SR = L + 2 * kHaloRows;
+    static constexpr int QS = next_mod(2 * L, 16, 8), GS = 4 * QS + 2;
+    static constexpr int kAxisFloats = cmax((L / 4) * G2, (L / 8) * G8);
     static constexpr int kDiagFloats = (L / 4) * GD;
-    static constexpr int kOutFloats = kAxisFloats;                              // second plane of a slanted channel
+    static constexpr int kSlantInFloats = (SR / 4) * GS;       // both channels of a pair
+    static constexpr int kSlantOutFloats = (L / 4) * GS;
     static constexpr int kTilesX = L / 8, kTilesBand = (kBR / 4) * kTilesX, kTilesImage = (L / 4) * kTilesX;
     static constexpr int NB = L / kBR;
     static constexpr int kStageBytes = kBR * L * kCC * 4;
 };
 
+// Shared memory a chunk with these line kinds needs for its planes (floats).  Slanted channels come
+// in pairs; `ok` is cleared for a chunk with an odd number of them.
+template <int L>
+__host__ __device__ inline int chunk_plane_floats(const int (&kind)[kCC], bool *ok) {
+    using G = Geo<L>;
+    int total = 0, ns = 0;
+    for (int j = 0; j < kCC; j++) {
+        if (kind[j] == KIND_AXIS) total += G::kAxisFloats;
+        else if (kind[j] == KIND_DIAG) total += G::kDiagFloats;
+        else ns++;
+    }
+    if (ok) *ok = (ns % 2) == 0;
+    return total + (ns / 2) * (G::kSlantInFloats + G::kSlantOutFloats);
+}
+
 struct WlParams {
     int N, C, K, nchunks, total_items;
     int flip, add_identity;
-    int in_off[kCC], out_off[kCC];       // plane offsets (floats); out_off == in_off for in-place kinds
-    int plane_floats;                    // floats to clear at kernel start
-    int off_wts;                         // [kCC][32] floats
+    int plane_floats;                    // floats to clear at kernel start (largest chunk)
+    int off_wts;                         // [kCC][32] floats, then mover maps and band counters
     int off_stage_bytes, nstg, off_bar_bytes;
+    int step_n, step_chunk;              // item += gridDim.x as (n += step_n, chunk += step_chunk, carry)
 };
 
 // ---- mbarrier / TMA primitives -----------------------------------------------------------------
@@ -101,7 +131,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: gives up (and raises the caller's flag) if the data never arrives.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err_flag) {
+__device__ __noinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err_flag) {
     for (uint32_t i = 0; i < kSpinLimit; i++)
         if (mbar_try_wait(bar, parity)) return true;
     atomicExch(err_flag, 1);
@@ -114,6 +144,14 @@ __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, u
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
+// Brings a box into L2 without a destination in shared memory: the later tma_load_4d of the same
+// box then costs an L2 hit instead of a trip to HBM.  No completion to wait for.
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap *map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 template <int I, int N, typename F>
 __device__ __forceinline__ void static_for(F &&f) {
     if constexpr (I < N) {
@@ -122,45 +160,85 @@ __device__ __forceinline__ void static_for(F &&f) {
     }
 }
 
-// ---- plane addressing ----------------------------------------------------------------------------
-// Start of storage row r of a plane at `off`.
-struct RowBase {
-    int off, sh, msk, G, Q;
-    __device__ __forceinline__ int operator()(int r) const { return off + (r >> sh) * G + (r & msk) * Q; }
-};
+// ---- packed fp32 arithmetic -----------------------------------------------------------------------
+// fma.rn.f32x2 issues two independent IEEE fp32 FMAs (the low and the high half of a 64-bit
+// register) as ONE instruction; each half is rounded exactly as a scalar fmaf would be.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ f32x2 ffma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 fmul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 ld2(const float *p) { return *reinterpret_cast<const f32x2 *>(p); }
+__device__ __forceinline__ void st2(float *p, f32x2 v) { *reinterpret_cast<f32x2 *>(p) = v; }
 
-// Where a mover lane's pixel of a tile lands in a channel plane: addr = a*hb + b*wb + c, with hb, wb
-// the tile's row (4 image rows) and column (8 pixels) index, plus `wrapfix` on the second piece of
-// a wrapped diagonal (4*hb + tb*wb + tc >= L).
+// Element `w` of a small register array, for a warp-uniform w (a sum of masked terms keeps the
+// array in registers, where an indexed read would spill it to local memory).
+template <int N>
+__device__ __forceinline__ int pick(const int (&v)[N], int w) {
+    int r = 0;
+#pragma unroll
+    for (int j = 0; j < N; j++) r += v[j] * (w == j);
+    return r;
+}
+
+// ---- plane addressing ----------------------------------------------------------------------------
+// Where a mover lane's pixel of a tile lands: addr = a*hb + b*wb + c, with hb, wb the tile's row
+// (4 image rows) and column (8 pixels) index, plus `wrapfix` on the second piece of a wrapped
+// diagonal (4*hb + tb*wb + tc >= L).  (hi, wi) is the lane's pixel inside the tile.
 struct ChanMap {
     int a, b, c;
     int tb, tc, wrapfix;
 };
 
+// o: canonical line id; off: plane offset (even); half: 0/1, the channel's half of a slanted pair;
+// halo: zero rows above the image rows (slanted input planes).
 template <int L>
-__device__ __forceinline__ ChanMap make_map(int o, int off, int halo, int hi, int wi) {
+__device__ __forceinline__ ChanMap make_map(int o, int off, int half, int halo, int hi, int wi) {
     using G = Geo<L>;
     const int kind = canon_kind(o), mode = canon_mode(o);
-    const bool fp = (mode & MODE_FP) != 0;
+    const bool fp = (mode & MODE_FP) != 0, tr = (mode & MODE_T) != 0;
     ChanMap m;
     m.tb = 0; m.tc = -(1 << 24); m.wrapfix = 0;
     if (kind == KIND_DIAG) {
+        // row r = (h + w') mod L with w' = w or L-1-w; position w' (+ kGap on the wrapped piece)
         const int wi2 = fp ? 7 - wi : wi, s = hi + wi2;
-        const int per_wb = 2 * G::GD + 8;
+        const int per_wb = 2 * G::GD + 16;                 // r grows by 8, the position by 8 pairs
         m.a = G::GD;
         m.b = fp ? -per_wb : per_wb;
-        m.c = off + (s >> 2) * G::GD + (s & 3) * G::QD + wi2 + (fp ? (L / 8 - 1) * per_wb : 0);
+        m.c = off + (s >> 2) * G::GD + ((s >> 1) & 1) * G::QD + (s & 1) + 2 * wi2 + (fp ? (L / 8 - 1) * per_wb : 0);
         m.tb = fp ? -8 : 8;
         m.tc = s + (fp ? 8 * (L / 8 - 1) : 0);
-        m.wrapfix = kGap - (L / 4) * G::GD;
-    } else if (!(mode & MODE_T)) {
-        m.a = G::G4;
-        m.b = fp ? -8 : 8;
-        m.c = off + (halo / 4) * G::G4 + hi * G::Q4 + (fp ? L - 1 - wi : wi);
-    } else {
-        m.a = fp ? -4 : 4;
+        m.wrapfix = 2 * kGap - (L / 4) * G::GD;
+    } else if (kind == KIND_AXIS && !tr) {
+        m.a = G::G2;
+        m.b = fp ? -16 : 16;
+        m.c = off + (hi >> 1) * G::Q2 + (hi & 1) + 2 * (fp ? L - 1 - wi : wi);
+    } else if (kind == KIND_AXIS) {
+        // row r = w, pair q = r >> 1 = 4*wb + (wi >> 1); position h
+        m.a = fp ? -8 : 8;
         m.b = G::G8;
-        m.c = off + (halo / 8) * G::G8 + wi * G::Q8 + (fp ? L - 1 - hi : hi);
+        m.c = off + (wi >> 1) * G::Q8 + (wi & 1) + 2 * (fp ? L - 1 - hi : hi);
+    } else if (!tr) {
+        // slanted, rows are image rows: r = h + halo
+        m.a = G::GS;
+        m.b = fp ? -16 : 16;
+        m.c = off + half + (halo / 4) * G::GS + hi * G::QS + 2 * (fp ? L - 1 - wi : wi);
+    } else {
+        // slanted, rows are image columns: r = w + halo = 8*wb + wi + halo
+        m.a = fp ? -8 : 8;
+        m.b = 2 * G::GS;
+        m.c = off + half + (halo / 4 + (wi >> 2)) * G::GS + (wi & 3) * G::QS + 2 * (fp ? L - 1 - hi : hi);
     }
     return m;
 }
@@ -171,13 +249,13 @@ __device__ __forceinline__ int map_addr(const ChanMap &m, int hb, int wb, int Ls
     return a;
 }
 
+// Start of the storage row pair q (rows 2q, 2q+1) of an axis or diagonal plane.
 template <int L>
-__device__ __forceinline__ RowBase row_base_of(int o, int off) {
+__device__ __forceinline__ int pair_base(int o, int off, int q) {
     using G = Geo<L>;
-    const int kind = canon_kind(o), mode = canon_mode(o);
-    if (kind == KIND_DIAG) return RowBase{off, 2, 3, G::GD, G::QD};
-    if (!(mode & MODE_T)) return RowBase{off, 2, 3, G::G4, G::Q4};
-    return RowBase{off, 3, 7, G::G8, G::Q8};
+    if (canon_kind(o) == KIND_DIAG) return off + (q >> 1) * G::GD + (q & 1) * G::QD;
+    if (!(canon_mode(o) & MODE_T)) return off + (q >> 1) * G::G2 + (q & 1) * G::Q2;
+    return off + (q >> 2) * G::G8 + (q & 3) * G::Q8;
 }
 
 // Sum colliding taps into the first of their group (the reference adds the products of all taps
@@ -193,73 +271,56 @@ __device__ __forceinline__ void merge_weights(float (&w)[kMaxTaps]) {
 }
 
 // ---- compute bodies --------------------------------------------------------------------------------
-// Every body evaluates HALF of its outputs and is run twice: the second half is the first half of
-// the mirrored problem (positions counted from the far end of the row, rows from the far end of the
-// plane), which for these odd-symmetric lines is the same arithmetic with the weights read in
-// reverse order.  That halves the unrolled code (the instruction cache is what limits these
-// kernels' size) while a tap that would fall off the near end of a row still vanishes at compile
-// time and the far end needs no test.
-
-// Reversed copy of the 31 original weights (tap k <-> tap 30-k).
-__device__ __forceinline__ void reverse_weights(const float (&w)[kMaxTaps], float (&wr)[kMaxTaps]) {
+// AXIS / DIAG: 1-D convolution along the two storage rows of a pair (length ROW, one row per half),
+// in place, with taps at dp = -R .. R (weight pairs wt[dp + R] = (w, w)).  The rows slide through
+// a register window: each input is loaded from shared memory once, positions before the row start
+// are zeros and loads past its end are skipped.  Results may overwrite the rows as the sweep goes,
+// because every later load lies ahead of every earlier store.  GAP (diagonal rows): columns
+// rho+1 .. rho+kGap of row rho separate the two diagonals that share it; they stay zero, so results
+// there are not written.
+template <int R, int ROW, int CH, bool GAP>
+__device__ __forceinline__ void row_pair_sweep(float *__restrict__ sm, int base, int rho0, const f32x2 (&wt)[2 * R + 1]) {
+    static_assert(ROW % CH == 0 && R + CH <= ROW, "chunking");
+    constexpr int WN = CH + 2 * R;
+    f32x2 win[WN];                       // win[i] <-> position c*CH - R + i of both rows
 #pragma unroll
-    for (int k = 0; k < kMaxTaps; k++) wr[k] = w[kMaxTaps - 1 - k];
-}
-
-// AXIS / DIAG: 1-D convolution along storage rows of length ROW, in place.  A lane works through
-// `nrows` rows (row0, row0 + row_step, ..) x 2 halves.  Each half loads a window of ROW/2 + reach
-// inputs once, and holds its ROW/2 results back until the next window has been read, because the
-// next window may overlap the columns they overwrite.  KIND_DIAG rows hold two diagonals separated
-// by kGap zeros at columns rho+1 .. rho+kGap; results there are not written, so the gap stays zero.
-template <int KIND, int JH, int ROW>
-__device__ __forceinline__ void rows_in_place(float *__restrict__ sm, const RowBase &rb, int row0, int row_step,
-                                              int nrows, const float (&w)[kMaxTaps], const float (&wr)[kMaxTaps]) {
-    using P = LP<KIND, JH>;
-    constexpr int HALF = ROW / 2;
-    constexpr int REACH = (KIND == KIND_DIAG) ? kGap : JH;
-    constexpr int WN = (HALF + REACH < ROW) ? HALF + REACH : ROW;
-    static_assert(ROW % 2 == 0, "rows are processed in two halves");
-    float pend[HALF];
-    int pend_at = 0, pend_dir = 0, pend_c0 = 0, pend_rho = 0;
+    for (int i = 0; i < R; i++) win[i] = 0ull;
+#pragma unroll
+    for (int i = R; i < WN; i++) win[i] = ld2(sm + base + 2 * (i - R));
 #pragma unroll 1
-    for (int it = 0; it < 2 * nrows; it++) {
-        const int rho = row0 + (it >> 1) * row_step;
-        const bool mirror = (it & 1) != 0;
-        const int c0 = mirror ? ROW - 1 : 0, dir = mirror ? -1 : 1;
-        const int at = rb(rho) + c0;
-        float x[WN];
+    for (int c = 0; c < ROW / CH; c++) {
+        f32x2 acc[CH];
 #pragma unroll
-        for (int i = 0; i < WN; i++) x[i] = sm[at + dir * i];
-        if (it > 0) {
+        for (int o = 0; o < CH; o++) acc[o] = fmul2(wt[0], win[o]);
 #pragma unroll
-            for (int o = 0; o < HALF; o++) {
-                const int col = pend_c0 + pend_dir * o;
-                if (KIND != KIND_DIAG || col <= pend_rho || col > pend_rho + kGap) sm[pend_at + pend_dir * o] = pend[o];
+        for (int t = 1; t < 2 * R + 1; t++)
+#pragma unroll
+            for (int o = 0; o < CH; o++) acc[o] = ffma2(wt[t], win[o + t], acc[o]);
+        const int at = base + 2 * c * CH;
+#pragma unroll
+        for (int o = 0; o < CH; o++) {
+            if (!GAP) {
+                st2(sm + at + 2 * o, acc[o]);
+            } else {
+                const int col = c * CH + o;
+                const float v0 = __uint_as_float((uint32_t)acc[o]), v1 = __uint_as_float((uint32_t)(acc[o] >> 32));
+                if (col <= rho0 || col > rho0 + kGap) sm[at + 2 * o] = v0;
+                if (col <= rho0 + 1 || col > rho0 + 1 + kGap) sm[at + 2 * o + 1] = v1;
             }
         }
-        float wv[kMaxTaps];
 #pragma unroll
-        for (int k = 0; k < kMaxTaps; k++) wv[k] = mirror ? wr[k] : w[k];
+        for (int i = 0; i < 2 * R; i++) win[i] = win[i + CH];
 #pragma unroll
-        for (int o = 0; o < HALF; o++) pend[o] = 0.f;
-        static_for<0, P::p.ntaps>([&](auto ti) {
-            constexpr int t = decltype(ti)::value;
-            constexpr int dp = P::p.tap_dp[t], k = P::p.tap_k[t];
-#pragma unroll
-            for (int o = 0; o < HALF; o++)
-                if (o + dp >= 0 && o + dp < WN) pend[o] = fmaf(wv[k], x[o + dp], pend[o]);
-        });
-        pend_at = at; pend_dir = dir; pend_c0 = c0; pend_rho = rho;
-    }
-#pragma unroll
-    for (int o = 0; o < HALF; o++) {
-        const int col = pend_c0 + pend_dir * o;
-        if (KIND != KIND_DIAG || col <= pend_rho || col > pend_rho + kGap) sm[pend_at + pend_dir * o] = pend[o];
+        for (int i = 0; i < CH; i++) {
+            const int pos = (c + 1) * CH + R + i;                 // uniform over the warp
+            win[2 * R + i] = pos < ROW ? ld2(sm + base + 2 * pos) : 0ull;
+        }
     }
 }
 
-// SLANT.  Window of (mirrored) storage row 2*rp + e needed by the outputs of rows 2*rp + m, m = 0, 1,
-// columns 0 .. R-1: the union over m of the taps with line offset d = e - m, clipped to the row.
+// SLANT.  Offsets (relative to the first output column of a chunk) of the segment of storage row
+// 2*rp + e that the chunk's outputs in rows 2*rp + m, m = 0, 1, need: the union over m of the taps
+// with line offset d = e - m.
 struct SlWin { int lo, hi; };
 constexpr int slant_find_row(const LinePlan &p, int d) {
     for (int r = 0; r < p.nrows; r++)
@@ -267,52 +328,61 @@ constexpr int slant_find_row(const LinePlan &p, int d) {
     return -1;
 }
 template <int JH>
-constexpr SlWin slant_window(int e, int R, int L) {
+constexpr SlWin slant_window(int e, int CH) {
     const LinePlan &p = LP<KIND_SLANT, JH>::p;
     int lo = 1 << 20, hi = -(1 << 20);
     for (int m = 0; m < 2; m++) {
         const int r = slant_find_row(p, e - m);
         if (r < 0) continue;
         if (p.row_lo[r] < lo) lo = p.row_lo[r];
-        if (R - 1 + p.row_hi[r] > hi) hi = R - 1 + p.row_hi[r];
+        if (CH - 1 + p.row_hi[r] > hi) hi = CH - 1 + p.row_hi[r];
     }
-    if (lo < 0) lo = 0;
-    if (hi > L - 1) hi = L - 1;
     return SlWin{lo, hi};
 }
 
-// Slanted channel: a lane owns the row pair rp and evaluates, per pass, the outputs of its two rows
-// in the columns 0 .. L/2-1 of the plain (pass 0) or mirrored (pass 1) plane, so that every loaded
-// row segment serves both rows.  `in` addresses the input plane (kHaloRows zero rows above and below
-// the image rows), `out` the result plane (no halo).
-template <int L, int JH>
-__device__ __forceinline__ void slant_rows(const float *__restrict__ sm, float *__restrict__ smo, const RowBase &in,
-                                           const RowBase &out, int rp, const float (&w)[kMaxTaps],
-                                           const float (&wr)[kMaxTaps]) {
+// Pair of slanted channels, one half (L/2 columns) of the plane: chunks c0 .. c0 + L/2/CH - 1 of CH
+// columns.  Lane rp owns the row pair rp; every loaded row segment serves both rows and (as a 64-bit
+// load) both channels.  Columns that fall off the row are skipped with warp-uniform tests (they
+// depend on the chunk index only, and a given load can only ever miss on one side).  `in` is the
+// input plane (kHaloRows zero rows above and below the image rows), `out` the result plane.
+// w2[k] = (channel A's weight k, channel B's).
+template <int L, int JH, int CH>
+__device__ __forceinline__ void slant_sweep(float *__restrict__ sm, int in, int out, int rp, int c0,
+                                            const f32x2 (&w2)[kMaxTaps]) {
     using P = LP<KIND_SLANT, JH>;
-    constexpr int MD = P::p.max_d, R = L / 2;
-#pragma unroll 1
-    for (int pass = 0; pass < 2; pass++) {
-        const bool mirror = pass != 0;
-        const int rs = mirror ? -1 : 1, r0 = mirror ? L - 1 : 0;        // image row = rs * (mirrored row) + r0
-        const int cs = rs, cb = r0;                                     // same for columns
-        float wv[kMaxTaps];
+    using G = Geo<L>;
+    static_assert((L / 2) % CH == 0, "chunking");
+    constexpr int MD = P::p.max_d, NC = (L / 2) / CH, NE = 2 * MD + 2;
+    int rb[NE];                          // address of (row 2*rp + e, column 0)
 #pragma unroll
-        for (int k = 0; k < kMaxTaps; k++) wv[k] = mirror ? wr[k] : w[k];
-        float acc[2][R];
+    for (int i = 0; i < NE; i++) {
+        const int r = 2 * rp + i - MD + kHaloRows;
+        rb[i] = in + (r >> 2) * G::GS + (r & 3) * G::QS;
+    }
+    const int ob0 = out + (rp >> 1) * G::GS + (rp & 1) * 2 * G::QS;          // row 2*rp; row 2*rp + 1 is QS further
+#pragma unroll 1
+    for (int c = c0; c < c0 + NC; c++) {
+        const int cc = c * CH;
+        f32x2 acc[2][CH];
 #pragma unroll
         for (int m = 0; m < 2; m++)
 #pragma unroll
-            for (int o = 0; o < R; o++) acc[m][o] = 0.f;
-        static_for<0, 2 * MD + 2>([&](auto ei) {
+            for (int o = 0; o < CH; o++) acc[m][o] = 0ull;
+        static_for<0, NE>([&](auto ei) {
             constexpr int e = decltype(ei)::value - MD;
-            constexpr SlWin wn = slant_window<JH>(e, R, L);
+            constexpr SlWin wn = slant_window<JH>(e, CH);
             if constexpr (wn.hi >= wn.lo) {
                 constexpr int WN = wn.hi - wn.lo + 1;
-                const int base = in(rs * (2 * rp + e) + r0 + kHaloRows) + cb + cs * wn.lo;
-                float win[WN];
+                const float *src = sm + rb[e + MD] + 2 * cc;
+                f32x2 win[WN];
 #pragma unroll
-                for (int i = 0; i < WN; i++) win[i] = sm[base + cs * i];
+                for (int i = 0; i < WN; i++) {
+                    const int off = wn.lo + i;                          // compile-time after unrolling
+                    bool ok = true;
+                    if (off < 0) ok = cc >= -off;
+                    else if (off + L - CH > L - 1) ok = cc <= L - 1 - off;
+                    win[i] = ok ? ld2(src + 2 * off) : 0ull;
+                }
                 static_for<0, 2>([&](auto mi) {
                     constexpr int m = decltype(mi)::value;
                     constexpr int r = slant_find_row(P::p, e - m);
@@ -322,21 +392,18 @@ __device__ __forceinline__ void slant_rows(const float *__restrict__ sm, float *
                             if constexpr (P::p.tap_row[t] == r) {
                                 constexpr int dp = P::p.tap_dp[t], k = P::p.tap_k[t];
 #pragma unroll
-                                for (int o = 0; o < R; o++)
-                                    if (o + dp >= wn.lo && o + dp <= wn.hi)
-                                        acc[m][o] = fmaf(wv[k], win[o + dp - wn.lo], acc[m][o]);
+                                for (int o = 0; o < CH; o++) acc[m][o] = ffma2(w2[k], win[o + dp - wn.lo], acc[m][o]);
                             }
                         });
                     }
                 });
             }
         });
+        float *dst = sm + ob0 + 2 * cc;
 #pragma unroll
-        for (int m = 0; m < 2; m++) {
-            const int ob = out(rs * (2 * rp + m) + r0) + cb;
+        for (int m = 0; m < 2; m++)
 #pragma unroll
-            for (int o = 0; o < R; o++) smo[ob + cs * o] = acc[m][o];
-        }
+            for (int o = 0; o < CH; o++) st2(dst + m * G::QS + 2 * o, acc[m][o]);
     }
 }
 
@@ -344,9 +411,19 @@ __device__ __forceinline__ void slant_rows(const float *__restrict__ sm, float *
 // y = conv(x) (+ bias); with flip = 1 the weights are read in reverse order, which for stride 1 is
 // the input gradient.  Grid: persistent CTAs, items dealt image-major (neighbouring CTAs read
 // neighbouring 16-byte halves of the same pixels at the same time).
+//
+// Shared memory (floats unless noted): planes | wts [8][32] | mover maps (ints: 16 maps x (4 uniform
+// + 2 x 32 per lane)) | band counters (ints) | staging ring (bytes) | mbarriers.
+//
+// Warp roles: warp j owns channel j of the item unless that channel is slanted; slanted channels
+// are taken in pairs (in channel order), and the two warps of a pair each evaluate one half of
+// the plane for both channels.
 // ---------------------------------------------------------------------------------------------------
+constexpr int kMaps = 2 * kCC;                    // a restage and a destage map per channel
+constexpr int kMapInts = kMaps * 4 + kMaps * 32 * 2;     // uniform a, b, tb, wrapfix per map; c and tc per lane
+
 template <int L, int JH>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 wline_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restrict__ wgt,
                    const float *__restrict__ bias, const int8_t *__restrict__ chan, float *__restrict__ y,
                    int *__restrict__ err_flag, const WlParams p) {
@@ -355,6 +432,10 @@ wline_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__rest
     float *sm = reinterpret_cast<float *>(smem_raw);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + p.off_bar_bytes);
     float *wts = sm + p.off_wts;
+    int *map_u = reinterpret_cast<int *>(wts + kCC * 32);      // [kMaps][4]
+    int *map_c = map_u + kMaps * 4;                            // [kMaps][32]
+    int *map_tc = map_c + kMaps * 32;                          // [kMaps][32]
+    int *band_cnt = map_tc + kMaps * 32;                       // [kMaxStages] warps done with a slot
     __shared__ int err_s;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -363,7 +444,7 @@ wline_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__rest
 
     for (int i = tid; i < p.plane_floats; i += kThreads) sm[i] = 0.f;
     if (tid == 0) {
-        for (int s = 0; s < NSTG; s++) mbar_init(&full[s], 1);
+        for (int s = 0; s < NSTG; s++) { mbar_init(&full[s], 1); band_cnt[s] = 0; }
         err_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -372,88 +453,191 @@ wline_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__rest
 
     const int my_items = (p.total_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int total_bands = my_items * G::NB;
-    auto issue = [&](int gb) {   // one elected thread
-        const int it = gb / G::NB, b = gb - it * G::NB;
-        const int item = blockIdx.x + it * gridDim.x;
-        const int n = item / p.nchunks, chunk = item - n * p.nchunks;
-        const int s = gb % NSTG;
-        mbar_expect_tx(&full[s], G::kStageBytes);
-        tma_load_4d(smem_raw + p.off_stage_bytes + (size_t)s * G::kStageBytes, &tmap, &full[s], chunk * kCC, 0,
-                    b * kBR, n);
+    // consumer position (n, chunk) and producer position (pn, pchunk, pb): both advance without divisions
+    int n = (int)blockIdx.x / p.nchunks, chunk = (int)blockIdx.x - n * p.nchunks;
+    int pn = n, pchunk = chunk, pb = 0, pstage = 0, issued = 0;
+    // every thread tracks the producer position; `me` is true in the one thread that issues
+    auto issue = [&](bool me) {
+        if (me) {
+            mbar_expect_tx(&full[pstage], G::kStageBytes);
+            tma_load_4d(smem_raw + p.off_stage_bytes + (size_t)pstage * G::kStageBytes, &tmap, &full[pstage],
+                        pchunk * kCC, 0, pb * kBR, pn);
+        }
+        issued++;
+        if (++pstage == NSTG) pstage = 0;
+        if (++pb == G::NB) {
+            pb = 0;
+            pn += p.step_n; pchunk += p.step_chunk;
+            if (pchunk >= p.nchunks) { pchunk -= p.nchunks; pn++; }
+        }
     };
-    if (tid == 0)
-        for (int gb = 0; gb < NSTG && gb < total_bands; gb++) issue(gb);
+    for (int g = 0; g < NSTG && g < total_bands; g++) issue(tid == 0);
 
-    int gb = 0;                      // bands consumed so far
-    int prev_sig = -1;               // plane types of the previous item (re-zero when they change)
+    // Line id of channel (lane & 7) and this thread's weight (channel `warp`, tap `lane`; slot 31 is the
+    // bias) of the chunk starting at channel c0, in line order: reversed for lines stored mirrored and
+    // for the input gradient.  Loaded one item ahead, so that their latency hides behind the arithmetic.
+    auto load_tables = [&](int c0, int &o_lane, float &wv) {
+        o_lane = chan[c0 + (lane & (kCC - 1))];
+        const int o_w = __shfl_sync(0xffffffffu, o_lane, warp);
+        const int pad = p.K / 2, k = lane;
+        float v = 0.f;
+        if (k < kMaxTaps) {
+            int kk = k - kHalf + pad;
+            if (kk >= 0 && kk < p.K) {
+                const bool rev = ((canon_mode(o_w) & MODE_REV) != 0) != (p.flip != 0);
+                if (rev) kk = p.K - 1 - kk;
+                v = __ldg(wgt + (size_t)(c0 + warp) * p.K + kk);
+                if (p.add_identity && kk == pad) v += 1.f;
+            }
+        } else {
+            v = bias ? __ldg(bias + c0 + warp) : 0.f;
+        }
+        wv = v;
+    };
+    int o_lane_next = 0;
+    float wv_next = 0.f;
+    if (my_items > 0) load_tables(chunk * kCC, o_lane_next, wv_next);
+
+    int stage = 0;                   // ring slot and mbarrier parity of the next band to consume
+    uint32_t parity = 0;
+    int prev_sig = -1;               // plane layout of the previous item (re-zero when it changes)
+#pragma unroll 1
     for (int it = 0; it < my_items; it++) {
-        const int item = blockIdx.x + it * gridDim.x;
-        const int n = item / p.nchunks, chunk = item - n * p.nchunks;
         const int c0 = chunk * kCC;
 
-        // ---- per-item channel tables: line ids, mover maps, weights ------------------------------
-        int o_all[kCC];
+        // ---- per-item tables -----------------------------------------------------------------------------
+        // line ids of the four channels, plane offsets, this warp's role
+        int o_j[kCC], in_off[kCC], out_off[kCC], half_j[kCC];
 #pragma unroll
-        for (int j = 0; j < kCC; j++) o_all[j] = chan[c0 + j];
-        int sig = 0;
-#pragma unroll
-        for (int j = 0; j < kCC; j++) sig = sig * 16 + canon_kind(o_all[j]) * 4 + (canon_mode(o_all[j]) & MODE_T) * 2;
-        if (sig != prev_sig && prev_sig >= 0) {
-            // another mix of plane types: stale data would sit where zeros are expected
-            for (int i = tid; i < p.plane_floats; i += kThreads) sm[i] = 0.f;
-        }
-        prev_sig = sig;
+        for (int j = 0; j < kCC; j++) o_j[j] = __shfl_sync(0xffffffffu, o_lane_next, j);
+        int sig = 0, partner = -1;
         {
-            const int pad = p.K / 2;
-            const int j = tid >> 5, k = tid & 31;           // 4 x 32 entries, one per thread
-            float v = 0.f;
-            if (k < kMaxTaps) {
-                int kk = k - kHalf + pad;
-                if (kk >= 0 && kk < p.K) {
-                    const bool rev = ((canon_mode(o_all[j]) & MODE_REV) != 0) != (p.flip != 0);
-                    if (rev) kk = p.K - 1 - kk;
-                    v = __ldg(wgt + (size_t)(c0 + j) * p.K + kk);
-                    if (p.add_identity && kk == pad) v += 1.f;
+            int cur = 0, open_in = 0, open_out = 0, open_j = -1;
+#pragma unroll
+            for (int j = 0; j < kCC; j++) {
+                const int kind = canon_kind(o_j[j]);
+                sig = sig * 16 + kind * 4 + (canon_mode(o_j[j]) & MODE_T);
+                half_j[j] = 0;
+                if (kind == KIND_SLANT) {
+                    if (open_j < 0) {             // first channel of a pair
+                        open_in = cur; open_out = cur + G::kSlantInFloats; open_j = j;
+                        cur += G::kSlantInFloats + G::kSlantOutFloats;
+                    } else {                      // second channel: same planes, other half of the pairs
+                        half_j[j] = 1;
+                        if (warp == j) partner = open_j;
+                        if (warp == open_j) partner = j;
+                        open_j = -1;
+                    }
+                    in_off[j] = open_in; out_off[j] = open_out;
+                } else {
+                    in_off[j] = out_off[j] = cur;
+                    cur += kind == KIND_AXIS ? G::kAxisFloats : G::kDiagFloats;
                 }
             }
-            wts[tid] = v;
         }
-        ChanMap rmap[kCC];
-#pragma unroll
-        for (int j = 0; j < kCC; j++)
-            rmap[j] = make_map<L>(o_all[j], p.in_off[j], canon_kind(o_all[j]) == KIND_SLANT ? kHaloRows : 0, hi, wi);
+        if (sig != prev_sig && prev_sig >= 0)       // another plane layout: stale data would sit where
+            for (int i = tid; i < p.plane_floats; i += kThreads) sm[i] = 0.f;     // zeros are expected
+        prev_sig = sig;
+        const int o_mine = pick(o_j, warp), in_mine = pick(in_off, warp), out_mine = pick(out_off, warp),
+                  half_mine = pick(half_j, warp);
+        {
+            wts[tid] = wv_next;
+            const bool slant = canon_kind(o_mine) == KIND_SLANT;
+#pragma unroll 1
+            for (int q = 0; q < 2; q++) {                  // q = 0: restage map, q = 1: destage map
+                const ChanMap m = make_map<L>(o_mine, q ? out_mine : in_mine, half_mine,
+                                              (!q && slant) ? kHaloRows : 0, hi, wi);
+                const int mi = q * kCC + warp;
+                map_c[mi * 32 + lane] = m.c;
+                map_tc[mi * 32 + lane] = m.tc;
+                if (lane == 0) {
+                    map_u[mi * 4 + 0] = m.a; map_u[mi * 4 + 1] = m.b; map_u[mi * 4 + 2] = m.tb; map_u[mi * 4 + 3] = m.wrapfix;
+                }
+            }
+        }
         __syncthreads();
 
         // ---- restage: staging bands -> planes ---------------------------------------------------------
-        for (int b = 0; b < G::NB; b++) {
-            const int s = gb % NSTG;
-            const uint32_t parity = (gb / NSTG) & 1;
-            if (err_s == 0 && !mbar_wait(&full[s], parity, err_flag)) err_s = 1;
-            const float4 *stg = reinterpret_cast<const float4 *>(smem_raw + p.off_stage_bytes + (size_t)s * G::kStageBytes);
-            for (int t = warp; t < G::kTilesBand; t += 4) {
-                const int ty = t / G::kTilesX, tx = t - ty * G::kTilesX;
-                const int hb = b * (kBR / 4) + ty;
-                const float4 v = stg[(4 * ty + hi) * L + 8 * tx + wi];
-                sm[map_addr(rmap[0], hb, tx, L)] = v.x;
-                sm[map_addr(rmap[1], hb, tx, L)] = v.y;
-                sm[map_addr(rmap[2], hb, tx, L)] = v.z;
-                sm[map_addr(rmap[3], hb, tx, L)] = v.w;
+        // Warp tx moves tile column tx of every band (tiles of 8 pixels x 4 rows).  A lane carries one
+        // 16-byte half (4 channels) of two pixels of the tile, so that the 32 lanes of one load or
+        // store instruction cover 16 whole pixels: full 32-byte sectors in global memory, contiguous
+        // 256-byte runs in the staging ring.  All plane addresses advance by per-lane constants, and
+        // a wrapped diagonal switches to its second piece from tile row `thr` on.
+        const bool mover = warp < G::kTilesX;           // tile column tx = warp
+        const int mhalf = lane & 1, mpix = lane >> 1;   // channels 4*mhalf .. +3 of tile pixels mpix, mpix + 16
+        const int mhi = mpix >> 3, mwi = mpix & 7;      // pixel mpix = (row mhi, column mwi); mpix + 16 is two rows down
+        if (mover) {
+            int ra[4][2], thr[4][2], aj[4], wf[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int j = 4 * mhalf + i;
+                aj[i] = map_u[j * 4 + 0];
+                wf[i] = map_u[j * 4 + 3];
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    const int px = mpix + 16 * u;
+                    ra[i][u] = map_c[j * 32 + px] + map_u[j * 4 + 1] * warp;
+                    thr[i][u] = (L - map_tc[j * 32 + px] - map_u[j * 4 + 2] * warp + 3) >> 2;
+                }
             }
-            __syncthreads();
-            if (tid == 0 && gb + NSTG < total_bands) issue(gb + NSTG);
-            gb++;
+#pragma unroll 1
+            for (int b = 0; b < G::NB; b++) {
+                if (err_s == 0 && !mbar_wait(&full[stage], parity, err_flag)) err_s = 1;
+                const float4 *stg = reinterpret_cast<const float4 *>(smem_raw + p.off_stage_bytes + (size_t)stage * G::kStageBytes) +
+                                    (mhi * L + mwi + 8 * warp) * 2 + mhalf;
+                float4 v[kBR / 4][2];
+#pragma unroll
+                for (int ty = 0; ty < kBR / 4; ty++)
+#pragma unroll
+                    for (int u = 0; u < 2; u++) v[ty][u] = stg[(4 * ty + 2 * u) * L * 2];
+#pragma unroll
+                for (int ty = 0; ty < kBR / 4; ty++) {
+                    const int hb = b * (kBR / 4) + ty;
+#pragma unroll
+                    for (int u = 0; u < 2; u++) {
+                        const float f[4] = {v[ty][u].x, v[ty][u].y, v[ty][u].z, v[ty][u].w};
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+                            sm[ra[i][u] + ty * aj[i] + (hb >= thr[i][u] ? wf[i] : 0)] = f[i];
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int u = 0; u < 2; u++) ra[i][u] += (kBR / 4) * aj[i];
+                // the warp that finishes a slot last refills it: no CTA-wide barrier per band
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) {
+                    __threadfence_block();
+                    last = atomicAdd(&band_cnt[stage], 1) == G::kTilesX - 1;
+                    if (last) band_cnt[stage] = 0;
+                }
+                if (issued < total_bands) issue(last != 0);
+                if (++stage == NSTG) { stage = 0; parity ^= 1; }
+            }
+        } else {
+            // keep the ring bookkeeping in step
+#pragma unroll 1
+            for (int b = 0; b < G::NB; b++) {
+                if (issued < total_bands) issue(false);
+                if (++stage == NSTG) { stage = 0; parity ^= 1; }
+            }
+        }
+        __syncthreads();
+
+        // The ring only holds the next item's first bands; ask for the rest of it to be brought into
+        // L2 now, one compute and one destage phase ahead, and load its line ids and weights.
+        if (it + 1 < my_items) {
+            int nn = n + p.step_n, nc = chunk + p.step_chunk;
+            if (nc >= p.nchunks) { nc -= p.nchunks; nn++; }
+            if (tid >= NSTG && tid < G::NB) tma_prefetch_4d(&tmap, nc * kCC, 0, tid * kBR, nn);
+            load_tables(nc * kCC, o_lane_next, wv_next);
         }
 
-        // ---- compute: warp j evaluates channel j ----------------------------------------------------------
+        // ---- compute ----------------------------------------------------------------------------------------
         {
-            const int o = o_all[0] * (warp == 0) + o_all[1] * (warp == 1) + o_all[2] * (warp == 2) + o_all[3] * (warp == 3);
-            const int in_off = p.in_off[0] * (warp == 0) + p.in_off[1] * (warp == 1) + p.in_off[2] * (warp == 2) +
-                               p.in_off[3] * (warp == 3);
-            const int kind = canon_kind(o);
-            // results of a slanted channel go to its second plane; the other kinds work in place
-            const int out_off = kind != KIND_SLANT ? in_off
-                                                   : p.out_off[0] * (warp == 0) + p.out_off[1] * (warp == 1) +
-                                                         p.out_off[2] * (warp == 2) + p.out_off[3] * (warp == 3);
+            const int kind = canon_kind(o_mine);
             float w[kMaxTaps];
             {
                 const float4 *wp = reinterpret_cast<const float4 *>(wts + warp * 32);
@@ -465,48 +649,85 @@ wline_fprop_kernel(const __grid_constant__ CUtensorMap tmap, const float *__rest
                 }
             }
             if (lane < L / 2) {
-                float wr[kMaxTaps];
-                reverse_weights(w, wr);
                 if (kind == KIND_AXIS) {
-                    const RowBase rb = row_base_of<L>(o, in_off);
-                    rows_in_place<KIND_AXIS, JH, L>(sm, rb, lane, L / 2, 2, w, wr);
+                    f32x2 wt[2 * JH + 1];
+#pragma unroll
+                    for (int t = 0; t < 2 * JH + 1; t++) wt[t] = pack2(w[t - JH + kHalf], w[t - JH + kHalf]);
+                    row_pair_sweep<JH, L, 14, false>(sm, pair_base<L>(o_mine, in_mine, lane), 2 * lane, wt);
                 } else if (kind == KIND_DIAG) {
+                    using PD = LP<KIND_DIAG, JH>;
                     merge_weights<KIND_DIAG, JH>(w);
-                    merge_weights<KIND_DIAG, JH>(wr);
-                    const RowBase rb = row_base_of<L>(o, in_off);
-                    rows_in_place<KIND_DIAG, JH, G::LD>(sm, rb, lane, L / 2, 2, w, wr);
-                } else {
+                    f32x2 wt[2 * kGap + 1];
+#pragma unroll
+                    for (int t = 0; t < 2 * kGap + 1; t++) wt[t] = 0ull;
+                    static_for<0, PD::p.ntaps>([&](auto ti) {
+                        constexpr int t = decltype(ti)::value;
+                        constexpr int at = PD::p.tap_dp[t] + kGap, k = PD::p.tap_k[t];
+                        wt[at] = pack2(w[k], w[k]);
+                    });
+                    row_pair_sweep<kGap, G::LD, 11, true>(sm, pair_base<L>(o_mine, in_mine, lane), 2 * lane, wt);
+                } else if (partner >= 0) {
+                    // both channels' weights: mine from registers, the partner's from shared memory
+                    float wp[kMaxTaps];
+                    {
+                        const float4 *pp = reinterpret_cast<const float4 *>(wts + partner * 32);
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            const float4 v = pp[q];
+                            wp[4 * q] = v.x; wp[4 * q + 1] = v.y; wp[4 * q + 2] = v.z;
+                            if (4 * q + 3 < kMaxTaps) wp[4 * q + 3] = v.w;
+                        }
+                    }
                     merge_weights<KIND_SLANT, JH>(w);
-                    merge_weights<KIND_SLANT, JH>(wr);
-                    const RowBase in = row_base_of<L>(o, in_off), out = row_base_of<L>(o, out_off);
-                    slant_rows<L, JH>(sm, sm, in, out, lane, w, wr);
+                    merge_weights<KIND_SLANT, JH>(wp);
+                    f32x2 w2[kMaxTaps];
+#pragma unroll
+                    for (int k = 0; k < kMaxTaps; k++) w2[k] = half_mine ? pack2(wp[k], w[k]) : pack2(w[k], wp[k]);
+                    // first warp of the pair: left half of the plane, second warp: right half
+                    slant_sweep<L, JH, 7>(sm, in_mine, out_mine, lane, half_mine ? (L / 2) / 7 : 0, w2);
                 }
             }
         }
         __syncthreads();
 
         // ---- destage: planes -> NHWC, bias added ---------------------------------------------------------
-        {
-            ChanMap dmap[kCC];
-            float bv[kCC];
+        if (mover) {
+            int rd[4][2], thr[4][2], aj[4], wf[4];
+            float bv[4];
 #pragma unroll
-            for (int j = 0; j < kCC; j++) {
-                dmap[j] = make_map<L>(o_all[j], canon_kind(o_all[j]) == KIND_SLANT ? p.out_off[j] : p.in_off[j], 0, hi, wi);
-                bv[j] = bias ? __ldg(bias + c0 + j) : 0.f;
+            for (int i = 0; i < 4; i++) {
+                const int mi = kCC + 4 * mhalf + i;
+                aj[i] = map_u[mi * 4 + 0];
+                wf[i] = map_u[mi * 4 + 3];
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    const int px = mpix + 16 * u;
+                    rd[i][u] = map_c[mi * 32 + px] + map_u[mi * 4 + 1] * warp;
+                    thr[i][u] = (L - map_tc[mi * 32 + px] - map_u[mi * 4 + 2] * warp + 3) >> 2;
+                }
+                bv[i] = wts[(4 * mhalf + i) * 32 + 31];
             }
-            float *ybase = y + ((size_t)n * L * L) * p.C + c0;
-            for (int t = warp; t < G::kTilesImage; t += 4) {
-                const int hb = t / G::kTilesX, tx = t - hb * G::kTilesX;
-                float4 v;
-                v.x = sm[map_addr(dmap[0], hb, tx, L)] + bv[0];
-                v.y = sm[map_addr(dmap[1], hb, tx, L)] + bv[1];
-                v.z = sm[map_addr(dmap[2], hb, tx, L)] + bv[2];
-                v.w = sm[map_addr(dmap[3], hb, tx, L)] + bv[3];
-                const int h = 4 * hb + hi, wq = 8 * tx + wi;
-                *reinterpret_cast<float4 *>(ybase + ((size_t)h * L + wq) * p.C) = v;
+            float *yp = y + ((size_t)n * L * L) * p.C + c0 + ((size_t)mhi * L + mwi + 8 * warp) * p.C + 4 * mhalf;
+            const size_t ystep = (size_t)4 * L * p.C, yrow2 = (size_t)2 * L * p.C;
+#pragma unroll 2
+            for (int hb = 0; hb < L / 4; hb++) {
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    float f[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) f[i] = sm[rd[i][u] + (hb >= thr[i][u] ? wf[i] : 0)] + bv[i];
+                    *reinterpret_cast<float4 *>(yp + u * yrow2) = make_float4(f[0], f[1], f[2], f[3]);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int u = 0; u < 2; u++) rd[i][u] += aj[i];
+                yp += ystep;
             }
         }
         __syncthreads();
+        n += p.step_n; chunk += p.step_chunk;
+        if (chunk >= p.nchunks) { chunk -= p.nchunks; n++; }
     }
 }
 

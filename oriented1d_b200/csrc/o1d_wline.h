@@ -11,7 +11,6 @@ namespace o1d {
 struct WlConfig {
     int L;                       // side of the square map
     int N, C, K, nchunks;
-    int in_off[4], out_off[4];   // plane offsets in floats; out_off < 0: the slot never holds a slanted line
     int plane_floats, off_wts, off_stage_bytes, off_bar_bytes, nstg;
     int smem_bytes, grid, ctas_per_sm;
     int box_c, box_rows;         // TMA box: box_c channels x L pixels x box_rows rows x 1 image

@@ -356,6 +356,54 @@ def test_tiled_route_equals_general_route(hw, C, mode, dtype):
         assert float(((dx - dx_ref).abs() / dx_ref.abs().clamp_min(1e-2)).max()) <= 2 ** -7
 
 
+@pytest.mark.parametrize("mode,K,N", [("rr", 31, 3), ("rr", 15, 2), ("rr", 7, 1)])
+def test_whole_line_kernels(oracle, mode, K, N):
+    """The whole-line family (route 4: 8-channel items, lines slid through register windows, packed
+    fp32 arithmetic) against the oracle at the 56x56 stage shape, with bias and the identity tap,
+    forward and input gradient."""
+    C, hw = 96, 56
+    x, w, dy = make_inputs(K * 7 + N, N, C, hw, hw, K)
+    th = angle_list(mode, C)
+    bias = np.linspace(-1, 1, C).astype(np.float32)
+    plan = o1d.Plan(th, K)
+    wd, bd = torch.from_numpy(w).to(DEV), torch.from_numpy(bias).to(DEV)
+    try:
+        o1d.ops.set_route(4)
+        for resid in (False, True):
+            y = o1d.fprop(_to_dev(x, True), wd, bd, plan, 1, True, resid)
+            assert o1d.ops.last_route() == "lines"
+            dx = o1d.dgrad(_to_dev(dy, True), wd, plan, hw, hw, 1, True, resid)
+            assert o1d.ops.last_route() == "lines"
+            ry, (rdx, _, _) = _oracle_fwd_bwd(oracle, x, w, th, dy, bias, 1, resid)
+            assert rel_err(_to_nchw(y, True), ry) <= TOL_FPROP
+            assert rel_err(_to_nchw(dx, True), rdx) <= TOL_DGRAD
+    finally:
+        o1d.ops.set_route(0)
+    assert o1d.ops.device_status() == 0
+
+
+def test_whole_line_kernels_full_batch():
+    """Batch 128 through the whole-line family: every CTA walks several items (ring wrap-around,
+    tables loaded one item ahead); bit-equal to the same images run two at a time."""
+    C, hw, K, N = 96, 56, 31, 128
+    g = torch.Generator(device="cpu").manual_seed(3)
+    x = torch.randn((N, hw, hw, C), generator=g).to(DEV)
+    w = (0.02 * torch.randn((C, 1, 1, K), generator=g)).to(DEV)
+    plan = o1d.Plan(angle_list("rr", C), K)
+    try:
+        o1d.ops.set_route(4)
+        y = o1d.fprop(x, w, None, plan, 1, True)
+        assert o1d.ops.last_route() == "lines"
+        for i in (0, 37, 126):
+            assert torch.equal(o1d.fprop(x[i:i + 2].contiguous(), w, None, plan, 1, True), y[i:i + 2])
+        o1d.ops.set_route(2)
+        yt = o1d.fprop(x, w, None, plan, 1, True)
+    finally:
+        o1d.ops.set_route(0)
+    assert float((y - yt).abs().max()) <= 1e-5 * float(yt.abs().max())
+    assert o1d.ops.device_status() == 0
+
+
 @pytest.mark.parametrize("K", [7, 13, 15, 27])
 def test_tiled_short_kernels(oracle, K):
     """K < 31 uses the centre of the 31-tap line."""
