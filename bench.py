@@ -11,9 +11,17 @@ fprop, dgrad and wgrad once at each shape (12 operator calls).  Throughput is im
     python bench.py --impl reference ...                      # the reference's CPU operator
 
 Prints ONE JSON line.  Extra keys: `kernels` (per-kernel time, algorithmic GB/s and
-fraction of the measured HBM copy rate, fp32 and bf16), `roofline` (the kernel that takes
-the most time), `cpu_baseline`, `e2e` (same work through the nn.Module with host buffers:
-H2D of inputs and D2H of all results inside the timed region), `clocks`.
+fraction of the measured HBM copy rate, fp32 and bf16, round-robin angles; `tr_*` are the
+layout transposes), `kernels_block` (the same with the models' block-wise angle assignment),
+`roofline` (the kernel that takes the most time), `cpu_baseline`, `cpu_conv2d` (the operator as
+a torch depthwise conv2d over the rasterised kernel on all host cores), `e2e` (same work
+through the nn.Module with host buffers: H2D of inputs and D2H of all results inside the timed
+region), `model` (ConvNeXt-T-1D inference img/s on the same GPUs), `clocks`.
+
+Other workloads, one JSON line each: `--workload model` (ConvNeXt-T-1D inference, bf16, batch
+256 per GPU), `--workload train` (ConvNeXt-B-1D++ training step: cross-entropy, AdamW, one flat
+all-reduce of every gradient), `--workload dense` (dense-prediction backbone, forward + backward
+at 800x1280).
 """
 from __future__ import annotations
 
@@ -50,6 +58,13 @@ def round_robin_angles(C, n=8):
     """theta[c] = (c mod n) * pi / n as fp32: the sweep's channel -> orientation assignment."""
     import numpy as np
     return np.array([(c % n) * np.pi / n for c in range(C)], dtype=np.float64).astype(np.float32)
+
+
+def block_angles(C, n=8):
+    """The models' assignment: blocks of ~C/n consecutive channels share an angle
+    (reference: models/convnext.py:60-65)."""
+    import numpy as np
+    return np.array([((n * (c + 1) - 1) // C) * np.pi / n for c in range(C)], dtype=np.float64).astype(np.float32)
 
 
 def algorithmic_bytes(hw, C, esize, n=BATCH):
@@ -165,6 +180,46 @@ def cpu_step(loops, n_img, seed=0, threads=1):
     return total
 
 
+def cpu_conv2d_baseline():
+    """The operator as the reference's CPU formulation: torch depthwise conv2d over the (2 pad + 1)^2
+    kernel that has w[c, k] scatter-added at tap k's rasterised offset; forward plus autograd
+    backward (input and weight gradients) on all host cores, at N=2, 56x56x96, K=31, round-robin
+    angles (the single-layer CPU configuration)."""
+    import numpy as np
+    import torch
+    import torch.nn.functional as F
+    from oracle.oracle import Oracle
+    N, C, hw, pad = 2, 96, 56, K // 2
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn((N, C, hw, hw), generator=g, requires_grad=True)
+    w = (0.02 * torch.randn((C, K), generator=g)).requires_grad_(True)
+    dy = torch.randn((N, C, hw, hw), generator=g)
+    dh, dw = Oracle().offsets(round_robin_angles(C), K)
+    ci = torch.arange(C).repeat_interleave(K)
+    ri = torch.from_numpy(np.ascontiguousarray(dh, np.int64)).reshape(-1) + pad
+    qi = torch.from_numpy(np.ascontiguousarray(dw, np.int64)).reshape(-1) + pad
+
+    def fwd():
+        k2d = torch.zeros((C, 1, 2 * pad + 1, 2 * pad + 1)).index_put((ci, torch.zeros_like(ci), ri, qi),
+                                                                     w.reshape(-1), accumulate=True)
+        return F.conv2d(x, k2d, None, 1, pad, 1, C)
+
+    fwd().backward(dy)                       # warm-up
+    reps, tf, tb = 3, 0.0, 0.0
+    for _ in range(reps):
+        x.grad = w.grad = None
+        t0 = time.perf_counter()
+        y = fwd()
+        t1 = time.perf_counter()
+        y.backward(dy)
+        t2 = time.perf_counter()
+        tf, tb = tf + t1 - t0, tb + t2 - t1
+    return {"value": N * reps / (tf + tb), "unit": "img/s", "cores": torch.get_num_threads(), "kind": "port",
+            "forward_s": tf / reps, "backward_s": tb / reps,
+            "sample": f"N={N}, 56x56x96, K=31, fp32 NCHW, forward + backward, {reps} repetitions: "
+                      "F.conv2d(groups=C) over the scatter-added 31x31 kernel"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -204,14 +259,7 @@ def run_ours(args):
 
     import oriented1d_b200 as o1d
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        os.environ.setdefault("NCCL_DEBUG", "WARN")     # keep stdout to the one JSON line
-        dist.init_process_group("nccl", device_id=dev)
+    world, rank, local, dev = init_ranks()
 
     peak, peak_src = measured_peak()
     g = torch.Generator(device="cpu").manual_seed(rank)
@@ -221,12 +269,12 @@ def run_ours(args):
         their inputs in L2 (each set is touched once per `nsets` launches and the sets
         together exceed 4x the L2 size)."""
 
-        def __init__(self, hw, C, dtype):
+        def __init__(self, hw, C, dtype, angles=round_robin_angles):
             self.hw, self.C, self.dtype = hw, C, dtype
             es = 4 if dtype == torch.float32 else 2
             per_set = 2 * BATCH * hw * hw * C * es
             self.nsets = max(2, -(-4 * L2_BYTES // per_set))
-            self.plan = o1d.Plan(round_robin_angles(C), K)
+            self.plan = o1d.Plan(angles(C), K)
             self.w = (0.02 * torch.randn((C, 1, 1, K), generator=g)).to(dev)
             base_x = torch.randn((BATCH, hw, hw, C), generator=g)
             base_dy = torch.randn((BATCH, hw, hw, C), generator=g)
@@ -259,9 +307,12 @@ def run_ours(args):
         if world > 1:   # data-parallel training sums the weight gradients across ranks
             dist.all_reduce(flat)
 
+    comm = torch.cuda.Stream(device=dev) if world > 1 else None
+
     def graphed_multi_gpu_step(layers, cycle):
-        """world > 1: one CUDA graph per step of the input rotation (kernels only); the NCCL
-        all-reduce of that step's gradient buffer follows each replay, outside the graph."""
+        """world > 1: one CUDA graph per step of the input rotation (kernels only).  The NCCL
+        all-reduce of a step's gradient buffer runs on its own stream under the next step's
+        kernels; a graph is replayed again only after the all-reduce that read its buffer."""
         for _ in range(3):
             step(layers)
         torch.cuda.synchronize()
@@ -270,19 +321,25 @@ def run_ours(args):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 flat = compute(layers)
-            graphs.append((g, flat))
+            graphs.append((g, flat, torch.cuda.Event()))
         state = {"i": 0}
 
         def run():
-            g, flat = graphs[state["i"] % cycle]
+            cur = torch.cuda.current_stream()
+            g, flat, reduced = graphs[state["i"] % cycle]
             state["i"] += 1
+            cur.wait_event(reduced)             # the previous all-reduce of this buffer
             g.replay()
-            dist.all_reduce(flat)
+            comm.wait_stream(cur)
+            with torch.cuda.stream(comm):
+                dist.all_reduce(flat)
+                reduced.record(comm)
         return run
 
-    def timed(fn, steps, warmup, graph_cycle=0, all_ranks=True):
+    def timed(fn, steps, warmup, graph_cycle=0, all_ranks=True, tail=None):
         """Device time of `steps` calls of fn (CUDA events on the launching stream, barrier and
-        synchronize on both sides, max over ranks).  With graph_cycle > 0 the calls are captured
+        synchronize on both sides, max over ranks).  `tail` runs after the last call, inside the
+        timed region (joins work the calls left on other streams).  With graph_cycle > 0 the calls are captured
         once into a CUDA graph of `graph_cycle` consecutive calls (one full rotation of the input
         sets) and replayed, so that host launch latency does not sit between kernels.
         all_ranks=False: a measurement only this rank takes (no barrier, no max-reduce)."""
@@ -306,6 +363,8 @@ def run_ours(args):
         e0.record()
         for _ in range(reps):
             runner()
+        if tail is not None:
+            tail()
         e1.record()
         torch.cuda.synchronize()
         if multi:
@@ -326,7 +385,8 @@ def run_ours(args):
         step(layers32)
         per_step = launches["n"]
         if world > 1 and not args.no_graph:
-            ms = timed(graphed_multi_gpu_step(layers32, max(L.nsets for L in layers32)), args.steps, warm)
+            ms = timed(graphed_multi_gpu_step(layers32, max(L.nsets for L in layers32)), args.steps, warm,
+                       tail=lambda: torch.cuda.current_stream().wait_stream(comm))
         else:
             ms = timed(lambda: step(layers32), args.steps, warm, graph_cycle=cycle)
         n_launch = per_step * args.steps
@@ -335,37 +395,46 @@ def run_ours(args):
     value = BATCH * world * args.steps / (ms / 1e3)
 
     # ---- per-kernel timings (rank 0 only, after the headline) -------------------------
-    kernels, roof = {}, None
+    kernels, kernels_block, roof = {}, {}, None
     if rank == 0:
         reps = 40
-        for dtype, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
-            layers = layers32 if dtype == torch.float32 else [Layer(hw, C, dtype) for hw, C in STAGES]
-            for L in layers:
-                es = 4 if dtype == torch.float32 else 2
-                ab = algorithmic_bytes(L.hw, L.C, es)
+        for angles, table in ((round_robin_angles, kernels), (block_angles, kernels_block)):
+            for dtype, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+                own = not (dtype == torch.float32 and angles is round_robin_angles)
+                layers = [Layer(hw, C, dtype, angles) for hw, C in STAGES] if own else layers32
+                for L in layers:
+                    es = 4 if dtype == torch.float32 else 2
+                    ab = algorithmic_bytes(L.hw, L.C, es)
 
-                def f_fprop(L=L):
-                    x, _ = L.next()
-                    o1d.fprop(x, L.w, None, L.plan, 1, True)
+                    def f_fprop(L=L):
+                        x, _ = L.next()
+                        o1d.fprop(x, L.w, None, L.plan, 1, True)
 
-                def f_dgrad(L=L):
-                    _, dy = L.next()
-                    o1d.dgrad(dy, L.w, L.plan, L.hw, L.hw, 1, True)
+                    def f_dgrad(L=L):
+                        _, dy = L.next()
+                        o1d.dgrad(dy, L.w, L.plan, L.hw, L.hw, 1, True)
 
-                def f_wgrad(L=L):
-                    x, dy = L.next()
-                    o1d.wgrad(dy, x, L.plan, 1, True, True)
+                    def f_wgrad(L=L):
+                        x, dy = L.next()
+                        o1d.wgrad(dy, x, L.plan, 1, True, True)
 
-                for name, fn in (("fprop", f_fprop), ("dgrad", f_dgrad), ("wgrad", f_wgrad)):
-                    t_ms = timed(fn, reps, 3, graph_cycle=0 if args.no_graph else L.nsets, all_ranks=False) / reps
-                    gbs = ab / (t_ms * 1e-3) / 1e9
-                    kernels[f"{name}_{tag}_{L.hw}x{L.hw}x{L.C}"] = {
-                        "us": round(t_ms * 1e3, 2), "alg_bytes": ab, "gbs": round(gbs, 1),
-                        "frac": round(gbs / peak, 4)}
-            if dtype != torch.float32:
-                del layers
-                torch.cuda.empty_cache()
-        top = max((k for k in kernels if "_f32_" in k), key=lambda k: kernels[k]["us"])
+                    def f_tr(L=L):
+                        x, _ = L.next()
+                        o1d.nhwc_to_nchw(x)
+
+                    cases = [("fprop", f_fprop, ab), ("dgrad", f_dgrad, ab), ("wgrad", f_wgrad, ab)]
+                    if angles is round_robin_angles:       # the layout transposes do not depend on the angles
+                        cases.append(("tr", f_tr, 2 * BATCH * L.hw * L.hw * L.C * es))
+                    for name, fn, nbytes in cases:
+                        t_ms = timed(fn, reps, 3, graph_cycle=0 if args.no_graph else L.nsets, all_ranks=False) / reps
+                        gbs = nbytes / (t_ms * 1e-3) / 1e9
+                        table[f"{name}_{tag}_{L.hw}x{L.hw}x{L.C}"] = {
+                            "us": round(t_ms * 1e3, 2), "alg_bytes": nbytes, "gbs": round(gbs, 1),
+                            "frac": round(gbs / peak, 4), "route": o1d.ops.last_route()}
+                if own:
+                    del layers
+                    torch.cuda.empty_cache()
+        top = max((k for k in kernels if "_f32_" in k and not k.startswith("tr_")), key=lambda k: kernels[k]["us"])
         traffic = None
         try:
             with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
@@ -487,6 +556,18 @@ def run_ours(args):
         cpu = {"value": n_img / t, "unit": "img/s", "cores": threads, "kind": kind,
                "sample": f"{n_img} images at each of the 4 stage shapes (fprop+dgrad+wgrad), fp32 NCHW, {t:.1f} s: "
                          f"the reference's single-threaded loops on {threads} batch slices in {threads} threads"}
+    cpu_conv = None
+    if rank == 0 and not args.no_cpu:
+        try:
+            cpu_conv = cpu_conv2d_baseline()
+        except Exception as e:              # a reported baseline must not take the line down
+            cpu_conv = {"unavailable": repr(e)}
+
+    # ---- the metric's model figure: ConvNeXt-T-1D inference on the same GPUs ------------------
+    model_fig = None
+    if not args.no_model:
+        torch.cuda.empty_cache()
+        model_fig = measure_model(10, 3, 256, world, rank, dev, graph=not args.no_graph)
 
     if rank == 0:
         line = {
@@ -497,13 +578,14 @@ def run_ours(args):
                                    "stride 1, NHWC, 8 orientations round-robin; fprop+dgrad+wgrad per shape",
                        "l2": "inputs rotate over sets totalling >4x L2, so every launch reads from HBM",
                        "launch": ("eager" if args.no_graph else "CUDA graph of one full input rotation, replayed" if world == 1
-                                  else "one CUDA graph per step (kernels only), NCCL all-reduce after each replay"),
+                                  else "one CUDA graph per step (kernels only); the NCCL all-reduce of step i runs on "
+                                       "its own stream under the kernels of step i+1"),
                        "parallelism": f"dp{world} (batch-sharded; weight-gradient all-reduce when >1)"},
             "roofline": roof, "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": n_launch, "clocks": clocks, "kernels": kernels,
-            "reference_gpu_us": ref_gpu,
+            "gpu_launches": n_launch, "clocks": clocks, "kernels": kernels, "kernels_block": kernels_block,
+            "reference_gpu_us": ref_gpu, "cpu_conv2d": cpu_conv, "model": model_fig,
         }
         print(json.dumps(line))
     if world > 1:
@@ -569,26 +651,72 @@ def run_case(args):
                       "device_status": o1d.ops.device_status()}))
 
 
-def run_model(args):
-    """ConvNeXt-T-1D full-model inference: depths 3/3/9/3, dims 96..768, K=31
-    oriented convs in every block and in the stem, 1000 classes, random init, bf16, batch 256
-    per GPU of synthetic N(0,1) 224x224 images, batch-sharded over the GPUs with no collective."""
+def init_ranks():
+    """(world, rank, local, device); starts the NCCL process group when launched by torchrun."""
     import torch
     import torch.distributed as dist
-
-    import oriented1d_b200 as o1d
-    from oriented1d_b200 import convnext1d
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
-        os.environ.setdefault("NCCL_DEBUG", "WARN")
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("NCCL_DEBUG", "WARN")     # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
+    return world, rank, local, dev
+
+
+def timed_steps(fn, steps, warmup, world, dev, graph_cycle=0, tail=None):
+    """Device milliseconds of `steps` calls of fn: CUDA events on the launching stream, barrier and
+    synchronize on both sides, max over ranks.  graph_cycle > 0 captures that many consecutive
+    calls into one CUDA graph and replays it.  `tail` runs after the last call, inside the timed
+    region."""
+    import torch
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    runner, per = fn, 1
+    if graph_cycle > 0:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(graph_cycle):
+                fn()
+        g.replay()
+        runner, per = g.replay, graph_cycle
+    reps = max(1, -(-steps // per))
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        runner()
+    if tail is not None:
+        tail()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1) * steps / (reps * per)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def measure_model(steps, warmup, batch, world, rank, dev, graph=True):
+    """ConvNeXt-T-1D full-model inference: depths 3/3/9/3, dims 96..768, K=31 oriented convs in every
+    block and in the stem, 1000 classes, random init, bf16, `batch` synthetic N(0,1) 224x224 images per
+    GPU, batch-sharded over the GPUs with no collective.  Returns device-resident and end-to-end
+    throughput (every batch uploaded from pinned host memory, logits downloaded)."""
+    import torch
+    import torch.distributed as dist
+
+    from oriented1d_b200 import convnext1d
+
     torch.manual_seed(rank)
-    batch = args.batch if args.batch != 64 else 256
     model = convnext1d.convnext_tiny(variant="1d", drop_path_rate=0.0).to(dev).bfloat16().eval()
     nsets = 3
     imgs = [torch.randn((batch, 3, 224, 224), device=dev).bfloat16() for _ in range(nsets)]
@@ -627,90 +755,188 @@ def run_model(args):
             down.wait_event(ev_free[b])
             host_out.copy_(out, non_blocking=True)
 
-    def e2e_timed(steps, warmup):
-        for _ in range(warmup):
-            e2e_step()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        cur = torch.cuda.current_stream()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            e2e_step()
-        cur.wait_stream(down)
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            dist.barrier()
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+    ms = timed_steps(step, steps, max(warmup, 3), world, dev, graph_cycle=nsets if graph else 0)
+    n_e2e = max(4, min(steps, 10))
+    e2e_ms = timed_steps(e2e_step, n_e2e, 3, world, dev,
+                         tail=lambda: torch.cuda.current_stream().wait_stream(down))
+    out = {"value": batch * world * steps / (ms / 1e3), "unit": "img/s", "ms_per_step": ms / steps, "batch": batch,
+           "e2e": {"value": batch * world * n_e2e / (e2e_ms / 1e3), "unit": "img/s",
+                   "h2d_bytes_per_step": host_img.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2,
+                   "ms_per_step": e2e_ms / n_e2e},
+           "workload": "ConvNeXt-T-1D inference: depths 3/3/9/3, dims 96-768, K=31, 8 orientations (block-wise per "
+                       f"layer), batch {batch} per GPU, 224x224x3 bf16, random init, 1000 classes",
+           "gpu_launches_per_step": 20}      # oriented-conv launches per forward: 2 stem convs + 18 block convs
+    del model, imgs, dev_in
+    torch.cuda.empty_cache()
+    return out
 
-    def timed(fn, steps, warmup, graph):
-        for _ in range(warmup):
-            fn()
-        torch.cuda.synchronize()
-        runner, per = fn, 1
-        if graph:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                for _ in range(nsets):
-                    fn()
-            g.replay()
-            runner, per = g.replay, nsets
-        reps = max(1, -(-steps // per))
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            runner()
-        e1.record()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        ms = e0.elapsed_time(e1) * steps / (reps * per)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
 
-    warm = max(args.warmup, 3)
+def run_model(args):
+    import torch.distributed as dist
+    world, rank, local, dev = init_ranks()
+    batch = args.batch if args.batch != 64 else 256
     with ClockSampler(local) as clk:
-        ms = timed(step, args.steps, warm, graph=not args.no_graph)
+        m = measure_model(args.steps, args.warmup, batch, world, rank, dev, graph=not args.no_graph)
         time.sleep(0.25)
-    n_e2e = max(4, min(args.steps, 10))
-    e2e_ms = e2e_timed(n_e2e, 3)
-    # oriented-conv launches per forward: 2 stem convs + 18 block convs
     if rank == 0:
         print(json.dumps({
-            "metric": "ConvNeXt-T-1D inference throughput @224", "value": batch * world * args.steps / (ms / 1e3),
-            "unit": "img/s", "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps,
+            "metric": "ConvNeXt-T-1D inference throughput @224", "value": m["value"], "unit": "img/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": m["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "ConvNeXt-T-1D inference: depths 3/3/9/3, dims 96-768, K=31, 8 orientations, "
-                                   f"batch {batch} per GPU, 224x224x3 bf16, random init, 1000 classes",
-                       "l2": "activations exceed L2; 3 input batches rotate",
+            "config": {"workload": m["workload"], "l2": "activations exceed L2; 3 input batches rotate",
                        "launch": "eager" if args.no_graph else "CUDA graph replay",
                        "parallelism": f"dp{world} (batch-sharded, no collective)"},
-            "e2e": {"value": batch * world * n_e2e / (e2e_ms / 1e3), "unit": "img/s",
-                    "h2d_bytes_per_step": host_img.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2,
-                    "ms_per_step": e2e_ms / n_e2e},
-            "gpu_launches": 20 * args.steps, "clocks": clk.summary(),
+            "e2e": m["e2e"], "gpu_launches": m["gpu_launches_per_step"] * args.steps, "clocks": clk.summary(),
             "roofline": None, "cpu_baseline": None}))
     if world > 1:
         dist.destroy_process_group()
 
 
-def block_angles(C, n=8):
-    """The models' assignment: blocks of ~C/n consecutive channels share an angle
-    (reference: models/convnext.py:60-65)."""
-    import numpy as np
-    return np.array([((n * (c + 1) - 1) // C) * np.pi / n for c in range(C)], dtype=np.float64).astype(np.float32)
+def flat_gradient_buffer(model):
+    """One contiguous fp32/bf16 buffer holding every parameter's gradient (each p.grad is a view into
+    it), so that data-parallel training needs one all-reduce per step.  Parameters that never receive
+    a gradient (the oriented convs' angles) are left out, which is what spares the reference's
+    find_unused_parameters pass (main.py:346-348)."""
+    import torch
+    params = [p for n, p in model.named_parameters() if p.requires_grad and not n.endswith("theta")]
+    total = sum(p.numel() for p in params)
+    flat = torch.zeros(total, dtype=params[0].dtype, device=params[0].device)
+    off = 0
+    for p in params:
+        p.grad = flat[off:off + p.numel()].view_as(p)
+        off += p.numel()
+    return flat, params
+
+
+def run_train(args):
+    """ConvNeXt-B-1D++ data-parallel training step: depths 3/3/27/3, dims 128..1024, blocks with a K=15
+    oriented conv and a K=31 one on the 4x hidden tensor, stem K=15; batch 64 per GPU of synthetic
+    224x224x3 images with uniform labels in [0,1000), cross-entropy, torch AdamW, one all-reduce of
+    the flat gradient buffer (engine.py:29-82, main.py:346-348).  Weights, activations and optimizer
+    state in bf16 (no autocast)."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    from oriented1d_b200 import convnext1d
+
+    world, rank, local, dev = init_ranks()
+    torch.manual_seed(rank)
+    batch = args.batch if args.batch != 64 else 64
+    model = convnext1d.convnext_base(variant="1dpp", drop_path_rate=0.0).to(dev).bfloat16().train()
+    flat, params = flat_gradient_buffer(model)
+    opt = torch.optim.AdamW(params, lr=1e-4, weight_decay=0.05, fused=True)
+    nsets = 2
+    imgs = [torch.randn((batch, 3, 224, 224), device=dev).bfloat16() for _ in range(nsets)]
+    labels = [torch.randint(0, 1000, (batch,), device=dev) for _ in range(nsets)]
+    host_img = torch.randn((batch, 3, 224, 224)).bfloat16().pin_memory()
+    host_lab = torch.randint(0, 1000, (batch,)).pin_memory()
+    host_loss = torch.empty((), dtype=torch.float32).pin_memory()
+    state = {"i": 0}
+
+    def train_step(x, t):
+        flat.zero_()
+        loss = F.cross_entropy(model(x).float(), t)
+        loss.backward()
+        if world > 1:
+            dist.all_reduce(flat)
+            flat.div_(world)
+        opt.step()
+        return loss
+
+    def step():
+        state["i"] = (state["i"] + 1) % nsets
+        train_step(imgs[state["i"]], labels[state["i"]])
+
+    def e2e_step():
+        x = host_img.to(dev, non_blocking=True)
+        t = host_lab.to(dev, non_blocking=True)
+        host_loss.copy_(train_step(x, t).detach(), non_blocking=True)
+
+    with ClockSampler(local) as clk:
+        ms = timed_steps(step, args.steps, max(args.warmup, 3), world, dev)
+        time.sleep(0.25)
+    n_e2e = max(3, min(args.steps, 6))
+    e2e_ms = timed_steps(e2e_step, n_e2e, 2, world, dev)
+    n_conv = sum(1 for m in model.modules() if m.__class__.__name__ == "DepthwiseOrientedConv1d")
+    if rank == 0:
+        print(json.dumps({
+            "metric": "ConvNeXt-B-1D++ training throughput @224", "value": batch * world * args.steps / (ms / 1e3),
+            "unit": "img/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "ConvNeXt-B-1D++ training step: depths 3/3/27/3, dims 128-1024, K=(15,31), "
+                                   f"batch {batch} per GPU, 224x224x3 bf16, cross-entropy, AdamW (fused), random init",
+                       "l2": "activations exceed L2; 2 input batches rotate", "launch": "eager",
+                       "parallelism": f"dp{world}: one NCCL all-reduce of the flat gradient buffer "
+                                      f"({flat.numel() * flat.element_size() / 1e6:.0f} MB) per step",
+                       "parameters": sum(p.numel() for p in model.parameters())},
+            "e2e": {"value": batch * world * n_e2e / (e2e_ms / 1e3), "unit": "img/s",
+                    "h2d_bytes_per_step": host_img.numel() * 2 + host_lab.numel() * 8, "d2h_bytes_per_step": 4,
+                    "ms_per_step": e2e_ms / n_e2e},
+            "gpu_launches": 4 * n_conv * args.steps,      # fprop, dgrad, wgrad (2 kernels) per oriented conv
+            "clocks": clk.summary(), "roofline": None, "cpu_baseline": None}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_dense(args):
+    """Dense-prediction backbone shape: the ConvNeXt-T-1D backbone (kernels cropped to 31/31/27/13, four
+    normalised stage outputs; semantic_segmentation/backbone/convnext.py:316-327,433-443), forward +
+    backward at 2 x 3 x 800 x 1280 bf16 per GPU, loss = sum of the four outputs' sums; gradients
+    all-reduced as one flat buffer when more than one GPU runs."""
+    import torch
+    import torch.distributed as dist
+
+    from oriented1d_b200 import backbone
+
+    world, rank, local, dev = init_ranks()
+    torch.manual_seed(rank)
+    batch = args.batch if args.batch != 64 else 2
+    model = backbone.backbone_tiny(variant="1d").to(dev).bfloat16().train()
+    flat, params = flat_gradient_buffer(model)
+    nsets = 2
+    imgs = [torch.randn((batch, 3, 800, 1280), device=dev).bfloat16() for _ in range(nsets)]
+    host_img = torch.randn((batch, 3, 800, 1280)).bfloat16().pin_memory()
+    host_loss = torch.empty((), dtype=torch.float32).pin_memory()
+    state = {"i": 0}
+
+    def fwd_bwd(x):
+        flat.zero_()
+        loss = sum(o.float().sum() for o in model(x))
+        loss.backward()
+        if world > 1:
+            dist.all_reduce(flat)
+        return loss
+
+    def step():
+        state["i"] = (state["i"] + 1) % nsets
+        fwd_bwd(imgs[state["i"]])
+
+    def e2e_step():
+        host_loss.copy_(fwd_bwd(host_img.to(dev, non_blocking=True)).detach(), non_blocking=True)
+
+    with ClockSampler(local) as clk:
+        ms = timed_steps(step, args.steps, max(args.warmup, 3), world, dev)
+        time.sleep(0.25)
+    n_e2e = max(3, min(args.steps, 6))
+    e2e_ms = timed_steps(e2e_step, n_e2e, 2, world, dev)
+    n_conv = sum(1 for m in model.modules() if m.__class__.__name__ == "DepthwiseOrientedConv1d")
+    if rank == 0:
+        print(json.dumps({
+            "metric": "ConvNeXt-T-1D dense-prediction backbone forward+backward @800x1280",
+            "value": batch * world * args.steps / (ms / 1e3), "unit": "img/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"ConvNeXt-T-1D backbone, kernels 31/31/27/13, batch {batch} per GPU, 800x1280x3 bf16, "
+                                   "forward + backward, loss = sum of the four stage outputs, random init",
+                       "l2": "activations exceed L2", "launch": "eager",
+                       "parallelism": f"dp{world}: flat gradient all-reduce"},
+            "e2e": {"value": batch * world * n_e2e / (e2e_ms / 1e3), "unit": "img/s",
+                    "h2d_bytes_per_step": host_img.numel() * 2, "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / n_e2e},
+            "gpu_launches": 4 * n_conv * args.steps, "clocks": clk.summary(), "roofline": None, "cpu_baseline": None}))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main():
@@ -722,14 +948,17 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's CUDA kernels")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graphs")
-    ap.add_argument("--workload", default="sweep", choices=["sweep", "model"],
-                    help="sweep: kernel sweep at the stage shapes (default); model: ConvNeXt-T-1D inference")
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "model", "train", "dense"],
+                    help="sweep: kernel sweep at the stage shapes plus the model figure (default); model: "
+                         "ConvNeXt-T-1D inference; train: ConvNeXt-B-1D++ training step; dense: backbone at 800x1280")
     ap.add_argument("--case", default=None, help="run one kernel case alone, e.g. fprop_f32_56x56x96")
     ap.add_argument("--batch", type=int, default=64, help="batch for --case")
     ap.add_argument("--reps", type=int, default=3, help="launches for --case")
     ap.add_argument("--angles", default="rr", choices=["rr", "block"], help="channel->orientation map for --case")
-    ap.add_argument("--route", type=int, default=0, choices=[0, 1, 2, 3],
-                    help="kernel family: 0 automatic (default), 1 general only, 2 prefer tiled, 3 prefer direct")
+    ap.add_argument("--route", type=int, default=0, choices=[0, 1, 2, 3, 4],
+                    help="kernel family: 0 automatic (default), 1 general only, 2 prefer tiled, 3 prefer direct, "
+                         "4 prefer whole-line")
+    ap.add_argument("--no-model", action="store_true", help="sweep workload: skip the model figure")
     args = ap.parse_args()
     if args.route and args.impl == "ours":
         from oriented1d_b200 import ops
@@ -738,6 +967,10 @@ def main():
         run_case(args)
     elif args.workload == "model":
         run_model(args)
+    elif args.workload == "train":
+        run_train(args)
+    elif args.workload == "dense":
+        run_dense(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
