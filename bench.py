@@ -430,7 +430,7 @@ def run_ours(args):
                         gbs = nbytes / (t_ms * 1e-3) / 1e9
                         table[f"{name}_{tag}_{L.hw}x{L.hw}x{L.C}"] = {
                             "us": round(t_ms * 1e3, 2), "alg_bytes": nbytes, "gbs": round(gbs, 1),
-                            "frac": round(gbs / peak, 4), "route": o1d.ops.last_route()}
+                            "frac": round(gbs / peak, 4), "route": o1d.ops.last_route() if name != "tr" else None}
                 if own:
                     del layers
                     torch.cuda.empty_cache()

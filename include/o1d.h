@@ -85,6 +85,12 @@ int o1d_last_route(void);
 int o1d_device_status(int *flag_out);
 /* The same, and resets the flag to 0 afterwards (flag_out may be NULL). */
 int o1d_device_status_clear(int *flag_out);
+/* Exercises that failure path without a fault: launches one warp that waits, with a limit of
+ * about a thousand polls, on a barrier nothing will ever complete.  The wait runs out, the
+ * kernel raises the device flag, writes 1 to *scratch_dev (a caller-allocated int in device
+ * memory) and returns normally; the context stays usable.  Afterwards o1d_device_status()
+ * reads 1 until o1d_device_status_clear() is called.  (No counterpart in the reference.) */
+int o1d_selftest_wait_timeout(int *scratch_dev, void *stream);
 
 /* 1 if o1d_fprop would take one of the TMA-staged kernel families (tiled or direct) for this
  * request, 0 if the general kernels.  Lets a host decide whether converting an NCHW tensor

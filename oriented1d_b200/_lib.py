@@ -25,6 +25,7 @@ SIGNATURES = {
     "o1d_last_route": (_c_int, []),
     "o1d_device_status": (_c_int, [ctypes.POINTER(_c_int)]),
     "o1d_device_status_clear": (_c_int, [ctypes.POINTER(_c_int)]),
+    "o1d_selftest_wait_timeout": (_c_int, [_c_void_p, _c_void_p]),
     "o1d_uses_tiled": (_c_int, [_c_void_p] + [_c_int] * 8),
     "o1d_offsets": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p]),
     "o1d_plan_bytes": (_c_size_t, [_c_int, _c_int]),

@@ -500,6 +500,13 @@ int o1d_device_status(int *flag_out) {
     return O1D_OK;
 }
 
+int o1d_selftest_wait_timeout(int *scratch_dev, void *stream) {
+    if (!scratch_dev) return O1D_ERR_INVALID;
+    wait_timeout_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(1u << 10, scratch_dev);
+    O1D_CUDA(cudaGetLastError());
+    return O1D_OK;
+}
+
 int o1d_device_status_clear(int *flag_out) {
     int flag = 0;
     O1D_CUDA(cudaMemcpyFromSymbol(&flag, g_o1d_device_error, sizeof(int)));

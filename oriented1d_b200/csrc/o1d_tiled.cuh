@@ -104,11 +104,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: returns false (and raises the device flag) if the data never arrives.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpinLimit; i++)
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+    for (uint32_t i = 0; i < limit; i++)
         if (mbar_try_wait(bar, parity)) return true;
     atomicExch(&g_o1d_device_error, 1);
     return false;
+}
+
+// Self-test of that failure path: one warp waits, with a small poll limit, on an mbarrier that no
+// thread and no copy will ever complete.  The wait must run out, raise the device flag and let
+// the kernel return normally (no trap, no hang); *gave_up reports that it did.
+__global__ void wait_timeout_selftest_kernel(uint32_t limit, int *gave_up) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const bool ok = mbar_wait(&bar, 0, limit);
+    if (threadIdx.x == 0) *gave_up = ok ? 0 : 1;
 }
 __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1,
                                             int c2, int c3) {

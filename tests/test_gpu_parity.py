@@ -480,6 +480,28 @@ def test_module_forward_and_backward_stay_on_fast_kernels(dtype):
     assert o1d.ops.device_status() == 0
 
 
+def test_bounded_wait_runs_out_without_a_fault():
+    """The kernels wait for TMA transfers with a poll limit.  Here a wait is made to run out (a
+    barrier that nothing completes, a limit of about a thousand polls): the kernel must return, the
+    device flag must read 1, clearing must work, and the context must stay usable."""
+    from oriented1d_b200 import _lib
+    assert o1d.ops.device_status(clear=True) in (0, 1)
+    assert o1d.ops.device_status() == 0
+    gave_up = torch.zeros(1, dtype=torch.int32, device=DEV)
+    rc = _lib.lib.o1d_selftest_wait_timeout(gave_up.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(gave_up.item()) == 1
+    assert o1d.ops.device_status() == 1
+    assert o1d.ops.device_status(clear=True) == 1
+    assert o1d.ops.device_status() == 0
+    # the context is intact: a normal call still works and raises nothing
+    plan = o1d.Plan(angle_list("rr", 8), 7)
+    x = torch.ones((1, 8, 8, 8), device=DEV)
+    y = o1d.fprop(x, torch.ones((8, 1, 1, 7), device=DEV), None, plan, 1, True)
+    assert torch.isfinite(y).all() and o1d.ops.device_status() == 0
+
+
 DENSE = [
     # C, H, W, K, stride: the dense-prediction backbone at 800x1280 input — stage maps with the
     # kernel lengths that backbone crops to (semantic_segmentation/backbone/convnext.py:316-327)
