@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define O1D_ABI_VERSION 1
+#define O1D_ABI_VERSION 2
 
 enum {
     O1D_OK = 0,
@@ -46,6 +46,11 @@ enum {
 };
 
 enum { O1D_NCHW = 0, O1D_NHWC = 1 };
+/* Bits of the `add_identity` / `flags` argument of the operators. */
+enum {
+    O1D_FLAG_IDENTITY = 1,    /* w' = w + (k == pad): the reference's `resid`                     */
+    O1D_FLAG_GELU_INPUT = 2   /* the input tensor is a pre-activation: exact GELU is applied as it is loaded */
+};
 enum { O1D_F32 = 0, O1D_BF16 = 1 };
 
 /* Library identification.  (No counterpart in the reference: its modules are found by
@@ -120,7 +125,9 @@ int o1d_plan_num_classes(const void *plan_host);
  * (models/dwoconv1d/kernels/kernels.cu:15-27, kernels.h:207-310; specialized:
  * models/dwoconv1d_specialized/kernels/kernels.cu:17-30) together with the separate
  * bias add and w+resid passes of its Python wrapper (dwoconv1d.py:22-23,34-35).
- * bias may be NULL. */
+ * bias may be NULL.  `add_identity` is a flag word: O1D_FLAG_IDENTITY, and O1D_FLAG_GELU_INPUT for
+ * y = conv(GELU(x)) with x the pre-activation tensor, which removes the separate F.gelu pass in
+ * front of the 1D++ / 2D++ blocks' second conv (models/convnext.py:389-391, :463-465). */
 int o1d_fprop(const void *x, const float *w, const float *bias,
               const void *plan_host, const void *plan_dev, void *y,
               int N, int H, int W, int C, int K, int stride,
@@ -132,6 +139,14 @@ int o1d_dgrad(const void *dy, const float *w,
               const void *plan_host, const void *plan_dev, void *dx,
               int N, int H, int W, int C, int K, int stride,
               int layout, int dtype, int add_identity, void *stream);
+
+/* Input gradient of y = conv(GELU(pre)) with respect to `pre`: the input gradient above multiplied,
+ * as it is stored, by GELU'(pre) (the chain-rule pass the reference leaves to autograd behind
+ * models/convnext.py:389-391).  pre has the shape of dx; pre == NULL is o1d_dgrad(). */
+int o1d_dgrad_act(const void *dy, const float *w, const void *pre,
+                  const void *plan_host, const void *plan_dev, void *dx,
+                  int N, int H, int W, int C, int K, int stride,
+                  int layout, int dtype, int add_identity, void *stream);
 
 /* Weight gradient (and bias gradient when db != NULL).  Replaces wgrad(dy, x, theta)
  * (kernels.cu:42-54, kernels.h:402-518) and the separate dy.sum([0,2,3]) pass
@@ -145,6 +160,14 @@ int o1d_wgrad(const void *dy, const void *x,
               float *dw, float *db, void *workspace, size_t workspace_bytes,
               int N, int H, int W, int C, int K, int stride,
               int layout, int dtype, void *stream);
+
+/* o1d_wgrad() with a flag word: O1D_FLAG_GELU_INPUT makes `x` a pre-activation tensor to which exact
+ * GELU is applied as it is loaded (the weight gradient of y = conv(GELU(x))). */
+int o1d_wgrad_act(const void *dy, const void *x,
+                  const void *plan_host, const void *plan_dev,
+                  float *dw, float *db, void *workspace, size_t workspace_bytes,
+                  int N, int H, int W, int C, int K, int stride,
+                  int layout, int dtype, int flags, void *stream);
 
 /* Weight gradient without a workspace argument, for callers that are not able to allocate
  * device memory at the call site (plugin sandboxes and framework hooks that forbid it,

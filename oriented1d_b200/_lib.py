@@ -33,8 +33,10 @@ SIGNATURES = {
     "o1d_plan_num_classes": (_c_int, [_c_void_p]),
     "o1d_fprop": (_c_int, [_c_void_p] * 6 + [_c_int] * 9 + [_c_void_p]),
     "o1d_dgrad": (_c_int, [_c_void_p] * 5 + [_c_int] * 9 + [_c_void_p]),
+    "o1d_dgrad_act": (_c_int, [_c_void_p] * 6 + [_c_int] * 9 + [_c_void_p]),
     "o1d_wgrad_workspace_bytes": (_c_size_t, [_c_int] * 8),
     "o1d_wgrad": (_c_int, [_c_void_p] * 7 + [_c_size_t] + [_c_int] * 8 + [_c_void_p]),
+    "o1d_wgrad_act": (_c_int, [_c_void_p] * 7 + [_c_size_t] + [_c_int] * 9 + [_c_void_p]),
     "o1d_wgrad_static": (_c_int, [_c_void_p] * 6 + [_c_int] * 8 + [_c_void_p]),
     "o1d_layernorm_cl": (_c_int, [_c_void_p] * 4 + [ctypes.c_longlong, _c_int, ctypes.c_float, _c_int, _c_int,
                                                   _c_void_p]),
@@ -42,9 +44,10 @@ SIGNATURES = {
     "o1d_transpose": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p]),
 }
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 NCHW, NHWC = 0, 1
 F32, BF16 = 0, 1
+FLAG_IDENTITY, FLAG_GELU_INPUT = 1, 2
 
 
 class O1dError(RuntimeError):

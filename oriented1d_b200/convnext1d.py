@@ -121,8 +121,9 @@ class Block1D(nn.Module):
         self.dwconv = get_convolution_1d(dim, kernel_size=kernel_sizes[0], padding=kernel_sizes[0] // 2, nhwc=True,
                                          N=N, layer_offset=layer_offset, arbitrary_size=arbitrary_size)
 
-    def _mlp_in(self, x):
-        return F.gelu(self.pwconv1(self.norm(x)))
+    def _mlp_in(self, x, gelu=True):
+        h = self.pwconv1(self.norm(x))
+        return F.gelu(h) if gelu else h
 
     def forward(self, x):
         y = self.pwconv2(self._mlp_in(self.dwconv(x)))
@@ -150,7 +151,8 @@ class Block1DPP(Block1D):
                                           arbitrary_size=arbitrary_size)
 
     def forward(self, x):
-        y = self.pwconv2(self.dwconv2(self._mlp_in(self.dwconv1(x))))
+        fused = self.dwconv2.gelu_input              # the GELU then runs inside dwconv2's kernels
+        y = self.pwconv2(self.dwconv2(self._mlp_in(self.dwconv1(x), gelu=not fused)))
         return self._residual(x, y)
 
 
@@ -191,7 +193,8 @@ class Block2DPP(Block2D):
                                           arbitrary_size=arbitrary_size)
 
     def forward(self, x):
-        y = self._mlp_in(self._dw2d(self.dwconv1, x)).contiguous()
+        fused = self.dwconv2.gelu_input
+        y = self._mlp_in(self._dw2d(self.dwconv1, x), gelu=not fused).contiguous()
         return self._residual(x, self.pwconv2(self.dwconv2(y)))
 
 
@@ -237,7 +240,7 @@ class ConvNeXt1D(nn.Module):
 
     def __init__(self, in_chans=3, num_classes=1000, depths=(3, 3, 9, 3), dims=(96, 192, 384, 768),
                  drop_path_rate=0.0, layer_scale_init_value=1e-6, head_init_scale=1.0, variant="1d", N=8,
-                 stem_dim1=64, arbitrary_size=False, block_kernels=None, stem_kernel=None):
+                 stem_dim1=64, arbitrary_size=False, block_kernels=None, stem_kernel=None, fuse_gelu=False):
         super().__init__()
         assert variant in BLOCKS
         Block = BLOCKS[variant]
@@ -259,6 +262,10 @@ class ConvNeXt1D(nn.Module):
                       layer_offset=layer_wise_rotation_offset(j, cycle), arbitrary_size=arbitrary_size)
                 for j in range(depths[i])]))
             cur += depths[i]
+        if fuse_gelu:      # 1D++ / 2D++: GELU applied while dwconv2 loads its input
+            for m in self.modules():
+                if isinstance(m, (Block1DPP, Block2DPP)):
+                    m.dwconv2.gelu_input = True
         self.norm = nn.LayerNorm(dims[-1], eps=1e-6)
         self.head = nn.Linear(dims[-1], num_classes)
         self.apply(self._init_weights)

@@ -106,7 +106,7 @@ int grid_for(int64_t total, int threads, const DeviceInfo &d, int waves) {
 template <typename T, int LAYOUT>
 int launch_generic_fprop(const void *x, const float *w, const float *bias, const PlanHeader &ph,
                          const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride,
-                         int add_identity, cudaStream_t st, const DeviceInfo &d) {
+                         int add_identity, int act, cudaStream_t st, const DeviceInfo &d) {
     const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
     PlanView pv = plan_view(plan_dev, ph);
     // NHWC with class-uniform channel vectors: 128-bit loads per tap
@@ -122,7 +122,7 @@ int launch_generic_fprop(const void *x, const float *w, const float *bias, const
             if (smem > 48 * 1024) O1D_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
             const int grid = grid_for((int64_t)N * P * Q * (C / VE), kGenericThreads, d, 8);
             kern<<<grid, kGenericThreads, smem, st>>>((const T *)x, w, bias, pv.cls, pv.taps, ph.ncls, w_staged,
-                                                       (T *)y, N, H, W, C, K, stride, P, Q, add_identity);
+                                                       (T *)y, N, H, W, C, K, stride, P, Q, add_identity, act);
             O1D_CUDA(cudaGetLastError());
             g_last_route = O1D_ROUTE_GENERAL;
             return O1D_OK;
@@ -133,7 +133,7 @@ int launch_generic_fprop(const void *x, const float *w, const float *bias, const
     const int grid = grid_for((int64_t)N * P * Q * C, kGenericThreads, d, 16);
     generic_fprop_kernel<T, LAYOUT><<<grid, kGenericThreads, staged ? tap_bytes : 0, st>>>(
         (const T *)x, w, bias, pv.cls, pv.taps, ph.ncls, staged, (T *)y, N, H, W, C, K, stride, P, Q,
-        add_identity);
+        add_identity, act);
     O1D_CUDA(cudaGetLastError());
     g_last_route = O1D_ROUTE_GENERAL;
     return O1D_OK;
@@ -142,7 +142,7 @@ int launch_generic_fprop(const void *x, const float *w, const float *bias, const
 template <typename T, int LAYOUT>
 int launch_generic_dgrad(const void *dy, const float *w, const PlanHeader &ph, const void *plan_dev,
                          void *dx, int N, int H, int W, int C, int K, int stride, int add_identity,
-                         cudaStream_t st, const DeviceInfo &d) {
+                         const void *pre, cudaStream_t st, const DeviceInfo &d) {
     const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
     PlanView pv = plan_view(plan_dev, ph);
     const int tap_bytes = ph.ncls * K * 2;
@@ -150,7 +150,7 @@ int launch_generic_dgrad(const void *dy, const float *w, const PlanHeader &ph, c
     const int grid = grid_for((int64_t)N * H * W * C, kGenericThreads, d, 16);
     generic_dgrad_kernel<T, LAYOUT><<<grid, kGenericThreads, staged ? tap_bytes : 0, st>>>(
         (const T *)dy, w, pv.cls, pv.taps, ph.ncls, staged, (T *)dx, N, H, W, C, K, stride, P, Q,
-        add_identity);
+        add_identity, (const T *)pre);
     O1D_CUDA(cudaGetLastError());
     g_last_route = O1D_ROUTE_GENERAL;
     return O1D_OK;
@@ -173,13 +173,13 @@ int generic_wgrad_slices(int N, int P, int Q, int C, int layout) {
 template <typename T, int LAYOUT>
 int launch_generic_wgrad(const void *dy, const void *x, const PlanHeader &ph, const void *plan_dev,
                          float *dw, float *db, float *partial, int N, int H, int W, int C, int K,
-                         int stride, cudaStream_t st) {
+                         int stride, int act, cudaStream_t st) {
     const int P = ceil_div(H, stride), Q = ceil_div(W, stride);
     PlanView pv = plan_view(plan_dev, ph);
     const int slices = generic_wgrad_slices(N, P, Q, C, LAYOUT);
     dim3 grid(ceil_div(C, WgradShape<LAYOUT>::CL), slices);
     generic_wgrad_partial_kernel<T, LAYOUT><<<grid, kGenericThreads, 0, st>>>(
-        (const T *)dy, (const T *)x, pv.cls, pv.taps, partial, N, H, W, C, K, stride, P, Q, slices);
+        (const T *)dy, (const T *)x, pv.cls, pv.taps, partial, N, H, W, C, K, stride, P, Q, slices, act);
     O1D_CUDA(cudaGetLastError());
     const int tot = C * (K + 1);
     wgrad_final_kernel<<<ceil_div(tot, 256), 256, 0, st>>>(partial, dw, db, C, K, slices);
@@ -193,19 +193,20 @@ constexpr int kMaxTiledCtas = 256;   // upper bound on SMs (grid of the persiste
 // Forward / stride-1 input gradient through the tiled kernels; kNotTiled when they do not apply.
 int try_tiled(const void *x, const float *w, const float *bias, const PlanHeader &ph, const void *plan_host,
               const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride, int layout, int dtype,
-              int add_identity, int flip, cudaStream_t st, const DeviceInfo &d) {
+              int add_identity, int flip, int act, const void *pre, cudaStream_t st, const DeviceInfo &d) {
     if (g_force_generic) return kNotTiled;
     const int esize = dtype == O1D_F32 ? 4 : 2;
     TiledConfig cfg;
     if (!tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, OP_FPROP, &cfg))
         return kNotTiled;
-    if (((uintptr_t)y & 15) != 0) return kNotTiled;
+    if (((uintptr_t)y & 15) != 0 || ((uintptr_t)pre & 15) != 0) return kNotTiled;
     CUtensorMap map;
     O1D_MAP(make_nhwc_tensor_map(&map, x, N, H, W, C, esize, cfg.p.CC, cfg.p.BR), "tiled fprop");
     cfg.p.flip = flip;
     cfg.p.add_identity = add_identity;
+    cfg.p.act = act;
     PlanView pv = plan_view(plan_dev, ph);
-    cudaError_t e = launch_tiled<OP_FPROP>(cfg, dtype, map, w, bias, pv, y, nullptr, st);
+    cudaError_t e = launch_tiled<OP_FPROP>(cfg, dtype, map, w, bias, pv, y, nullptr, pre, st);
     if (e != cudaSuccess) return cuda_fail(e, "tiled fprop launch");
     g_last_route = O1D_ROUTE_TILED;
     return O1D_OK;
@@ -338,8 +339,12 @@ int try_wline(const void *x, const float *w, const float *bias, const PlanHeader
 //   4. general kernels (the caller falls through on kNotTiled).
 int route_forward(const void *x, const float *w, const float *bias, const PlanHeader &ph, const void *plan_host,
                   const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride, int layout,
-                  int dtype, int add_identity, int flip, cudaStream_t st, const DeviceInfo &d) {
+                  int dtype, int add_identity, int flip, int act, const void *pre, cudaStream_t st,
+                  const DeviceInfo &d) {
     int rc = kNotTiled;
+    if (act || pre)       // activation on load / its derivative on store: tiled kernels, else general
+        return try_tiled(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
+                         flip, act, pre, st, d);
     if (g_prefer == 0 || g_prefer == 4) {   // stage maps with whole lines per thread
         rc = try_wline(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
                        flip, st, d, /*need_two_ctas=*/g_prefer == 0);
@@ -365,7 +370,7 @@ int route_forward(const void *x, const float *w, const float *bias, const PlanHe
         if (rc != kNotTiled) return rc;
     }
     rc = try_tiled(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity, flip,
-                   st, d);
+                   0, nullptr, st, d);
     if (rc != kNotTiled) return rc;
     return try_direct(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
                       flip, st, d, false);
@@ -374,7 +379,7 @@ int route_forward(const void *x, const float *w, const float *bias, const PlanHe
 // Weight gradient through the tiled kernels.  `cfg_only`: just report the workspace size.
 int try_tiled_wgrad(const void *dy, const void *x, const PlanHeader &ph, const void *plan_host,
                     const void *plan_dev, float *dw, float *db, void *workspace, size_t workspace_bytes, int N,
-                    int H, int W, int C, int K, int stride, int layout, int dtype, cudaStream_t st,
+                    int H, int W, int C, int K, int stride, int layout, int dtype, int act, cudaStream_t st,
                     const DeviceInfo &d, size_t *need_bytes) {
     if (g_force_generic) return kNotTiled;
     const int esize = dtype == O1D_F32 ? 4 : 2;
@@ -389,7 +394,9 @@ int try_tiled_wgrad(const void *dy, const void *x, const PlanHeader &ph, const v
     O1D_MAP(make_nhwc_tensor_map(&map, x, N, H, W, C, esize, cfg.p.CC, cfg.p.BR), "tiled wgrad");
     PlanView pv = plan_view(plan_dev, ph);
     float *partial = (float *)workspace;
-    cudaError_t e = launch_tiled<OP_WGRAD>(cfg, dtype, map, nullptr, nullptr, pv, const_cast<void *>(dy), partial, st);
+    cfg.p.act = act;
+    cudaError_t e = launch_tiled<OP_WGRAD>(cfg, dtype, map, nullptr, nullptr, pv, const_cast<void *>(dy), partial,
+                                           nullptr, st);
     if (e != cudaSuccess) return cuda_fail(e, "tiled wgrad launch");
     const MergeTables mt = merge_tables_for(cfg.jh);
     const int tot = C * (K + 1);
@@ -650,16 +657,24 @@ int o1d_fprop(const void *x, const float *w, const float *bias, const void *plan
     DeviceInfo d;
     if ((rc = device_info(&d))) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    rc = route_forward(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
-                       /*flip=*/0, st, d);
+    const int identity = add_identity & O1D_FLAG_IDENTITY, act = (add_identity & O1D_FLAG_GELU_INPUT) ? 1 : 0;
+    rc = route_forward(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, identity,
+                       /*flip=*/0, act, nullptr, st, d);
     if (rc != kNotTiled) return rc;
     return O1D_DISPATCH(launch_generic_fprop, x, w, bias, ph, plan_dev, y, N, H, W, C, K, stride,
-                        add_identity, st, d);
+                        identity, act, st, d);
 }
 
 int o1d_dgrad(const void *dy, const float *w, const void *plan_host, const void *plan_dev, void *dx,
               int N, int H, int W, int C, int K, int stride, int layout, int dtype, int add_identity,
               void *stream) {
+    return o1d_dgrad_act(dy, w, nullptr, plan_host, plan_dev, dx, N, H, W, C, K, stride, layout, dtype,
+                         add_identity, stream);
+}
+
+int o1d_dgrad_act(const void *dy, const float *w, const void *pre, const void *plan_host, const void *plan_dev,
+                  void *dx, int N, int H, int W, int C, int K, int stride, int layout, int dtype, int add_identity,
+                  void *stream) {
     if (!dy || !w || !dx || !plan_dev || bad_common(N, H, W, C, K, stride, layout, dtype)) return O1D_ERR_INVALID;
     PlanHeader ph;
     int rc = check_plan(plan_host, C, K, &ph);
@@ -669,14 +684,15 @@ int o1d_dgrad(const void *dy, const float *w, const void *plan_host, const void 
     cudaStream_t st = (cudaStream_t)stream;
     // stride 1: dx = fprop(dy) with the taps mirrored, i.e. (the lines being odd-symmetric)
     // with the weights read in reverse order
+    add_identity &= O1D_FLAG_IDENTITY;
     rc = stride == 1 ? route_forward(dy, w, nullptr, ph, plan_host, plan_dev, dx, N, H, W, C, K, stride, layout,
-                                     dtype, add_identity, /*flip=*/1, st, d)
-         : stride == 2 ? try_direct_dgrad2(dy, w, ph, plan_host, plan_dev, dx, N, H, W, C, K, layout, dtype,
-                                           add_identity, st, d)
-                       : kNotTiled;
+                                     dtype, add_identity, /*flip=*/1, 0, pre, st, d)
+         : (stride == 2 && !pre) ? try_direct_dgrad2(dy, w, ph, plan_host, plan_dev, dx, N, H, W, C, K, layout, dtype,
+                                                     add_identity, st, d)
+                                 : kNotTiled;
     if (rc != kNotTiled) return rc;
     return O1D_DISPATCH(launch_generic_dgrad, dy, w, ph, plan_dev, dx, N, H, W, C, K, stride,
-                        add_identity, st, d);
+                        add_identity, pre, st, d);
 }
 
 size_t o1d_wgrad_workspace_bytes(int N, int H, int W, int C, int K, int stride, int layout, int dtype) {
@@ -703,8 +719,13 @@ namespace {
 // (stems, dense-prediction maps, arbitrary angles), then general.
 int wgrad_dispatch(const void *dy, const void *x, const PlanHeader &ph, const void *plan_host, const void *plan_dev,
                    float *dw, float *db, void *workspace, size_t workspace_bytes, int N, int H, int W, int C, int K,
-                   int stride, int layout, int dtype, cudaStream_t st, const DeviceInfo &d) {
+                   int stride, int layout, int dtype, int act, cudaStream_t st, const DeviceInfo &d) {
     int rc;
+    if (act) {                 // x is GELU(pre), applied on load: tiled kernels, else general
+        rc = try_tiled_wgrad(dy, x, ph, plan_host, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K, stride,
+                             layout, dtype, act, st, d, nullptr);
+        if (rc != kNotTiled && rc != O1D_ERR_WORKSPACE) return rc;
+    } else
     if (g_prefer == 0) {       // 7x7 maps on canonical lines: a channel plane per thread
         rc = try_small7_wgrad(dy, x, ph, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K, stride, layout,
                               dtype, st, d);
@@ -718,16 +739,18 @@ int wgrad_dispatch(const void *dy, const void *x, const PlanHeader &ph, const vo
                             OP_WGRAD, &t))
             weak_tiled = t.util < 0.7;
     }
-    const bool direct_first = g_prefer == 3 || (g_prefer == 0 && (small_map || weak_tiled));
+    const bool direct_first = !act && (g_prefer == 3 || (g_prefer == 0 && (small_map || weak_tiled)));
     if (direct_first) {
         rc = try_direct_wgrad(dy, x, ph, plan_host, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K,
                               stride, layout, dtype, st, d, nullptr);
         if (rc != kNotTiled && rc != O1D_ERR_WORKSPACE) return rc;
     }
-    rc = try_tiled_wgrad(dy, x, ph, plan_host, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K, stride,
-                         layout, dtype, st, d, nullptr);
-    if (rc != kNotTiled && rc != O1D_ERR_WORKSPACE) return rc;
-    if (!direct_first) {
+    if (!act) {
+        rc = try_tiled_wgrad(dy, x, ph, plan_host, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K, stride,
+                             layout, dtype, 0, st, d, nullptr);
+        if (rc != kNotTiled && rc != O1D_ERR_WORKSPACE) return rc;
+    }
+    if (!direct_first && !act) {
         rc = try_direct_wgrad(dy, x, ph, plan_host, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K,
                               stride, layout, dtype, st, d, nullptr);
         if (rc != kNotTiled && rc != O1D_ERR_WORKSPACE) return rc;
@@ -740,7 +763,7 @@ int wgrad_dispatch(const void *dy, const void *x, const PlanHeader &ph, const vo
         return O1D_ERR_WORKSPACE;
     }
     return O1D_DISPATCH(launch_generic_wgrad, dy, x, ph, plan_dev, dw, db, (float *)workspace, N, H, W,
-                        C, K, stride, st);
+                        C, K, stride, act, st);
 }
 }  // namespace
 
@@ -749,6 +772,13 @@ extern "C" {
 int o1d_wgrad(const void *dy, const void *x, const void *plan_host, const void *plan_dev, float *dw,
               float *db, void *workspace, size_t workspace_bytes, int N, int H, int W, int C, int K,
               int stride, int layout, int dtype, void *stream) {
+    return o1d_wgrad_act(dy, x, plan_host, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K, stride, layout,
+                         dtype, 0, stream);
+}
+
+int o1d_wgrad_act(const void *dy, const void *x, const void *plan_host, const void *plan_dev, float *dw,
+                  float *db, void *workspace, size_t workspace_bytes, int N, int H, int W, int C, int K,
+                  int stride, int layout, int dtype, int flags, void *stream) {
     if (!dy || !x || !dw || !plan_dev || bad_common(N, H, W, C, K, stride, layout, dtype)) return O1D_ERR_INVALID;
     PlanHeader ph;
     int rc = check_plan(plan_host, C, K, &ph);
@@ -758,7 +788,7 @@ int o1d_wgrad(const void *dy, const void *x, const void *plan_host, const void *
     DeviceInfo d;
     if ((rc = device_info(&d))) return rc;
     return wgrad_dispatch(dy, x, ph, plan_host, plan_dev, dw, db, workspace, workspace_bytes, N, H, W, C, K, stride,
-                          layout, dtype, (cudaStream_t)stream, d);
+                          layout, dtype, (flags & O1D_FLAG_GELU_INPUT) ? 1 : 0, (cudaStream_t)stream, d);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -815,7 +845,7 @@ int o1d_wgrad_static(const void *dy, const void *x, const void *plan_host, const
     // Same order of kernel families as o1d_wgrad(); a family whose partial sums exceed the array
     // is skipped, and when even the general kernels' do not fit the request is refused.
     rc = wgrad_dispatch(dy, x, ph, plan_host, plan_dev, dw, db, scratch, O1D_STATIC_SCRATCH_BYTES, N, H, W, C, K,
-                        stride, layout, dtype, (cudaStream_t)stream, d);
+                        stride, layout, dtype, 0, (cudaStream_t)stream, d);
     if (rc == O1D_ERR_WORKSPACE) {
         snprintf(g_err, sizeof(g_err), "o1d_wgrad_static: the partial sums of this shape do not fit the built-in "
                  "array of %d bytes; use o1d_wgrad() with a workspace", O1D_STATIC_SCRATCH_BYTES);

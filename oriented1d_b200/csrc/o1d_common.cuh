@@ -84,4 +84,12 @@ __device__ __forceinline__ int64_t at(int n, int c, int h, int w, int C, int H, 
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Exact (erf) GELU and its derivative, as torch.nn.functional.gelu computes them.  A conv whose
+// input is the GELU of a tensor applies it while loading that tensor ("activation on load"), and
+// its input gradient is multiplied by the derivative at the same pre-activation values.
+__device__ __forceinline__ float gelu_exact(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_exact_grad(float v) {
+    return 0.5f * (1.f + erff(v * 0.70710678118654752f)) + v * 0.3989422804014327f * expf(-0.5f * v * v);
+}
+
 }  // namespace o1d

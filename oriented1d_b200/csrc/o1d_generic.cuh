@@ -44,7 +44,7 @@ generic_fprop_kernel(const T *__restrict__ x, const float *__restrict__ w,
                      const float *__restrict__ bias, const uint16_t *__restrict__ cls,
                      const int8_t *__restrict__ taps_gmem, int ncls, int staged,
                      T *__restrict__ y, int N, int H, int W, int C, int K, int stride,
-                     int P, int Q, int add_identity) {
+                     int P, int Q, int add_identity, int act) {
     extern __shared__ int8_t s_taps[];
     const int8_t *taps = stage_taps(taps_gmem, ncls, K, s_taps, staged != 0);
     const int pad = K / 2;
@@ -61,7 +61,9 @@ generic_fprop_kernel(const T *__restrict__ x, const float *__restrict__ w,
             if ((unsigned)h < (unsigned)H && (unsigned)ww < (unsigned)W) {
                 float wk = __ldg(wc + k);
                 if (add_identity && k == pad) wk += 1.f;
-                acc = fmaf(ld(x + at<LAYOUT>(n, c, h, ww, C, H, W)), wk, acc);
+                float xv = ld(x + at<LAYOUT>(n, c, h, ww, C, H, W));
+                if (act) xv = gelu_exact(xv);
+                acc = fmaf(xv, wk, acc);
             }
         }
         st(y + idx, acc);
@@ -108,7 +110,7 @@ generic_fprop_nhwc_vec_kernel(const T *__restrict__ x, const float *__restrict__
                               const float *__restrict__ bias, const uint16_t *__restrict__ cls,
                               const int8_t *__restrict__ taps_gmem, int ncls, int w_staged,
                               T *__restrict__ y, int N, int H, int W, int C, int K, int stride,
-                              int P, int Q, int add_identity) {
+                              int P, int Q, int add_identity, int act) {
     constexpr int VE = GVec<T>::N;
     extern __shared__ __align__(16) unsigned char s_raw[];
     // [taps: ncls*K*2 bytes, padded to 16] [weights: K*C floats, if staged]
@@ -142,6 +144,10 @@ generic_fprop_nhwc_vec_kernel(const T *__restrict__ x, const float *__restrict__
             if ((unsigned)h < (unsigned)H && (unsigned)ww < (unsigned)W) {
                 float xv[VE], wv[VE];
                 GVec<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(x + (((int64_t)n * H + h) * W + ww) * C + c0)), xv);
+                if (act) {
+#pragma unroll
+                    for (int j = 0; j < VE; j++) xv[j] = gelu_exact(xv[j]);
+                }
                 if (w_staged) {
 #pragma unroll
                     for (int j = 0; j < VE; j += 4) {
@@ -168,7 +174,7 @@ __global__ void __launch_bounds__(kGenericThreads)
 generic_dgrad_kernel(const T *__restrict__ dy, const float *__restrict__ w,
                      const uint16_t *__restrict__ cls, const int8_t *__restrict__ taps_gmem,
                      int ncls, int staged, T *__restrict__ dx, int N, int H, int W, int C, int K,
-                     int stride, int P, int Q, int add_identity) {
+                     int stride, int P, int Q, int add_identity, const T *__restrict__ pre) {
     extern __shared__ int8_t s_taps[];
     const int8_t *taps = stage_taps(taps_gmem, ncls, K, s_taps, staged != 0);
     const int pad = K / 2;
@@ -190,6 +196,7 @@ generic_dgrad_kernel(const T *__restrict__ dy, const float *__restrict__ w,
                 acc = fmaf(ld(dy + at<LAYOUT>(n, c, p, q, C, P, Q)), wk, acc);
             }
         }
+        if (pre) acc *= gelu_exact_grad(ld(pre + idx));     // the input was GELU(pre): chain rule
         st(dx + idx, acc);
     }
 }
@@ -215,7 +222,7 @@ __global__ void __launch_bounds__(kGenericThreads)
 generic_wgrad_partial_kernel(const T *__restrict__ dy, const T *__restrict__ x,
                              const uint16_t *__restrict__ cls, const int8_t *__restrict__ taps,
                              float *__restrict__ partial, int N, int H, int W, int C, int K,
-                             int stride, int P, int Q, int slices) {
+                             int stride, int P, int Q, int slices, int act) {
     constexpr int CL = WgradShape<LAYOUT>::CL, PG = WgradShape<LAYOUT>::PG;
     __shared__ float red[kGenericThreads];
     const int lane = threadIdx.x % CL, grp = threadIdx.x / CL;
@@ -243,8 +250,11 @@ generic_wgrad_partial_kernel(const T *__restrict__ dy, const T *__restrict__ x,
                     const int k = k0 + i;
                     if (k < K) {
                         const int h = p * stride + t[2 * k], ww = q * stride + t[2 * k + 1];
-                        if ((unsigned)h < (unsigned)H && (unsigned)ww < (unsigned)W)
-                            acc[i] = fmaf(ld(x + at<LAYOUT>(n, c, h, ww, C, H, W)), g, acc[i]);
+                        if ((unsigned)h < (unsigned)H && (unsigned)ww < (unsigned)W) {
+                            float xv = ld(x + at<LAYOUT>(n, c, h, ww, C, H, W));
+                            if (act) xv = gelu_exact(xv);
+                            acc[i] = fmaf(xv, g, acc[i]);
+                        }
                     } else if (k == K) {
                         acc[i] += g;
                     }

@@ -68,6 +68,7 @@ struct TiledParams {
     int out_pitch_n, out_pitch_t, out_plane_stride;
     int nseg_line, nseg_diag;     // segments per channel per band
     int flip, add_identity;
+    int act;                      // 1: the planes hold GELU(x) (applied while restaging)
     int rezero;                   // planes must be cleared per item (H != W)
     int TR;                       // restage/store: rows of a band the movers cover per pass
     int max_visits;               // weight gradient: partial slots per CTA
@@ -275,7 +276,8 @@ template <typename T, int R, int JH, int OP>
 __global__ void __launch_bounds__(kTiledThreads, 1)
 tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restrict__ wgt,
                   const float *__restrict__ bias, const int8_t *__restrict__ chan,
-                  T *__restrict__ io, float *__restrict__ partial, const TiledParams p) {
+                  T *__restrict__ io, float *__restrict__ partial, const T *__restrict__ preact,
+                  const TiledParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float *sm = reinterpret_cast<float *>(smem_raw);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + p.off_bar_bytes);
@@ -556,6 +558,10 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 for (int pix = mover ? pix_first : band_pixels; pix < band_pixels; pix += pix_step) {
                     float f[VE];
                     Vec16<T>::unpack(stg[pix * GV + g_vec], f);
+                    if (p.act) {
+#pragma unroll
+                        for (int j = 0; j < VE; j++) f[j] = gelu_exact(f[j]);
+                    }
 #pragma unroll
                     for (int j = 0; j < VE; j++) { sm[idx[j]] = f[j]; idx[j] += dstep[j]; }
                 }
@@ -731,6 +737,12 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                     float f[VE];
 #pragma unroll
                     for (int j = 0; j < VE; j++) { f[j] = src[idx[j]]; idx[j] += ostep[j]; }
+                    if (preact) {   // input gradient of a conv over GELU(preact): times GELU'(preact)
+                        float g[VE];
+                        Vec16<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(preact + (gdst - io) + (size_t)pix * C)), g);
+#pragma unroll
+                        for (int j = 0; j < VE; j++) f[j] *= gelu_exact_grad(g[j]);
+                    }
                     *reinterpret_cast<uint4 *>(gdst + (size_t)pix * C) = Vec16<T>::pack(f);
                 }
             }

@@ -343,33 +343,34 @@ inline int make_nhwc_tensor_map(CUtensorMap *map, const void *base, int N, int H
 
 template <typename T, int R, int JH, int OP>
 cudaError_t launch_tiled_one(const TiledConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
-                             const PlanView &pv, void *io, float *partial, cudaStream_t st) {
+                             const PlanView &pv, void *io, float *partial, const void *pre, cudaStream_t st) {
     auto kern = tiled_nhwc_kernel<T, R, JH, OP>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
     if (e != cudaSuccess) return e;
-    kern<<<cfg.grid, cfg.threads, cfg.smem_bytes, st>>>(map, w, bias, pv.chan, (T *)io, partial, cfg.p);
+    kern<<<cfg.grid, cfg.threads, cfg.smem_bytes, st>>>(map, w, bias, pv.chan, (T *)io, partial, (const T *)pre, cfg.p);
     return cudaGetLastError();
 }
 
 template <typename T, int R, int OP>
 cudaError_t launch_tiled_jh(const TiledConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
-                            const PlanView &pv, void *io, float *partial, cudaStream_t st) {
+                            const PlanView &pv, void *io, float *partial, const void *pre, cudaStream_t st) {
     switch (cfg.jh) {
-        case 7: return launch_tiled_one<T, R, 7, OP>(cfg, map, w, bias, pv, io, partial, st);
-        case 9: return launch_tiled_one<T, R, 9, OP>(cfg, map, w, bias, pv, io, partial, st);
-        default: return launch_tiled_one<T, R, kHalf, OP>(cfg, map, w, bias, pv, io, partial, st);
+        case 7: return launch_tiled_one<T, R, 7, OP>(cfg, map, w, bias, pv, io, partial, pre, st);
+        case 9: return launch_tiled_one<T, R, 9, OP>(cfg, map, w, bias, pv, io, partial, pre, st);
+        default: return launch_tiled_one<T, R, kHalf, OP>(cfg, map, w, bias, pv, io, partial, pre, st);
     }
 }
 
 // Dispatch over (element type, segment length, tap reach) for one operation.
 template <int OP>
 cudaError_t launch_tiled(const TiledConfig &cfg, int dtype, const CUtensorMap &map, const float *w,
-                         const float *bias, const PlanView &pv, void *io, float *partial, cudaStream_t st) {
+                         const float *bias, const PlanView &pv, void *io, float *partial, const void *pre,
+                         cudaStream_t st) {
     if (dtype == O1D_F32)
-        return cfg.p.R == 8 ? launch_tiled_jh<float, 8, OP>(cfg, map, w, bias, pv, io, partial, st)
-                            : launch_tiled_jh<float, 7, OP>(cfg, map, w, bias, pv, io, partial, st);
-    return cfg.p.R == 8 ? launch_tiled_jh<__nv_bfloat16, 8, OP>(cfg, map, w, bias, pv, io, partial, st)
-                        : launch_tiled_jh<__nv_bfloat16, 7, OP>(cfg, map, w, bias, pv, io, partial, st);
+        return cfg.p.R == 8 ? launch_tiled_jh<float, 8, OP>(cfg, map, w, bias, pv, io, partial, pre, st)
+                            : launch_tiled_jh<float, 7, OP>(cfg, map, w, bias, pv, io, partial, pre, st);
+    return cfg.p.R == 8 ? launch_tiled_jh<__nv_bfloat16, 8, OP>(cfg, map, w, bias, pv, io, partial, pre, st)
+                        : launch_tiled_jh<__nv_bfloat16, 7, OP>(cfg, map, w, bias, pv, io, partial, pre, st);
 }
 
 inline MergeTables merge_tables_for(int jh) {

@@ -39,11 +39,12 @@ class _DepthwiseOrientedConv1d(torch.autograd.Function):
     converts NHWC inputs to NCHW around NCHW-only kernels (dwoconv1d.py:25-26,36-37)."""
 
     @staticmethod
-    def forward(ctx, x, w, theta, bias, plan, stride, nhwc=False, add_identity=False):
+    def forward(ctx, x, w, theta, bias, plan, stride, nhwc=False, add_identity=False, gelu_input=False):
         x = x.contiguous()
         ctx.set_materialize_grads(False)
+        ctx.gelu_input = gelu_input
         via_nhwc = False
-        if not nhwc and x.is_cuda and x.dim() == 4:
+        if not nhwc and not gelu_input and x.is_cuda and x.dim() == 4:
             N, C, H, W = x.shape
             via_nhwc = (ops.uses_tiled(plan, N, H, W, stride, True, x.dtype)
                         and not ops.uses_tiled(plan, N, H, W, stride, False, x.dtype))
@@ -55,12 +56,12 @@ class _DepthwiseOrientedConv1d(torch.autograd.Function):
             ctx.save_for_backward(xh, w)
             return ops.nhwc_to_nchw(ops.fprop(xh, w, bias, plan, stride, True, add_identity))
         ctx.save_for_backward(x, w)
-        return ops.fprop(x, w, bias, plan, stride, nhwc, add_identity)
+        return ops.fprop(x, w, bias, plan, stride, nhwc, add_identity, gelu_input)
 
     @staticmethod
     def backward(ctx, dy):
         if dy is None:
-            return None, None, None, None, None, None, None, None
+            return None, None, None, None, None, None, None, None, None
         x, w = ctx.saved_tensors
         dy = dy.contiguous()
         if dy.dtype != x.dtype:
@@ -74,16 +75,17 @@ class _DepthwiseOrientedConv1d(torch.autograd.Function):
         else:
             H, W = x.shape[2], x.shape[3]
         if ctx.needs_input_grad[0]:
-            dx = ops.dgrad(dy, w, ctx.plan, H, W, ctx.stride, nhwc, ctx.add_identity)
+            dx = ops.dgrad(dy, w, ctx.plan, H, W, ctx.stride, nhwc, ctx.add_identity,
+                           pre=x if ctx.gelu_input else None)
             if ctx.via_nhwc:
                 dx = ops.nhwc_to_nchw(dx)
         need_db = ctx.has_bias and ctx.needs_input_grad[3]
         if ctx.needs_input_grad[1] or need_db:
-            dw, db = ops.wgrad(dy, x, ctx.plan, ctx.stride, nhwc, with_bias=need_db)
+            dw, db = ops.wgrad(dy, x, ctx.plan, ctx.stride, nhwc, with_bias=need_db, gelu_input=ctx.gelu_input)
             dw = dw.to(w.dtype) if ctx.needs_input_grad[1] else None
             # bias shares the weight's dtype in an nn.Conv2d
             db = db.to(w.dtype) if need_db else None
-        return dx, dw, None, db, None, None, None, None
+        return dx, dw, None, db, None, None, None, None, None
 
 
 class DepthwiseOrientedConv1d(nn.Conv2d):
@@ -110,6 +112,11 @@ class DepthwiseOrientedConv1d(nn.Conv2d):
                                         else torch.tensor(angle, dtype=torch.float32))
         self.nhwc = nhwc
         self.add_identity = bool(resid)
+        # Set by a caller whose input is a pre-activation tensor: forward then computes
+        # conv(GELU(x)) with the GELU applied inside the kernels (the reference runs F.gelu as a
+        # separate pass in front of its second block conv, models/convnext.py:389-391).  Not a
+        # constructor argument: the reference's signature is kept as it is.
+        self.gelu_input = False
         # kept for parity with the reference attribute (dwoconv1d.py:136-141); the kernels
         # add the identity tap themselves and never read this tensor
         if resid:
@@ -147,7 +154,7 @@ class DepthwiseOrientedConv1d(nn.Conv2d):
 
     def _apply_op(self, x):
         return _DepthwiseOrientedConv1d.apply(x, self.weight, self.theta, self.bias, self._get_plan(),
-                                              self.stride[0], self.nhwc, self.add_identity)
+                                              self.stride[0], self.nhwc, self.add_identity, self.gelu_input)
 
     def forward_safe(self, x):
         """Any H x W; output extents ceil(H/stride) x ceil(W/stride) (dwoconv1d.py:154-187)."""

@@ -89,8 +89,10 @@ def _check_params(plan: Plan, C: int, w=None, bias=None) -> None:
         raise ValueError(f"bias has {bias.numel()} elements, expected C = {C}")
 
 
-def fprop(x, w, bias, plan: Plan, stride: int = 1, nhwc: bool = False, add_identity: bool = False):
-    """y = oriented conv of x.  x: [N,C,H,W] (or [N,H,W,C] if nhwc), contiguous."""
+def fprop(x, w, bias, plan: Plan, stride: int = 1, nhwc: bool = False, add_identity: bool = False,
+          gelu_input: bool = False):
+    """y = oriented conv of x.  x: [N,C,H,W] (or [N,H,W,C] if nhwc), contiguous.  gelu_input: x is a
+    pre-activation tensor and exact GELU is applied as it is loaded, y = conv(GELU(x))."""
     N, C, H, W = _dims(x, nhwc)
     K = plan.K
     _check_params(plan, C, w, bias)
@@ -103,14 +105,16 @@ def fprop(x, w, bias, plan: Plan, stride: int = 1, nhwc: bool = False, add_ident
     with torch.cuda.device(x.device):
         check(lib.o1d_fprop(x.data_ptr(), w32.data_ptr(), b32.data_ptr() if b32 is not None else None,
                             plan.host.data_ptr(), plan.on(x.device).data_ptr(), y.data_ptr(),
-                            N, H, W, C, K, stride, int(nhwc), _dtype_code(x), int(add_identity),
+                            N, H, W, C, K, stride, int(nhwc), _dtype_code(x),
+                            int(bool(add_identity)) * _lib.FLAG_IDENTITY + int(bool(gelu_input)) * _lib.FLAG_GELU_INPUT,
                             _stream()), "o1d_fprop")
     return y
 
 
 def dgrad(dy, w, plan: Plan, H: int, W: int, stride: int = 1, nhwc: bool = False,
-          add_identity: bool = False):
-    """dx [.., H, W ..] from dy [.., ceil(H/s), ceil(W/s) ..]."""
+          add_identity: bool = False, pre=None):
+    """dx [.., H, W ..] from dy [.., ceil(H/s), ceil(W/s) ..].  pre (shape of dx): the forward pass was
+    conv(GELU(pre)); the result is then the gradient with respect to pre (times GELU'(pre))."""
     N, C, P, Q = _dims(dy, nhwc)
     if P != -(-H // stride) or Q != -(-W // stride):
         raise ValueError("dy extents do not match ceil(H/stride) x ceil(W/stride)")
@@ -120,15 +124,23 @@ def dgrad(dy, w, plan: Plan, H: int, W: int, stride: int = 1, nhwc: bool = False
     dy = dy.contiguous()
     w32 = w.detach().reshape(C, K).to(torch.float32).contiguous()
     dx = torch.empty((N, H, W, C) if nhwc else (N, C, H, W), dtype=dy.dtype, device=dy.device)
+    if pre is not None:
+        if tuple(pre.shape) != tuple(dx.shape) or pre.dtype != dy.dtype:
+            raise ValueError("pre must have the shape and dtype of dx")
+        _need_cuda(pre)
+        pre = pre.contiguous()
     with torch.cuda.device(dy.device):
-        check(lib.o1d_dgrad(dy.data_ptr(), w32.data_ptr(), plan.host.data_ptr(),
-                            plan.on(dy.device).data_ptr(), dx.data_ptr(), N, H, W, C, K, stride,
-                            int(nhwc), _dtype_code(dy), int(add_identity), _stream()), "o1d_dgrad")
+        check(lib.o1d_dgrad_act(dy.data_ptr(), w32.data_ptr(), pre.data_ptr() if pre is not None else None,
+                                plan.host.data_ptr(), plan.on(dy.device).data_ptr(), dx.data_ptr(), N, H, W, C, K,
+                                stride, int(nhwc), _dtype_code(dy), int(bool(add_identity)), _stream()),
+              "o1d_dgrad")
     return dx
 
 
-def wgrad(dy, x, plan: Plan, stride: int = 1, nhwc: bool = False, with_bias: bool = False):
-    """(dw [C,1,1,K] fp32, db [C] fp32 or None).  Deterministic."""
+def wgrad(dy, x, plan: Plan, stride: int = 1, nhwc: bool = False, with_bias: bool = False,
+          gelu_input: bool = False):
+    """(dw [C,1,1,K] fp32, db [C] fp32 or None).  Deterministic.  gelu_input: x is the pre-activation
+    tensor of a forward pass conv(GELU(x))."""
     if dy.dtype != x.dtype:
         raise TypeError("dy and x must have the same dtype")
     N, C, H, W = _dims(x, nhwc)
@@ -146,10 +158,11 @@ def wgrad(dy, x, plan: Plan, stride: int = 1, nhwc: bool = False, with_bias: boo
     nbytes = lib.o1d_wgrad_workspace_bytes(N, H, W, C, K, stride, int(nhwc), code)
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
     with torch.cuda.device(x.device):
-        check(lib.o1d_wgrad(dy.data_ptr(), x.data_ptr(), plan.host.data_ptr(),
-                            plan.on(x.device).data_ptr(), dw.data_ptr(),
-                            db.data_ptr() if db is not None else None, ws.data_ptr(), ws.numel(),
-                            N, H, W, C, K, stride, int(nhwc), code, _stream()), "o1d_wgrad")
+        check(lib.o1d_wgrad_act(dy.data_ptr(), x.data_ptr(), plan.host.data_ptr(),
+                                plan.on(x.device).data_ptr(), dw.data_ptr(),
+                                db.data_ptr() if db is not None else None, ws.data_ptr(), ws.numel(),
+                                N, H, W, C, K, stride, int(nhwc), code,
+                                _lib.FLAG_GELU_INPUT if gelu_input else 0, _stream()), "o1d_wgrad")
     return dw, db
 
 

@@ -480,6 +480,61 @@ def test_module_forward_and_backward_stay_on_fast_kernels(dtype):
     assert o1d.ops.device_status() == 0
 
 
+@pytest.mark.parametrize("N,C,H,W,K,nhwc,mode,dtype", [
+    (2, 96, 56, 56, 31, True, "rr", torch.float32),         # tiled kernels, segments of 8
+    (2, 64, 28, 28, 31, True, "model+", torch.float32),     # tiled kernels, segments of 7, block-wise angles
+    (2, 128, 7, 7, 31, True, "model", torch.float32),       # 7x7: tiled instead of the plane kernels
+    (2, 16, 20, 28, 15, True, "random", torch.float32),     # general kernels (arbitrary angles)
+    (2, 16, 12, 12, 7, False, "rr", torch.float32),         # general kernels, NCHW
+    (2, 64, 28, 28, 31, True, "model", torch.bfloat16),
+])
+def test_gelu_on_load(N, C, H, W, K, nhwc, mode, dtype):
+    """conv(GELU(x)) with the GELU applied inside the kernels (the 1D++ blocks' second conv,
+    models/convnext.py:389-391): forward, gradient with respect to the pre-activation tensor and
+    weight gradient against float64 autograd through F.gelu and the unfused operator's dense form."""
+    import torch.nn.functional as F
+    g = torch.Generator(device="cpu").manual_seed(H * C + K)
+    shape = (N, H, W, C) if nhwc else (N, C, H, W)
+    x = torch.randn(shape, generator=g).to(DEV).to(dtype)
+    dy = torch.randn(shape, generator=g).to(DEV).to(dtype)
+    th = angle_list(mode, C, seed=C)
+    m = o1d.DepthwiseOrientedConv1d(C, C, K, groups=C, padding=K // 2, nhwc=nhwc, resid=True,
+                                    angle=[float(a) for a in th]).to(DEV)
+    with torch.no_grad():
+        m.weight.copy_(0.05 * torch.randn(m.weight.shape, generator=g))
+        m.bias.copy_(torch.randn((C,), generator=g))
+    m.gelu_input = True
+    xf = x.clone().requires_grad_(True)
+    y = m(xf)
+    y.backward(dy)
+    assert o1d.ops.device_status() == 0
+    # reference: float64, GELU by torch, the conv as a dense depthwise conv2d over the rasterised kernel
+    dh, dw = o1d.offsets(th, K)
+    pad = K // 2
+    wd = m.weight.detach().double().reshape(C, K).clone().requires_grad_(True)
+    xr = x.double().clone().requires_grad_(True)
+    wfull = wd + torch.nn.functional.one_hot(torch.tensor(pad), K).double().to(DEV)
+    k2d = torch.zeros((C, 1, K, K), dtype=torch.float64, device=DEV)
+    ci = torch.arange(C, device=DEV).repeat_interleave(K)
+    ri = torch.from_numpy(dh.astype(np.int64)).reshape(-1).to(DEV) + pad
+    qi = torch.from_numpy(dw.astype(np.int64)).reshape(-1).to(DEV) + pad
+    k2d = k2d.index_put((ci, torch.zeros_like(ci), ri, qi), wfull.reshape(-1), accumulate=True)
+    gx = F.gelu(xr)
+    gx_nchw = gx.permute(0, 3, 1, 2) if nhwc else gx
+    yr = F.conv2d(gx_nchw, k2d, m.bias.detach().double(), 1, pad, 1, C)
+    yr = yr.permute(0, 2, 3, 1) if nhwc else yr
+    yr.backward(dy.double())
+    if dtype == torch.float32:
+        tol_y, tol_w = 2e-5, 1e-4
+    else:                                   # one bf16 rounding of each output
+        tol_y, tol_w = 2 ** -7, 2e-3
+    rel = lambda a, b: float((a.double() - b).abs().max() / b.abs().max())
+    assert rel(y.detach(), yr.detach()) <= tol_y
+    assert rel(xf.grad, xr.grad) <= tol_y
+    assert rel(m.weight.grad.reshape(C, K), wd.grad) <= tol_w
+    assert rel(m.bias.grad, dy.double().sum(dim=(0, 1, 2) if nhwc else (0, 2, 3))) <= tol_w
+
+
 def test_bounded_wait_runs_out_without_a_fault():
     """The kernels wait for TMA transfers with a poll limit.  Here a wait is made to run out (a
     barrier that nothing completes, a limit of about a thousand polls): the kernel must return, the

@@ -114,6 +114,39 @@ def test_model_forward_matches_pytorch_restatement(variant):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("variant", ["1dpp", "2dpp"])
+def test_fused_gelu_model_equals_unfused(variant):
+    """fuse_gelu=True moves the GELU in front of each block's second conv into that conv's kernels; the
+    model's output and every gradient must not change beyond rounding."""
+    torch.manual_seed(3)
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    kw = dict(depths=(1, 1, 1, 1), dims=(32, 64, 96, 128), variant=variant, stem_dim1=16, layer_scale_init_value=0.5,
+              num_classes=10)
+    a = convnext1d.ConvNeXt1D(**kw).cuda().train()
+    for p in a.parameters():
+        if p.dim() > 1:
+            torch.nn.init.normal_(p, std=0.1)
+    b = convnext1d.ConvNeXt1D(fuse_gelu=True, **kw).cuda().train()
+    b.load_state_dict(a.state_dict())
+    img = torch.randn(2, 3, 64, 64, device="cuda")
+    target = torch.randn(2, 10, device="cuda")
+    outs = []
+    for m in (a, b):
+        out = m(img)
+        (out * target).sum().backward()
+        outs.append(out.detach())
+    assert float((outs[0] - outs[1]).abs().max()) <= 1e-4 * float(outs[0].abs().max())
+    ga, gb = dict(a.named_parameters()), dict(b.named_parameters())
+    for k, p in ga.items():
+        if p.grad is None:
+            assert gb[k].grad is None
+            continue
+        err = float((p.grad - gb[k].grad).abs().max() / p.grad.abs().max().clamp_min(1e-30))
+        assert err < 5e-4, (k, err)
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("variant", ["1d", "1dpp", "2dpp"])
 def test_model_training_step_gradients(variant):
     """Forward + backward through the autograd function of every oriented conv in the model
