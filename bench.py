@@ -823,7 +823,8 @@ def run_train(args):
     world, rank, local, dev = init_ranks()
     torch.manual_seed(rank)
     batch = args.batch if args.batch != 64 else 64
-    model = convnext1d.convnext_base(variant="1dpp", drop_path_rate=0.0).to(dev).bfloat16().train()
+    model = convnext1d.convnext_base(variant="1dpp", drop_path_rate=0.0, fuse_gelu="auto" if args.fuse_gelu else False)
+    model = model.to(dev).bfloat16().train()
     flat, params = flat_gradient_buffer(model)
     opt = torch.optim.AdamW(params, lr=1e-4, weight_decay=0.05, fused=True)
     nsets = 2
@@ -868,6 +869,7 @@ def run_train(args):
             "config": {"workload": "ConvNeXt-B-1D++ training step: depths 3/3/27/3, dims 128-1024, K=(15,31), "
                                    f"batch {batch} per GPU, 224x224x3 bf16, cross-entropy, AdamW (fused), random init",
                        "l2": "activations exceed L2; 2 input batches rotate", "launch": "eager",
+                       "gelu": "inside the second conv's kernels on 56x56 and 28x28 maps" if args.fuse_gelu else "separate pass",
                        "parallelism": f"dp{world}: one NCCL all-reduce of the flat gradient buffer "
                                       f"({flat.numel() * flat.element_size() / 1e6:.0f} MB) per step",
                        "parameters": sum(p.numel() for p in model.parameters())},
@@ -958,6 +960,8 @@ def main():
     ap.add_argument("--route", type=int, default=0, choices=[0, 1, 2, 3, 4],
                     help="kernel family: 0 automatic (default), 1 general only, 2 prefer tiled, 3 prefer direct, "
                          "4 prefer whole-line")
+    ap.add_argument("--fuse-gelu", action="store_true",
+                    help="train workload: apply each block's GELU inside its second oriented conv's kernels")
     ap.add_argument("--no-model", action="store_true", help="sweep workload: skip the model figure")
     args = ap.parse_args()
     if args.route and args.impl == "ours":

@@ -262,10 +262,10 @@ class ConvNeXt1D(nn.Module):
                       layer_offset=layer_wise_rotation_offset(j, cycle), arbitrary_size=arbitrary_size)
                 for j in range(depths[i])]))
             cur += depths[i]
-        if fuse_gelu:      # 1D++ / 2D++: GELU applied while dwconv2 loads its input
+        if fuse_gelu:      # 1D++ / 2D++: dwconv2 takes the pre-activation tensor (True or "auto")
             for m in self.modules():
                 if isinstance(m, (Block1DPP, Block2DPP)):
-                    m.dwconv2.gelu_input = True
+                    m.dwconv2.gelu_input = fuse_gelu
         self.norm = nn.LayerNorm(dims[-1], eps=1e-6)
         self.head = nn.Linear(dims[-1], num_classes)
         self.apply(self._init_weights)

@@ -115,7 +115,10 @@ class DepthwiseOrientedConv1d(nn.Conv2d):
         # Set by a caller whose input is a pre-activation tensor: forward then computes
         # conv(GELU(x)) with the GELU applied inside the kernels (the reference runs F.gelu as a
         # separate pass in front of its second block conv, models/convnext.py:389-391).  Not a
-        # constructor argument: the reference's signature is kept as it is.
+        # constructor argument: the reference's signature is kept as it is.  True: always inside
+        # the kernels; "auto": inside the kernels where that saves time (large maps, which the
+        # tiled kernels serve anyway), as a separate F.gelu pass elsewhere (small maps, where
+        # the kernel families without activation-on-load are the faster ones).
         self.gelu_input = False
         # kept for parity with the reference attribute (dwoconv1d.py:136-141); the kernels
         # add the identity tap themselves and never read this tensor
@@ -152,9 +155,26 @@ class DepthwiseOrientedConv1d(nn.Conv2d):
             self._plan_key = key
         return self._plan
 
+    def _gelu_in_kernel(self, x) -> bool:
+        """The "auto" rule: activation on load only on maps of 28x28 and larger that the tiled
+        kernels serve anyway.  What it buys is memory (the GELU output is never stored, one 4*dim
+        activation less per block kept for backward), not time: the tiled kernels are bound by
+        instruction issue, so the erf costs more there than the memory pass it removes (B200,
+        ConvNeXt-B-1D++ training step, batch 64: 60.3 ms unfused, 63.5 ms with this rule, 74.1 ms
+        with the activation forced into every stage)."""
+        if self.gelu_input != "auto":
+            return bool(self.gelu_input)
+        if not (x.is_cuda and x.dim() == 4 and self.nhwc and self.stride[0] == 1):
+            return False
+        N, H, W, _ = x.shape
+        return H * W >= 28 * 28 and ops.uses_tiled(self._get_plan(), N, H, W, 1, True, x.dtype)
+
     def _apply_op(self, x):
+        gelu = self._gelu_in_kernel(x)
+        if self.gelu_input and not gelu:
+            x = torch.nn.functional.gelu(x)
         return _DepthwiseOrientedConv1d.apply(x, self.weight, self.theta, self.bias, self._get_plan(),
-                                              self.stride[0], self.nhwc, self.add_identity, self.gelu_input)
+                                              self.stride[0], self.nhwc, self.add_identity, gelu)
 
     def forward_safe(self, x):
         """Any H x W; output extents ceil(H/stride) x ceil(W/stride) (dwoconv1d.py:154-187)."""

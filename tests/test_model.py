@@ -114,8 +114,8 @@ def test_model_forward_matches_pytorch_restatement(variant):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("variant", ["1dpp", "2dpp"])
-def test_fused_gelu_model_equals_unfused(variant):
+@pytest.mark.parametrize("variant,fuse", [("1dpp", True), ("2dpp", True), ("1dpp", "auto")])
+def test_fused_gelu_model_equals_unfused(variant, fuse):
     """fuse_gelu=True moves the GELU in front of each block's second conv into that conv's kernels; the
     model's output and every gradient must not change beyond rounding."""
     torch.manual_seed(3)
@@ -127,9 +127,10 @@ def test_fused_gelu_model_equals_unfused(variant):
     for p in a.parameters():
         if p.dim() > 1:
             torch.nn.init.normal_(p, std=0.1)
-    b = convnext1d.ConvNeXt1D(fuse_gelu=True, **kw).cuda().train()
+    b = convnext1d.ConvNeXt1D(fuse_gelu=fuse, **kw).cuda().train()
     b.load_state_dict(a.state_dict())
-    img = torch.randn(2, 3, 64, 64, device="cuda")
+    side = 128 if fuse == "auto" else 64       # "auto" fuses on maps of 28x28 and more: stage 1 at 32x32
+    img = torch.randn(2, 3, side, side, device="cuda")
     target = torch.randn(2, 10, device="cuda")
     outs = []
     for m in (a, b):
