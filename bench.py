@@ -618,7 +618,7 @@ def run_case(args):
         bias = torch.randn((C,), generator=g).to(dev)
         alg = n * H * W * (3 + C) * es
     else:
-        plan = o1d.Plan(round_robin_angles(C) if args.angles == "rr" else block_angles(C), K)
+        plan = o1d.Plan(round_robin_angles(C) if args.angles == "rr" else [0.0] * C if args.angles == "zero" else block_angles(C), K)
         w = (0.02 * torch.randn((C, 1, 1, K), generator=g)).to(dev)
         bias = torch.randn((C,), generator=g).to(dev)
         sets = [(torch.randn((n, H, W, C), generator=g).to(dev).to(dtype),
@@ -956,8 +956,8 @@ def main():
     ap.add_argument("--case", default=None, help="run one kernel case alone, e.g. fprop_f32_56x56x96")
     ap.add_argument("--batch", type=int, default=64, help="batch for --case")
     ap.add_argument("--reps", type=int, default=3, help="launches for --case")
-    ap.add_argument("--angles", default="rr", choices=["rr", "block"], help="channel->orientation map for --case")
-    ap.add_argument("--route", type=int, default=0, choices=[0, 1, 2, 3, 4],
+    ap.add_argument("--angles", default="rr", choices=["rr", "block", "zero"], help="channel->orientation map for --case")
+    ap.add_argument("--route", type=int, default=0, choices=[0, 1, 2, 3, 4, 5],
                     help="kernel family: 0 automatic (default), 1 general only, 2 prefer tiled, 3 prefer direct, "
                          "4 prefer whole-line")
     ap.add_argument("--fuse-gelu", action="store_true",

@@ -62,7 +62,7 @@ const char *o1d_last_error(void);
 
 /* Kernel routing, for tests and A/B timing: 0 = automatic, 1 = general kernels only,
  * 2 = prefer the tiled kernels, 3 = prefer the direct kernels, 4 = prefer the whole-line
- * kernels.  Process-wide.  (No counterpart in
+ * kernels, 5 = prefer the walker kernels.  Process-wide.  (No counterpart in
  * the reference, which picks general vs specialised kernels with the SPECIALIZED
  * environment variable at import time, models/convnext.py:16-23.) */
 int o1d_set_route(int route);
@@ -79,7 +79,8 @@ enum {
     O1D_ROUTE_TILED = 1,     /* restaged channel planes with register windows                  */
     O1D_ROUTE_DIRECT = 2,    /* TMA halo tiles, one tap list per thread                        */
     O1D_ROUTE_PLANE7 = 3,    /* 7x7 maps, one channel plane per thread                         */
-    O1D_ROUTE_LINES = 4      /* whole lines per thread (round-robin angle assignment)          */
+    O1D_ROUTE_LINES = 4,     /* whole lines per thread (round-robin angle assignment)          */
+    O1D_ROUTE_WALK = 5       /* items computed in place in their NHWC layout (square fp32 maps) */
 };
 int o1d_last_route(void);
 

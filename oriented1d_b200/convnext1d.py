@@ -151,7 +151,7 @@ class Block1DPP(Block1D):
                                           arbitrary_size=arbitrary_size)
 
     def forward(self, x):
-        fused = self.dwconv2.gelu_input              # the GELU then runs inside dwconv2's kernels
+        fused = getattr(self.dwconv2, "gelu_input", False)      # the GELU then runs inside dwconv2's kernels
         y = self.pwconv2(self.dwconv2(self._mlp_in(self.dwconv1(x), gelu=not fused)))
         return self._residual(x, y)
 
@@ -193,7 +193,7 @@ class Block2DPP(Block2D):
                                           arbitrary_size=arbitrary_size)
 
     def forward(self, x):
-        fused = self.dwconv2.gelu_input
+        fused = getattr(self.dwconv2, "gelu_input", False)
         y = self._mlp_in(self._dw2d(self.dwconv1, x), gelu=not fused).contiguous()
         return self._residual(x, self.pwconv2(self.dwconv2(y)))
 
@@ -264,7 +264,8 @@ class ConvNeXt1D(nn.Module):
             cur += depths[i]
         if fuse_gelu:      # 1D++ / 2D++: dwconv2 takes the pre-activation tensor (True or "auto")
             for m in self.modules():
-                if isinstance(m, (Block1DPP, Block2DPP)):
+                # only the operator module itself knows the flag (a wrapper for arbitrary sizes keeps the separate pass)
+                if isinstance(m, (Block1DPP, Block2DPP)) and hasattr(m.dwconv2, "_apply_op"):
                     m.dwconv2.gelu_input = fuse_gelu
         self.norm = nn.LayerNorm(dims[-1], eps=1e-6)
         self.head = nn.Linear(dims[-1], num_classes)

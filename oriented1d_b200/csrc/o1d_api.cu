@@ -17,6 +17,7 @@
 #include "o1d_transpose.cuh"
 #include "o1d_pointwise.cuh"
 #include "o1d_wline.h"
+#include "o1d_walk.h"
 
 using namespace o1d;
 
@@ -25,7 +26,7 @@ namespace {
 thread_local char g_err[256] = "";
 thread_local int g_last_route = O1D_ROUTE_NONE;   // kernel family of this thread's last operator call
 int g_force_generic = 0;   // o1d_set_route(): 1 = general kernels only (testing aid)
-int g_prefer = 0;          // o1d_set_route(): 2 = prefer the tiled kernels, 3 = direct, 4 = whole-line
+int g_prefer = 0;          // o1d_set_route(): 2 = prefer the tiled kernels, 3 = direct, 4 = whole-line, 5 = walker
 
 int cuda_fail(cudaError_t e, const char *what) {
     snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
@@ -332,6 +333,32 @@ int try_wline(const void *x, const float *w, const float *bias, const PlanHeader
     return O1D_OK;
 }
 
+// Forward / stride-1 input gradient through the walker kernels (square fp32 NHWC maps, canonical lines).
+int try_walk(const void *x, const float *w, const float *bias, const PlanHeader &ph, const void *plan_host,
+             const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride, int layout, int dtype,
+             int add_identity, int flip, cudaStream_t st, const DeviceInfo &d) {
+    if (g_force_generic || !ph.all_canon || ph.chan_off == 0) return kNotTiled;
+    const int esize = dtype == O1D_F32 ? 4 : 2;
+    const int8_t *chan_host = reinterpret_cast<const int8_t *>(static_cast<const char *>(plan_host) + ph.chan_off);
+    WalkConfig cfg;
+    if (!walk_configure(chan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, &cfg)) return kNotTiled;
+    if (((uintptr_t)y & 15) != 0) return kNotTiled;
+    const cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    const cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)W * C * esize, (cuuint64_t)H * W * C * esize};
+    const cuuint32_t box[4] = {(cuuint32_t)cfg.box_c, (cuuint32_t)cfg.box_w, (cuuint32_t)cfg.box_rows, 1};
+    CUtensorMap in_map, out_map;
+    O1D_MAP(encode_map4(&in_map, x, esize, dims, strides, box), "walker fprop (input)");
+    O1D_MAP(encode_map4(&out_map, y, esize, dims, strides, box), "walker fprop (output)");
+    int *flag = nullptr;
+    int rc = device_flag_ptr(&flag);
+    if (rc) return rc;
+    PlanView pv = plan_view(plan_dev, ph);
+    const cudaError_t e = walk_launch_fprop(cfg, in_map, out_map, w, bias, pv.chan, flip, add_identity, flag, st);
+    if (e != cudaSuccess) return cuda_fail(e, "walker fprop launch");
+    g_last_route = O1D_ROUTE_WALK;
+    return O1D_OK;
+}
+
 // Route of a forward-type call (flip = 1: stride-1 input gradient):
 //   1. direct kernels when one tile holds a whole image (small maps),
 //   2. tiled kernels (canonical lines, stride 1, sizes in multiples of 7/8),
@@ -345,6 +372,11 @@ int route_forward(const void *x, const float *w, const float *bias, const PlanHe
     if (act || pre)       // activation on load / its derivative on store: tiled kernels, else general
         return try_tiled(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
                          flip, act, pre, st, d);
+    if (g_prefer == 5) {                    // items computed in place in their NHWC layout
+        rc = try_walk(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity, flip,
+                      st, d);
+        if (rc != kNotTiled) return rc;
+    }
     if (g_prefer == 0 || g_prefer == 4) {   // stage maps with whole lines per thread
         rc = try_wline(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
                        flip, st, d, /*need_two_ctas=*/g_prefer == 0);
@@ -495,7 +527,7 @@ const char *o1d_last_error(void) { return g_err; }
 int o1d_last_route(void) { return g_last_route; }
 
 int o1d_set_route(int route) {
-    if (route < 0 || route > 4) return O1D_ERR_INVALID;
+    if (route < 0 || route > 5) return O1D_ERR_INVALID;
     g_force_generic = (route == 1);
     g_prefer = (route >= 2) ? route : 0;
     return O1D_OK;

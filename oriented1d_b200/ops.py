@@ -231,11 +231,12 @@ def uses_tiled(plan: Plan, N: int, H: int, W: int, stride: int, nhwc: bool, dtyp
 
 def set_route(route) -> None:
     """Testing aid.  False/0: automatic choice; True/1: general kernels only; 2: prefer the
-    tiled kernels; 3: prefer the direct kernels."""
+    tiled kernels; 3: prefer the direct kernels; 4: the whole-line kernels; 5: the walker kernels
+    (the last two serve square fp32 NHWC stage maps only and fall through elsewhere)."""
     check(lib.o1d_set_route(int(route)), "o1d_set_route")
 
 
-ROUTE_NAMES = {-1: "none", 0: "general", 1: "tiled", 2: "direct", 3: "plane7", 4: "lines"}
+ROUTE_NAMES = {-1: "none", 0: "general", 1: "tiled", 2: "direct", 3: "plane7", 4: "lines", 5: "walk"}
 
 
 def last_route() -> str:

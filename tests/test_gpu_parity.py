@@ -404,6 +404,55 @@ def test_whole_line_kernels_full_batch():
     assert o1d.ops.device_status() == 0
 
 
+@pytest.mark.parametrize("mode,K,N,C,hw", [("rr", 31, 3, 96, 56), ("model+", 31, 2, 96, 56), ("zero", 31, 2, 32, 56),
+                                           ("rr", 15, 2, 96, 56), ("rr", 7, 1, 32, 56), ("rr", 31, 3, 64, 28),
+                                           ("model", 27, 2, 64, 28)])
+def test_walker_kernels(oracle, mode, K, N, C, hw):
+    """The walker family (route 5: items kept in their NHWC layout in shared memory and computed in
+    place, TMA loads and stores on both sides) against the oracle, with bias and the identity tap,
+    forward and input gradient, round-robin and block-wise angle assignment."""
+    x, w, dy = make_inputs(K * 5 + N + hw, N, C, hw, hw, K)
+    th = angle_list(mode, C)
+    bias = np.linspace(-1, 1, C).astype(np.float32)
+    plan = o1d.Plan(th, K)
+    wd, bd = torch.from_numpy(w).to(DEV), torch.from_numpy(bias).to(DEV)
+    try:
+        o1d.ops.set_route(5)
+        for resid in (False, True):
+            y = o1d.fprop(_to_dev(x, True), wd, bd, plan, 1, True, resid)
+            assert o1d.ops.last_route() == "walk"
+            dx = o1d.dgrad(_to_dev(dy, True), wd, plan, hw, hw, 1, True, resid)
+            assert o1d.ops.last_route() == "walk"
+            ry, (rdx, _, _) = _oracle_fwd_bwd(oracle, x, w, th, dy, bias, 1, resid)
+            assert rel_err(_to_nchw(y, True), ry) <= TOL_FPROP
+            assert rel_err(_to_nchw(dx, True), rdx) <= TOL_DGRAD
+    finally:
+        o1d.ops.set_route(0)
+    assert o1d.ops.device_status() == 0
+
+
+def test_walker_kernels_full_batch():
+    """Batch 128 through the walker family: every CTA streams about ten items through its two tiles;
+    bit-equal to the same images run two at a time, and equal to the tiled kernels up to rounding."""
+    C, hw, K, N = 96, 56, 31, 128
+    g = torch.Generator(device="cpu").manual_seed(5)
+    x = torch.randn((N, hw, hw, C), generator=g).to(DEV)
+    w = (0.02 * torch.randn((C, 1, 1, K), generator=g)).to(DEV)
+    plan = o1d.Plan(angle_list("rr", C), K)
+    try:
+        o1d.ops.set_route(5)
+        y = o1d.fprop(x, w, None, plan, 1, True)
+        assert o1d.ops.last_route() == "walk"
+        for i in (0, 37, 126):
+            assert torch.equal(o1d.fprop(x[i:i + 2].contiguous(), w, None, plan, 1, True), y[i:i + 2])
+        o1d.ops.set_route(2)
+        yt = o1d.fprop(x, w, None, plan, 1, True)
+    finally:
+        o1d.ops.set_route(0)
+    assert float((y - yt).abs().max()) <= 1e-5 * float(yt.abs().max())
+    assert o1d.ops.device_status() == 0
+
+
 @pytest.mark.parametrize("K", [7, 13, 15, 27])
 def test_tiled_short_kernels(oracle, K):
     """K < 31 uses the centre of the 31-tap line."""
