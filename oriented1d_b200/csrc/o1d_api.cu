@@ -201,6 +201,7 @@ int try_tiled(const void *x, const float *w, const float *bias, const PlanHeader
     if (!tiled_configure(ph, plan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, OP_FPROP, &cfg))
         return kNotTiled;
     if (((uintptr_t)y & 15) != 0 || ((uintptr_t)pre & 15) != 0) return kNotTiled;
+    if ((act || pre) && !tiled_supports_act(cfg)) return kNotTiled;
     CUtensorMap map;
     O1D_MAP(make_nhwc_tensor_map(&map, x, N, H, W, C, esize, cfg.p.CC, cfg.p.BR), "tiled fprop");
     cfg.p.flip = flip;
@@ -426,6 +427,7 @@ int try_tiled_wgrad(const void *dy, const void *x, const PlanHeader &ph, const v
     O1D_MAP(make_nhwc_tensor_map(&map, x, N, H, W, C, esize, cfg.p.CC, cfg.p.BR), "tiled wgrad");
     PlanView pv = plan_view(plan_dev, ph);
     float *partial = (float *)workspace;
+    if (act && !tiled_supports_act(cfg)) return kNotTiled;
     cfg.p.act = act;
     cudaError_t e = launch_tiled<OP_WGRAD>(cfg, dtype, map, nullptr, nullptr, pv, const_cast<void *>(dy), partial,
                                            nullptr, st);

@@ -272,7 +272,9 @@ __host__ __device__ inline int wgrad_item_lo(int cta, int ctas, int total) {
 //           for stride 1 is the input gradient.  `io` is y.
 // OP_WGRAD: partial[(cta, visit)][CC][32] = per-chunk sums of x (*) dy; `io` is dy.
 // ---------------------------------------------------------------------------------
-template <typename T, int R, int JH, int OP>
+// ACT: the instantiation that applies GELU while restaging (p.act) and multiplies the stored
+// result by GELU'(preact) (preact != nullptr); the plain instantiation carries neither test.
+template <typename T, int R, int JH, int OP, bool ACT>
 __global__ void __launch_bounds__(kTiledThreads, 1)
 tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restrict__ wgt,
                   const float *__restrict__ bias, const int8_t *__restrict__ chan,
@@ -558,7 +560,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                 for (int pix = mover ? pix_first : band_pixels; pix < band_pixels; pix += pix_step) {
                     float f[VE];
                     Vec16<T>::unpack(stg[pix * GV + g_vec], f);
-                    if (p.act) {
+                    if (ACT && p.act) {
 #pragma unroll
                         for (int j = 0; j < VE; j++) f[j] = gelu_exact(f[j]);
                     }
@@ -737,7 +739,7 @@ tiled_nhwc_kernel(const __grid_constant__ CUtensorMap tmap, const float *__restr
                     float f[VE];
 #pragma unroll
                     for (int j = 0; j < VE; j++) { f[j] = src[idx[j]]; idx[j] += ostep[j]; }
-                    if (preact) {   // input gradient of a conv over GELU(preact): times GELU'(preact)
+                    if (ACT && preact) {   // input gradient of a conv over GELU(preact): times GELU'(preact)
                         float g[VE];
                         Vec16<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(preact + (gdst - io) + (size_t)pix * C)), g);
 #pragma unroll

@@ -341,23 +341,30 @@ inline int make_nhwc_tensor_map(CUtensorMap *map, const void *base, int N, int H
     return encode_map4(map, base, esize, dims, strides, box);
 }
 
-template <typename T, int R, int JH, int OP>
+template <typename T, int R, int JH, int OP, bool ACT>
 cudaError_t launch_tiled_one(const TiledConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
                              const PlanView &pv, void *io, float *partial, const void *pre, cudaStream_t st) {
-    auto kern = tiled_nhwc_kernel<T, R, JH, OP>;
+    auto kern = tiled_nhwc_kernel<T, R, JH, OP, ACT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.smem_bytes);
     if (e != cudaSuccess) return e;
     kern<<<cfg.grid, cfg.threads, cfg.smem_bytes, st>>>(map, w, bias, pv.chan, (T *)io, partial, (const T *)pre, cfg.p);
     return cudaGetLastError();
 }
 
+// Activation on load / its derivative on store exist for the full 31-tap reach only (the second
+// conv of a 1D++ block has K = 31); tiled_supports_act() tells the caller beforehand.
+inline bool tiled_supports_act(const TiledConfig &cfg) { return cfg.jh == kHalf; }
+
 template <typename T, int R, int OP>
 cudaError_t launch_tiled_jh(const TiledConfig &cfg, const CUtensorMap &map, const float *w, const float *bias,
                             const PlanView &pv, void *io, float *partial, const void *pre, cudaStream_t st) {
+    if (cfg.p.act || pre)
+        return cfg.jh == kHalf ? launch_tiled_one<T, R, kHalf, OP, true>(cfg, map, w, bias, pv, io, partial, pre, st)
+                               : cudaErrorNotSupported;
     switch (cfg.jh) {
-        case 7: return launch_tiled_one<T, R, 7, OP>(cfg, map, w, bias, pv, io, partial, pre, st);
-        case 9: return launch_tiled_one<T, R, 9, OP>(cfg, map, w, bias, pv, io, partial, pre, st);
-        default: return launch_tiled_one<T, R, kHalf, OP>(cfg, map, w, bias, pv, io, partial, pre, st);
+        case 7: return launch_tiled_one<T, R, 7, OP, false>(cfg, map, w, bias, pv, io, partial, pre, st);
+        case 9: return launch_tiled_one<T, R, 9, OP, false>(cfg, map, w, bias, pv, io, partial, pre, st);
+        default: return launch_tiled_one<T, R, kHalf, OP, false>(cfg, map, w, bias, pv, io, partial, pre, st);
     }
 }
 
