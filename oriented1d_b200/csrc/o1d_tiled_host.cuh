@@ -173,8 +173,13 @@ inline bool tiled_configure_pitch(const PlanHeader &ph, const void *plan_host, i
                 // DRAM-friendly image-major order with a single flush.  Worth giving up some SMs
                 // (forward: up to 15%; weight gradient: up to 30%, chunk-major order re-reads
                 // every DRAM sector).
+                // Not for the forward kernels when chunks differ in line kinds (block-wise angle
+                // assignment): slanted chunks cost more than axis chunks, and CTAs pinned to one
+                // chunk would finish at different times; a grid that is no multiple of the chunk
+                // count rotates every CTA through all chunks.
+                const bool mixed_cost = op != OP_WGRAD && comps[ci].n > 1;
                 const int g = (best.grid / p.nchunks) * p.nchunks;
-                if (g * 100 >= best.grid * (op == OP_WGRAD ? 70 : 85)) {
+                if (!mixed_cost && g * 100 >= best.grid * (op == OP_WGRAD ? 70 : 85)) {
                     best.grid = g;
                     best.p.order = 0;
                 }
