@@ -901,6 +901,36 @@ int launch_ln(const void *x, const float *gamma, const float *beta, void *y, int
     O1D_CUDA(cudaGetLastError());
     return O1D_OK;
 }
+// Grid of the LayerNorm backward for `rows` rows handled by groups of G lanes.
+inline int ln_bwd_grid(int64_t rows, int G, int sms) {
+    const int64_t groups = (rows * G + kLnThreads - 1) / kLnThreads;
+    const int64_t cap = (int64_t)sms * 4;
+    return (int)(groups < cap ? (groups > 0 ? groups : 1) : cap);
+}
+template <typename T, int G, int VPL>
+int launch_ln_bwd(const void *x, const void *dy, const float *gamma, void *dx, float *dgamma, float *dbeta,
+                  float *partial, int64_t rows, int C, float eps, cudaStream_t st, const DeviceInfo &d) {
+    const int grid = ln_bwd_grid(rows, G, d.sms);
+    const int smem = (kLnThreads / 32) * 2 * C * (int)sizeof(float);
+    auto kern = layernorm_cl_bwd_kernel<T, G, VPL>;
+    if (smem > 48 * 1024) O1D_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<grid, kLnThreads, smem, st>>>((const T *)x, (const T *)dy, gamma, (T *)dx, partial, rows, C, eps);
+    O1D_CUDA(cudaGetLastError());
+    layernorm_cl_bwd_final_kernel<<<ceil_div(2 * C, 256), 256, 0, st>>>(partial, dgamma, dbeta, grid, C);
+    O1D_CUDA(cudaGetLastError());
+    return O1D_OK;
+}
+template <typename T>
+int dispatch_ln_bwd(const void *x, const void *dy, const float *gamma, void *dx, float *dgamma, float *dbeta,
+                    float *partial, int64_t rows, int C, float eps, cudaStream_t st, const DeviceInfo &d) {
+    const int nvec = C / (16 / (int)sizeof(T));
+    if (nvec <= 8) return launch_ln_bwd<T, 8, 1>(x, dy, gamma, dx, dgamma, dbeta, partial, rows, C, eps, st, d);
+    if (nvec <= 16) return launch_ln_bwd<T, 8, 2>(x, dy, gamma, dx, dgamma, dbeta, partial, rows, C, eps, st, d);
+    if (nvec <= 32) return launch_ln_bwd<T, 16, 2>(x, dy, gamma, dx, dgamma, dbeta, partial, rows, C, eps, st, d);
+    if (nvec <= 64) return launch_ln_bwd<T, 32, 2>(x, dy, gamma, dx, dgamma, dbeta, partial, rows, C, eps, st, d);
+    if (nvec <= 128) return launch_ln_bwd<T, 32, 4>(x, dy, gamma, dx, dgamma, dbeta, partial, rows, C, eps, st, d);
+    return O1D_ERR_UNSUPPORTED;
+}
 template <typename T>
 int dispatch_ln(const void *x, const float *gamma, const float *beta, void *y, int64_t rows, int C, float eps,
                 int gelu, cudaStream_t st, const DeviceInfo &d) {
@@ -930,6 +960,32 @@ int o1d_layernorm_cl(const void *x, const float *gamma, const float *beta, void 
     cudaStream_t st = (cudaStream_t)stream;
     return dtype == O1D_F32 ? dispatch_ln<float>(x, gamma, beta, y, rows, C, eps, gelu, st, d)
                             : dispatch_ln<__nv_bfloat16>(x, gamma, beta, y, rows, C, eps, gelu, st, d);
+}
+
+size_t o1d_layernorm_cl_bwd_workspace_bytes(long long rows, int C) {
+    if (rows <= 0 || C <= 0) return 0;
+    DeviceInfo d;
+    if (device_info(&d)) return 0;
+    return (size_t)d.sms * 4 * 2 * (size_t)C * sizeof(float);       // one partial per CTA of the largest grid
+}
+
+int o1d_layernorm_cl_bwd(const void *x, const void *dy, const float *gamma, void *dx, float *dgamma, float *dbeta,
+                         void *workspace, size_t workspace_bytes, long long rows, int C, float eps, int dtype,
+                         void *stream) {
+    if (!x || !dy || !gamma || !dx || !dgamma || !dbeta || rows <= 0 || C <= 0 ||
+        (dtype != O1D_F32 && dtype != O1D_BF16))
+        return O1D_ERR_INVALID;
+    const int ve = dtype == O1D_F32 ? 4 : 8;
+    if (C % ve != 0 || C / ve > 128 || ((uintptr_t)x & 15) || ((uintptr_t)dy & 15) || ((uintptr_t)dx & 15))
+        return O1D_ERR_UNSUPPORTED;
+    if (!workspace || workspace_bytes < o1d_layernorm_cl_bwd_workspace_bytes(rows, C)) return O1D_ERR_WORKSPACE;
+    DeviceInfo d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    return dtype == O1D_F32
+               ? dispatch_ln_bwd<float>(x, dy, gamma, dx, dgamma, dbeta, (float *)workspace, rows, C, eps, st, d)
+               : dispatch_ln_bwd<__nv_bfloat16>(x, dy, gamma, dx, dgamma, dbeta, (float *)workspace, rows, C, eps, st, d);
 }
 
 int o1d_pointwise_in(const void *x, const float *w, const float *bias, void *y, int N, int Cin, long long HW,

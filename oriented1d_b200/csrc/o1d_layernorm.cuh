@@ -87,4 +87,148 @@ layernorm_cl_kernel(const T *__restrict__ x, const float *__restrict__ gamma, co
     }
 }
 
+
+// Backward of the same LayerNorm (no GELU): dx, and per-CTA partial sums of dgamma / dbeta that a
+// second kernel adds in CTA order (no atomics: bit-reproducible).  The row statistics are
+// recomputed from x (the row sits in registers anyway), so the forward pass keeps nothing but x.
+//   xhat = (x - mean) * rstd,  g = dy * gamma,
+//   dx = rstd * (g - mean_C(g) - xhat * mean_C(g * xhat)),  dgamma = sum_rows dy * xhat,  dbeta = sum_rows dy.
+// F.layer_norm's backward in the reference's training step (models/convnext.py:28-56 through autograd).
+// partial: [gridDim.x][2][C] floats.  Dynamic shared memory: (kLnThreads / 32) * 2 * C floats.
+template <typename T, int G, int VPL>
+__global__ void __launch_bounds__(kLnThreads)
+layernorm_cl_bwd_kernel(const T *__restrict__ x, const T *__restrict__ dy, const float *__restrict__ gamma,
+                        T *__restrict__ dx, float *__restrict__ partial, int64_t rows, int C, float eps) {
+    extern __shared__ float ln_red[];                 // [warps][2][C]
+    constexpr int VE = GVec<T>::N;
+    const int lane_in_group = threadIdx.x % G;
+    const int64_t group = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+    const int64_t ngroups = ((int64_t)gridDim.x * blockDim.x) / G;
+    const int nvec = C / VE;
+    float g[VPL][VE], sg[VPL][VE], sb[VPL][VE];
+#pragma unroll
+    for (int v = 0; v < VPL; v++) {
+        const int vi = lane_in_group + v * G;
+#pragma unroll
+        for (int j = 0; j < VE; j++) {
+            g[v][j] = (vi < nvec) ? __ldg(gamma + vi * VE + j) : 0.f;
+            sg[v][j] = 0.f; sb[v][j] = 0.f;
+        }
+    }
+    const float inv_c = 1.f / (float)C;
+    // The loop count must be the same for every lane of a warp: the column sums are shuffled across the
+    // warp's groups after the loop, and a lane that left the loop early would meet the others at a
+    // different shuffle.  So a warp walks its groups' rows together; a group past the last row runs on zeros.
+    const int group_in_warp = (threadIdx.x & 31) / G;
+    for (int64_t rb = group - group_in_warp; rb < rows; rb += ngroups) {
+        const int64_t r = rb + group_in_warp;
+        const bool act = r < rows;
+        const T *xr = x + (act ? r : 0) * C, *dr = dy + (act ? r : 0) * C;
+        float f[VPL][VE], d[VPL][VE];
+        float sum = 0.f;
+#pragma unroll
+        for (int v = 0; v < VPL; v++) {
+            const int vi = lane_in_group + v * G;
+            if (act && vi < nvec) {
+                GVec<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(xr + vi * VE)), f[v]);
+                GVec<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(dr + vi * VE)), d[v]);
+#pragma unroll
+                for (int j = 0; j < VE; j++) sum += f[v][j];
+            } else {
+#pragma unroll
+                for (int j = 0; j < VE; j++) { f[v][j] = 0.f; d[v][j] = 0.f; }
+            }
+        }
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mean = sum * inv_c;
+        float sq = 0.f;
+#pragma unroll
+        for (int v = 0; v < VPL; v++) {
+            const int vi = lane_in_group + v * G;
+            if (vi < nvec) {
+#pragma unroll
+                for (int j = 0; j < VE; j++) { const float c = f[v][j] - mean; sq += c * c; }
+            }
+        }
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        const float rstd = rsqrtf(sq * inv_c + eps);
+        float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+        for (int v = 0; v < VPL; v++) {
+            const int vi = lane_in_group + v * G;
+            if (vi < nvec) {
+#pragma unroll
+                for (int j = 0; j < VE; j++) {
+                    const float xh = (f[v][j] - mean) * rstd;
+                    f[v][j] = xh;                                 // keep xhat
+                    const float gg = d[v][j] * g[v][j];
+                    c1 += gg; c2 += gg * xh;
+                    sg[v][j] += d[v][j] * xh; sb[v][j] += d[v][j];
+                }
+            }
+        }
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) {
+            c1 += __shfl_xor_sync(0xffffffffu, c1, o);
+            c2 += __shfl_xor_sync(0xffffffffu, c2, o);
+        }
+        c1 *= inv_c; c2 *= inv_c;
+        T *xo = dx + (act ? r : 0) * C;
+#pragma unroll
+        for (int v = 0; v < VPL; v++) {
+            const int vi = lane_in_group + v * G;
+            if (act && vi < nvec) {
+                float o[VE];
+#pragma unroll
+                for (int j = 0; j < VE; j++) o[j] = rstd * (d[v][j] * g[v][j] - c1 - f[v][j] * c2);
+                *reinterpret_cast<uint4 *>(xo + vi * VE) = GVec<T>::pack(o);
+            }
+        }
+    }
+    // column sums: groups of one warp (same lane_in_group), then the warps of the CTA in order
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+#pragma unroll
+    for (int v = 0; v < VPL; v++)
+#pragma unroll
+        for (int j = 0; j < VE; j++) {
+#pragma unroll
+            for (int o = G; o < 32; o <<= 1) {
+                sg[v][j] += __shfl_xor_sync(0xffffffffu, sg[v][j], o);
+                sb[v][j] += __shfl_xor_sync(0xffffffffu, sb[v][j], o);
+            }
+        }
+    if (lane < G) {
+#pragma unroll
+        for (int v = 0; v < VPL; v++) {
+            const int vi = lane_in_group + v * G;
+            if (vi < nvec) {
+#pragma unroll
+                for (int j = 0; j < VE; j++) {
+                    ln_red[(warp * 2 + 0) * C + vi * VE + j] = sg[v][j];
+                    ln_red[(warp * 2 + 1) * C + vi * VE + j] = sb[v][j];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 2 * C; e += blockDim.x) {
+        const int which = e / C, c = e - which * C;
+        float s = 0.f;
+        for (int w = 0; w < nwarps; w++) s += ln_red[(w * 2 + which) * C + c];
+        partial[(size_t)blockIdx.x * 2 * C + e] = s;
+    }
+}
+
+// dgamma[c] = sum over CTAs (in order) of partial[cta][0][c], dbeta likewise from partial[cta][1][c].
+__global__ void layernorm_cl_bwd_final_kernel(const float *__restrict__ partial, float *__restrict__ dgamma,
+                                              float *__restrict__ dbeta, int ctas, int C) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= 2 * C) return;
+    float s = 0.f;
+    for (int b = 0; b < ctas; b++) s += partial[(size_t)b * 2 * C + e];
+    if (e < C) dgamma[e] = s; else dbeta[e - C] = s;
+}
+
 }  // namespace o1d

@@ -204,6 +204,60 @@ def layer_norm_cl(x, weight, bias, eps: float = 1e-6, gelu: bool = False):
     return y
 
 
+def layer_norm_cl_supported(x, gelu: bool = False, backward: bool = False) -> bool:
+    """Can layer_norm_cl (and, with backward=True, layer_norm_cl_bwd) take this tensor?"""
+    if not (x.is_cuda and x.dtype in (torch.float32, torch.bfloat16)):
+        return False
+    C, ve = x.shape[-1], (4 if x.dtype == torch.float32 else 8)
+    if backward:
+        return not gelu and C % ve == 0 and C // ve <= 128
+    return C % ve == 0 and C <= 1024
+
+
+def layer_norm_cl_bwd(x, dy, weight, eps: float = 1e-6):
+    """Gradients of layer_norm_cl (no GELU): dx in x's dtype, dweight and dbias in fp32.  The
+    statistics are recomputed from x; dweight / dbias are summed in a fixed order."""
+    _need_cuda(x, dy, weight)
+    x, dy = x.contiguous(), dy.contiguous()
+    if dy.shape != x.shape or dy.dtype != x.dtype:
+        raise ValueError(f"dy {tuple(dy.shape)} {dy.dtype} does not match x {tuple(x.shape)} {x.dtype}")
+    C = x.shape[-1]
+    if weight.numel() != C:
+        raise ValueError(f"weight has {weight.numel()} elements, expected {C}")
+    rows = x.numel() // C
+    dx = torch.empty_like(x)
+    g32 = weight.detach().to(torch.float32).contiguous()
+    dg = torch.empty((C,), dtype=torch.float32, device=x.device)
+    db = torch.empty((C,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        nbytes = lib.o1d_layernorm_cl_bwd_workspace_bytes(rows, C)
+        ws = torch.empty((max(nbytes, 4),), dtype=torch.uint8, device=x.device)
+        check(lib.o1d_layernorm_cl_bwd(x.data_ptr(), dy.data_ptr(), g32.data_ptr(), dx.data_ptr(), dg.data_ptr(),
+                                       db.data_ptr(), ws.data_ptr(), nbytes, rows, C, float(eps), _dtype_code(x),
+                                       _stream()), "o1d_layernorm_cl_bwd")
+    return dx, dg, db
+
+
+class LayerNormCL(torch.autograd.Function):
+    """Channels-last LayerNorm with this library's kernels on both passes (F.layer_norm and its
+    autograd backward in the reference, models/convnext.py:28-56)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        x = x.contiguous()
+        ctx.save_for_backward(x, weight)
+        ctx.eps = eps
+        ctx.bias_dtype = bias.dtype
+        return layer_norm_cl(x, weight, bias, eps, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dx, dg, db = layer_norm_cl_bwd(x, dy, weight, ctx.eps)
+        return (dx if ctx.needs_input_grad[0] else None, dg.to(weight.dtype) if ctx.needs_input_grad[1] else None,
+                db.to(ctx.bias_dtype) if ctx.needs_input_grad[2] else None, None)
+
+
 def pointwise_in(x, weight, bias):
     """Channels-last ``Linear`` over the few channels of an NCHW image: x [N,Cin,H,W] (Cin <= 4),
     weight [Cout,Cin], bias [Cout] or None -> [N,H,W,Cout] (models/convnext.py:143,170-176 in one

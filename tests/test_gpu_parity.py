@@ -691,6 +691,34 @@ def test_layernorm_channels_last(C, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("C,rows", [(64, (3, 5, 7)), (96, (2, 56, 56)), (128, (1, 9, 11)), (384, (4, 14, 14)),
+                                    (512, (2, 7, 7)), (768, (5, 7, 7)), (1024, (3, 7, 5))])
+def test_layernorm_channels_last_backward(C, rows, dtype):
+    """o1d_layernorm_cl_bwd (through the autograd function the caller model uses) against float64
+    autograd of F.layer_norm on the same inputs: dx, dweight, dbias; the sums are reproducible."""
+    if dtype == torch.float32 and C > 512:
+        pytest.skip("fp32 rows of more than 512 channels stay on the library LayerNorm")
+    g = torch.Generator(device="cpu").manual_seed(C + rows[0])
+    x = (1.5 * torch.randn(rows + (C,), generator=g) + 0.25).to(DEV).to(dtype)
+    dy = torch.randn(rows + (C,), generator=g).to(DEV).to(dtype)
+    w = (1.0 + 0.5 * torch.randn((C,), generator=g)).to(DEV).requires_grad_(True)
+    b = torch.randn((C,), generator=g).to(DEV).requires_grad_(True)
+    xg = x.clone().requires_grad_(True)
+    y = o1d.ops.LayerNormCL.apply(xg, w, b, 1e-6)
+    y.backward(dy)
+    xr = x.double().requires_grad_(True)
+    wr, br = w.detach().double().requires_grad_(True), b.detach().double().requires_grad_(True)
+    torch.nn.functional.layer_norm(xr, (C,), wr, br, 1e-6).backward(dy.double())
+    rel = lambda a, r: float((a.double() - r).abs().max() / r.abs().max())
+    tol = 2e-5 if dtype == torch.float32 else 2 ** -7            # bf16: one rounding of dx
+    assert rel(xg.grad, xr.grad) <= tol
+    assert rel(w.grad, wr.grad) <= 1e-4 and rel(b.grad, br.grad) <= 1e-4
+    dx2, dg2, db2 = o1d.ops.layer_norm_cl_bwd(x, dy, w.detach(), 1e-6)
+    assert torch.equal(dx2, xg.grad) and torch.equal(dg2, w.grad) and torch.equal(db2, b.grad)
+    assert o1d.ops.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 @pytest.mark.parametrize("cin,cout", [(3, 64), (1, 8), (4, 96)])
 def test_pointwise_in(dtype, cin, cout):
     """Stem input projection (NCHW image -> channels-last, Linear over the input channels)
