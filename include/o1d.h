@@ -205,16 +205,17 @@ int o1d_wgrad_static(const void *dy, const void *x,
 int o1d_layernorm_cl(const void *x, const float *gamma, const float *beta, void *y,
                      long long rows, int C, float eps, int dtype, int gelu, void *stream);
 
-/* Backward of o1d_layernorm_cl without GELU (what autograd derives from F.layer_norm in the
- * reference's training step, models/convnext.py:28-56): dx [rows, C] in the element type,
- * dgamma, dbeta [C] fp32.  The row statistics are recomputed from x, so the forward pass keeps
- * nothing but x.  dgamma / dbeta are summed from per-CTA partials in a fixed order (bit-
+/* Backward of o1d_layernorm_cl (what autograd derives from F.layer_norm, and F.gelu after it when
+ * gelu != 0, in the reference's training step, models/convnext.py:28-56,183-189): dx [rows, C] in
+ * the element type, dgamma, dbeta [C] fp32.  dy is the gradient of the forward call's output.  The
+ * row statistics are recomputed from x, so the forward pass keeps nothing but x.  beta is read only
+ * when gelu != 0.  dgamma / dbeta are summed from per-CTA partials in a fixed order (bit-
  * reproducible).  C a multiple of 4 (fp32) / 8 (bf16), at most 512 (fp32) / 1024 (bf16).
  * workspace: o1d_layernorm_cl_bwd_workspace_bytes(rows, C) bytes, no initialisation needed. */
 size_t o1d_layernorm_cl_bwd_workspace_bytes(long long rows, int C);
-int o1d_layernorm_cl_bwd(const void *x, const void *dy, const float *gamma, void *dx, float *dgamma,
-                         float *dbeta, void *workspace, size_t workspace_bytes, long long rows, int C,
-                         float eps, int dtype, void *stream);
+int o1d_layernorm_cl_bwd(const void *x, const void *dy, const float *gamma, const float *beta, void *dx,
+                         float *dgamma, float *dbeta, void *workspace, size_t workspace_bytes,
+                         long long rows, int C, float eps, int dtype, int gelu, void *stream);
 
 /* Stem input projection: y[n,hw,o] = bias[o] + sum_c w[o,c] * x[n,c,hw], x an NCHW image
  * tensor with Cin <= 4 channels, y channels-last with Cout (a multiple of 8) channels: the

@@ -71,7 +71,7 @@ class LayerNorm(nn.Module):
         if fast:      # inference: one pass over the tensor (see csrc/o1d_layernorm.cuh)
             return ops.layer_norm_cl(x, self.weight, self.bias, self.eps, gelu)
         if torch.is_grad_enabled() and ops.layer_norm_cl_supported(x, gelu, backward=True):
-            return ops.LayerNormCL.apply(x, self.weight, self.bias, self.eps)       # training: both passes here
+            return ops.LayerNormCL.apply(x, self.weight, self.bias, self.eps, gelu)   # training: both passes here
         y = F.layer_norm(x, self.normalized_shape, self.weight, self.bias, self.eps)
         return F.gelu(y) if gelu else y
 

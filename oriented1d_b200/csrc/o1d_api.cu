@@ -908,27 +908,37 @@ inline int ln_bwd_grid(int64_t rows, int G, int sms) {
     return (int)(groups < cap ? (groups > 0 ? groups : 1) : cap);
 }
 template <typename T, int G, int VPL>
-int launch_ln_bwd(const void *x, const void *dy, const float *gamma, void *dx, float *dgamma, float *dbeta,
-                  float *partial, int64_t rows, int C, float eps, cudaStream_t st, const DeviceInfo &d) {
+int launch_ln_bwd(const void *x, const void *dy, const float *gamma, const float *beta, void *dx, float *dgamma,
+                  float *dbeta, float *partial, int64_t rows, int C, float eps, int gelu, cudaStream_t st,
+                  const DeviceInfo &d) {
     const int grid = ln_bwd_grid(rows, G, d.sms);
     const int smem = (kLnThreads / 32) * 2 * C * (int)sizeof(float);
-    auto kern = layernorm_cl_bwd_kernel<T, G, VPL>;
-    if (smem > 48 * 1024) O1D_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<grid, kLnThreads, smem, st>>>((const T *)x, (const T *)dy, gamma, (T *)dx, partial, rows, C, eps);
+    if (gelu) {
+        auto kern = layernorm_cl_bwd_kernel<T, G, VPL, true>;
+        if (smem > 48 * 1024) O1D_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kern<<<grid, kLnThreads, smem, st>>>((const T *)x, (const T *)dy, gamma, beta, (T *)dx, partial, rows, C, eps);
+    } else {
+        auto kern = layernorm_cl_bwd_kernel<T, G, VPL, false>;
+        if (smem > 48 * 1024) O1D_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kern<<<grid, kLnThreads, smem, st>>>((const T *)x, (const T *)dy, gamma, beta, (T *)dx, partial, rows, C, eps);
+    }
     O1D_CUDA(cudaGetLastError());
-    layernorm_cl_bwd_final_kernel<<<ceil_div(2 * C, 256), 256, 0, st>>>(partial, dgamma, dbeta, grid, C);
+    layernorm_cl_bwd_final_kernel<<<ceil_div(2 * C, 32), dim3(32, 8), 0, st>>>(partial, dgamma, dbeta, grid, C);
     O1D_CUDA(cudaGetLastError());
     return O1D_OK;
 }
 template <typename T>
-int dispatch_ln_bwd(const void *x, const void *dy, const float *gamma, void *dx, float *dgamma, float *dbeta,
-                    float *partial, int64_t rows, int C, float eps, cudaStream_t st, const DeviceInfo &d) {
+int dispatch_ln_bwd(const void *x, const void *dy, const float *gamma, const float *beta, void *dx, float *dgamma,
+                    float *dbeta, float *partial, int64_t rows, int C, float eps, int gelu, cudaStream_t st,
+                    const DeviceInfo &d) {
     const int nvec = C / (16 / (int)sizeof(T));
-    if (nvec <= 8) return launch_ln_bwd<T, 8, 1>(x, dy, gamma, dx, dgamma, dbeta, partial, rows, C, eps, st, d);
-    if (nvec <= 16) return launch_ln_bwd<T, 8, 2>(x, dy, gamma, dx, dgamma, dbeta, partial, rows, C, eps, st, d);
-    if (nvec <= 32) return launch_ln_bwd<T, 16, 2>(x, dy, gamma, dx, dgamma, dbeta, partial, rows, C, eps, st, d);
-    if (nvec <= 64) return launch_ln_bwd<T, 32, 2>(x, dy, gamma, dx, dgamma, dbeta, partial, rows, C, eps, st, d);
-    if (nvec <= 128) return launch_ln_bwd<T, 32, 4>(x, dy, gamma, dx, dgamma, dbeta, partial, rows, C, eps, st, d);
+#define O1D_LNB(G, V) launch_ln_bwd<T, G, V>(x, dy, gamma, beta, dx, dgamma, dbeta, partial, rows, C, eps, gelu, st, d)
+    if (nvec <= 8) return O1D_LNB(8, 1);
+    if (nvec <= 16) return O1D_LNB(8, 2);
+    if (nvec <= 32) return O1D_LNB(16, 2);
+    if (nvec <= 64) return O1D_LNB(32, 2);
+    if (nvec <= 128) return O1D_LNB(32, 4);
+#undef O1D_LNB
     return O1D_ERR_UNSUPPORTED;
 }
 template <typename T>
@@ -969,10 +979,10 @@ size_t o1d_layernorm_cl_bwd_workspace_bytes(long long rows, int C) {
     return (size_t)d.sms * 4 * 2 * (size_t)C * sizeof(float);       // one partial per CTA of the largest grid
 }
 
-int o1d_layernorm_cl_bwd(const void *x, const void *dy, const float *gamma, void *dx, float *dgamma, float *dbeta,
-                         void *workspace, size_t workspace_bytes, long long rows, int C, float eps, int dtype,
-                         void *stream) {
-    if (!x || !dy || !gamma || !dx || !dgamma || !dbeta || rows <= 0 || C <= 0 ||
+int o1d_layernorm_cl_bwd(const void *x, const void *dy, const float *gamma, const float *beta, void *dx, float *dgamma,
+                         float *dbeta, void *workspace, size_t workspace_bytes, long long rows, int C, float eps,
+                         int dtype, int gelu, void *stream) {
+    if (!x || !dy || !gamma || !dx || !dgamma || !dbeta || (gelu && !beta) || rows <= 0 || C <= 0 ||
         (dtype != O1D_F32 && dtype != O1D_BF16))
         return O1D_ERR_INVALID;
     const int ve = dtype == O1D_F32 ? 4 : 8;
@@ -983,9 +993,10 @@ int o1d_layernorm_cl_bwd(const void *x, const void *dy, const float *gamma, void
     int rc = device_info(&d);
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    return dtype == O1D_F32
-               ? dispatch_ln_bwd<float>(x, dy, gamma, dx, dgamma, dbeta, (float *)workspace, rows, C, eps, st, d)
-               : dispatch_ln_bwd<__nv_bfloat16>(x, dy, gamma, dx, dgamma, dbeta, (float *)workspace, rows, C, eps, st, d);
+    return dtype == O1D_F32 ? dispatch_ln_bwd<float>(x, dy, gamma, beta, dx, dgamma, dbeta, (float *)workspace, rows, C,
+                                                     eps, gelu, st, d)
+                            : dispatch_ln_bwd<__nv_bfloat16>(x, dy, gamma, beta, dx, dgamma, dbeta, (float *)workspace,
+                                                             rows, C, eps, gelu, st, d);
 }
 
 int o1d_pointwise_in(const void *x, const float *w, const float *bias, void *y, int N, int Cin, long long HW,

@@ -95,23 +95,27 @@ layernorm_cl_kernel(const T *__restrict__ x, const float *__restrict__ gamma, co
 //   dx = rstd * (g - mean_C(g) - xhat * mean_C(g * xhat)),  dgamma = sum_rows dy * xhat,  dbeta = sum_rows dy.
 // F.layer_norm's backward in the reference's training step (models/convnext.py:28-56 through autograd).
 // partial: [gridDim.x][2][C] floats.  Dynamic shared memory: (kLnThreads / 32) * 2 * C floats.
-template <typename T, int G, int VPL>
+// GELU: the forward pass was LayerNorm followed by exact GELU (the stems); dy is then the gradient of the
+// GELU output and is first multiplied by GELU'(xhat * gamma + beta).
+template <typename T, int G, int VPL, bool GELU>
 __global__ void __launch_bounds__(kLnThreads)
 layernorm_cl_bwd_kernel(const T *__restrict__ x, const T *__restrict__ dy, const float *__restrict__ gamma,
-                        T *__restrict__ dx, float *__restrict__ partial, int64_t rows, int C, float eps) {
+                        const float *__restrict__ beta, T *__restrict__ dx, float *__restrict__ partial, int64_t rows,
+                        int C, float eps) {
     extern __shared__ float ln_red[];                 // [warps][2][C]
     constexpr int VE = GVec<T>::N;
     const int lane_in_group = threadIdx.x % G;
     const int64_t group = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
     const int64_t ngroups = ((int64_t)gridDim.x * blockDim.x) / G;
     const int nvec = C / VE;
-    float g[VPL][VE], sg[VPL][VE], sb[VPL][VE];
+    float g[VPL][VE], bt[GELU ? VPL : 1][VE], sg[VPL][VE], sb[VPL][VE];
 #pragma unroll
     for (int v = 0; v < VPL; v++) {
         const int vi = lane_in_group + v * G;
 #pragma unroll
         for (int j = 0; j < VE; j++) {
             g[v][j] = (vi < nvec) ? __ldg(gamma + vi * VE + j) : 0.f;
+            if (GELU) bt[GELU ? v : 0][j] = (vi < nvec) ? __ldg(beta + vi * VE + j) : 0.f;
             sg[v][j] = 0.f; sb[v][j] = 0.f;
         }
     }
@@ -163,6 +167,7 @@ layernorm_cl_bwd_kernel(const T *__restrict__ x, const T *__restrict__ dy, const
                 for (int j = 0; j < VE; j++) {
                     const float xh = (f[v][j] - mean) * rstd;
                     f[v][j] = xh;                                 // keep xhat
+                    if (GELU) d[v][j] *= gelu_exact_grad(xh * g[v][j] + bt[GELU ? v : 0][j]);
                     const float gg = d[v][j] * g[v][j];
                     c1 += gg; c2 += gg * xh;
                     sg[v][j] += d[v][j] * xh; sb[v][j] += d[v][j];
@@ -221,14 +226,24 @@ layernorm_cl_bwd_kernel(const T *__restrict__ x, const T *__restrict__ dy, const
     }
 }
 
-// dgamma[c] = sum over CTAs (in order) of partial[cta][0][c], dbeta likewise from partial[cta][1][c].
+// dgamma[c] = sum over CTAs of partial[cta][0][c], dbeta likewise from partial[cta][1][c].  Block (32, 8):
+// thread (x, y) adds the CTAs congruent to y modulo 8 for one column, the eight sums are then added in
+// order of y: a fixed order, with an eighth of the dependent loads per thread.
 __global__ void layernorm_cl_bwd_final_kernel(const float *__restrict__ partial, float *__restrict__ dgamma,
                                               float *__restrict__ dbeta, int ctas, int C) {
-    const int e = blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= 2 * C) return;
+    __shared__ float part[8][33];
+    const int e = blockIdx.x * 32 + threadIdx.x;
     float s = 0.f;
-    for (int b = 0; b < ctas; b++) s += partial[(size_t)b * 2 * C + e];
-    if (e < C) dgamma[e] = s; else dbeta[e - C] = s;
+    if (e < 2 * C)
+        for (int b = threadIdx.y; b < ctas; b += 8) s += partial[(size_t)b * 2 * C + e];
+    part[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && e < 2 * C) {
+        float t = 0.f;
+#pragma unroll
+        for (int y = 0; y < 8; y++) t += part[y][threadIdx.x];
+        if (e < C) dgamma[e] = t; else dbeta[e - C] = t;
+    }
 }
 
 }  // namespace o1d

@@ -210,13 +210,14 @@ def layer_norm_cl_supported(x, gelu: bool = False, backward: bool = False) -> bo
         return False
     C, ve = x.shape[-1], (4 if x.dtype == torch.float32 else 8)
     if backward:
-        return not gelu and C % ve == 0 and C // ve <= 128
+        return C % ve == 0 and C // ve <= 128
     return C % ve == 0 and C <= 1024
 
 
-def layer_norm_cl_bwd(x, dy, weight, eps: float = 1e-6):
-    """Gradients of layer_norm_cl (no GELU): dx in x's dtype, dweight and dbias in fp32.  The
-    statistics are recomputed from x; dweight / dbias are summed in a fixed order."""
+def layer_norm_cl_bwd(x, dy, weight, eps: float = 1e-6, bias=None, gelu: bool = False):
+    """Gradients of layer_norm_cl: dx in x's dtype, dweight and dbias in fp32.  With gelu=True the
+    forward call ended in exact GELU and `bias` is needed again.  The statistics are recomputed
+    from x; dweight / dbias are summed in a fixed order."""
     _need_cuda(x, dy, weight)
     x, dy = x.contiguous(), dy.contiguous()
     if dy.shape != x.shape or dy.dtype != x.dtype:
@@ -227,14 +228,17 @@ def layer_norm_cl_bwd(x, dy, weight, eps: float = 1e-6):
     rows = x.numel() // C
     dx = torch.empty_like(x)
     g32 = weight.detach().to(torch.float32).contiguous()
+    if gelu and (bias is None or bias.numel() != C):
+        raise ValueError("gelu=True needs the forward call's bias")
+    b32 = bias.detach().to(torch.float32).contiguous() if gelu else None
     dg = torch.empty((C,), dtype=torch.float32, device=x.device)
     db = torch.empty((C,), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         nbytes = lib.o1d_layernorm_cl_bwd_workspace_bytes(rows, C)
         ws = torch.empty((max(nbytes, 4),), dtype=torch.uint8, device=x.device)
-        check(lib.o1d_layernorm_cl_bwd(x.data_ptr(), dy.data_ptr(), g32.data_ptr(), dx.data_ptr(), dg.data_ptr(),
-                                       db.data_ptr(), ws.data_ptr(), nbytes, rows, C, float(eps), _dtype_code(x),
-                                       _stream()), "o1d_layernorm_cl_bwd")
+        check(lib.o1d_layernorm_cl_bwd(x.data_ptr(), dy.data_ptr(), g32.data_ptr(), b32.data_ptr() if gelu else None,
+                                       dx.data_ptr(), dg.data_ptr(), db.data_ptr(), ws.data_ptr(), nbytes, rows, C,
+                                       float(eps), _dtype_code(x), int(gelu), _stream()), "o1d_layernorm_cl_bwd")
     return dx, dg, db
 
 
@@ -243,19 +247,18 @@ class LayerNormCL(torch.autograd.Function):
     autograd backward in the reference, models/convnext.py:28-56)."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, eps):
+    def forward(ctx, x, weight, bias, eps, gelu=False):
         x = x.contiguous()
-        ctx.save_for_backward(x, weight)
-        ctx.eps = eps
-        ctx.bias_dtype = bias.dtype
-        return layer_norm_cl(x, weight, bias, eps, False)
+        ctx.save_for_backward(x, weight, bias)
+        ctx.eps, ctx.gelu = eps, bool(gelu)
+        return layer_norm_cl(x, weight, bias, eps, gelu)
 
     @staticmethod
     def backward(ctx, dy):
-        x, weight = ctx.saved_tensors
-        dx, dg, db = layer_norm_cl_bwd(x, dy, weight, ctx.eps)
+        x, weight, bias = ctx.saved_tensors
+        dx, dg, db = layer_norm_cl_bwd(x, dy, weight, ctx.eps, bias, ctx.gelu)
         return (dx if ctx.needs_input_grad[0] else None, dg.to(weight.dtype) if ctx.needs_input_grad[1] else None,
-                db.to(ctx.bias_dtype) if ctx.needs_input_grad[2] else None, None)
+                db.to(bias.dtype) if ctx.needs_input_grad[2] else None, None, None)
 
 
 def pointwise_in(x, weight, bias):

@@ -703,18 +703,21 @@ def test_layernorm_channels_last_backward(C, rows, dtype):
     dy = torch.randn(rows + (C,), generator=g).to(DEV).to(dtype)
     w = (1.0 + 0.5 * torch.randn((C,), generator=g)).to(DEV).requires_grad_(True)
     b = torch.randn((C,), generator=g).to(DEV).requires_grad_(True)
-    xg = x.clone().requires_grad_(True)
-    y = o1d.ops.LayerNormCL.apply(xg, w, b, 1e-6)
-    y.backward(dy)
-    xr = x.double().requires_grad_(True)
-    wr, br = w.detach().double().requires_grad_(True), b.detach().double().requires_grad_(True)
-    torch.nn.functional.layer_norm(xr, (C,), wr, br, 1e-6).backward(dy.double())
     rel = lambda a, r: float((a.double() - r).abs().max() / r.abs().max())
     tol = 2e-5 if dtype == torch.float32 else 2 ** -7            # bf16: one rounding of dx
-    assert rel(xg.grad, xr.grad) <= tol
-    assert rel(w.grad, wr.grad) <= 1e-4 and rel(b.grad, br.grad) <= 1e-4
-    dx2, dg2, db2 = o1d.ops.layer_norm_cl_bwd(x, dy, w.detach(), 1e-6)
-    assert torch.equal(dx2, xg.grad) and torch.equal(dg2, w.grad) and torch.equal(db2, b.grad)
+    for gelu in (False, True):                                   # True: the stems' LayerNorm -> GELU
+        xg = x.clone().requires_grad_(True)
+        w.grad = b.grad = None
+        y = o1d.ops.LayerNormCL.apply(xg, w, b, 1e-6, gelu)
+        y.backward(dy)
+        xr = x.double().requires_grad_(True)
+        wr, br = w.detach().double().requires_grad_(True), b.detach().double().requires_grad_(True)
+        ref = torch.nn.functional.layer_norm(xr, (C,), wr, br, 1e-6)
+        (torch.nn.functional.gelu(ref) if gelu else ref).backward(dy.double())
+        assert rel(xg.grad, xr.grad) <= tol
+        assert rel(w.grad, wr.grad) <= 1e-4 and rel(b.grad, br.grad) <= 1e-4
+        dx2, dg2, db2 = o1d.ops.layer_norm_cl_bwd(x, dy, w.detach(), 1e-6, b.detach(), gelu)
+        assert torch.equal(dx2, xg.grad) and torch.equal(dg2, w.grad) and torch.equal(db2, b.grad)
     assert o1d.ops.device_status() == 0
 
 
