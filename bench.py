@@ -826,7 +826,7 @@ def run_train(args):
     model = convnext1d.convnext_base(variant="1dpp", drop_path_rate=0.0, fuse_gelu="auto" if args.fuse_gelu else False)
     model = model.to(dev).bfloat16().train()
     flat, params = flat_gradient_buffer(model)
-    opt = torch.optim.AdamW(params, lr=1e-4, weight_decay=0.05, fused=True)
+    opt = torch.optim.AdamW(params, lr=1e-4, weight_decay=0.05, fused=True, capturable=True)
     nsets = 2
     imgs = [torch.randn((batch, 3, 224, 224), device=dev).bfloat16() for _ in range(nsets)]
     labels = [torch.randint(0, 1000, (batch,), device=dev) for _ in range(nsets)]
@@ -845,14 +845,48 @@ def run_train(args):
         opt.step()
         return loss
 
+    # One process, one GPU: the whole step (forward, backward, optimizer) is captured into a CUDA graph
+    # after three eager steps and replayed on static input buffers, which takes the ~4000 kernel
+    # launches per step off the host.  With several ranks the step stays eager (the all-reduce sits in it).
+    static_x, static_t = torch.empty_like(imgs[0]), torch.empty_like(labels[0])
+    graph, static_loss, launch = None, None, "eager"
+    if world == 1 and not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for i in range(3):
+                    static_x.copy_(imgs[i % nsets]); static_t.copy_(labels[i % nsets])
+                    train_step(static_x, static_t)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_loss = train_step(static_x, static_t)
+            launch = "CUDA graph of the whole step"
+        except Exception as e:                      # noqa: BLE001 - any capture failure: run eagerly
+            print(f"[bench] step not captured ({type(e).__name__}: {e}); running eagerly", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+
+    def run_step(x, t):
+        if graph is None:
+            return train_step(x, t)
+        static_x.copy_(x, non_blocking=True); static_t.copy_(t, non_blocking=True)
+        graph.replay()
+        return static_loss
+
     def step():
         state["i"] = (state["i"] + 1) % nsets
-        train_step(imgs[state["i"]], labels[state["i"]])
+        run_step(imgs[state["i"]], labels[state["i"]])
 
     def e2e_step():
-        x = host_img.to(dev, non_blocking=True)
-        t = host_lab.to(dev, non_blocking=True)
-        host_loss.copy_(train_step(x, t).detach(), non_blocking=True)
+        if graph is None:
+            x = host_img.to(dev, non_blocking=True)
+            t = host_lab.to(dev, non_blocking=True)
+            host_loss.copy_(train_step(x, t).detach(), non_blocking=True)
+        else:
+            host_loss.copy_(run_step(host_img, host_lab).detach(), non_blocking=True)
 
     with ClockSampler(local) as clk:
         ms = timed_steps(step, args.steps, max(args.warmup, 3), world, dev)
@@ -868,7 +902,7 @@ def run_train(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "ConvNeXt-B-1D++ training step: depths 3/3/27/3, dims 128-1024, K=(15,31), "
                                    f"batch {batch} per GPU, 224x224x3 bf16, cross-entropy, AdamW (fused), random init",
-                       "l2": "activations exceed L2; 2 input batches rotate", "launch": "eager",
+                       "l2": "activations exceed L2; 2 input batches rotate", "launch": launch,
                        "gelu": "inside the second conv's kernels on 56x56 and 28x28 maps" if args.fuse_gelu else "separate pass",
                        "parallelism": f"dp{world}: one NCCL all-reduce of the flat gradient buffer "
                                       f"({flat.numel() * flat.element_size() / 1e6:.0f} MB) per step",
@@ -911,12 +945,41 @@ def run_dense(args):
             dist.all_reduce(flat)
         return loss
 
+    # one GPU: forward + backward captured into a CUDA graph after three eager passes (see run_train)
+    static_x = torch.empty_like(imgs[0])
+    graph, static_loss, launch = None, None, "eager"
+    if world == 1 and not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for i in range(3):
+                    static_x.copy_(imgs[i % nsets])
+                    fwd_bwd(static_x)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_loss = fwd_bwd(static_x)
+            launch = "CUDA graph of forward + backward"
+        except Exception as e:                      # noqa: BLE001 - any capture failure: run eagerly
+            print(f"[bench] pass not captured ({type(e).__name__}: {e}); running eagerly", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+
+    def run_pass(x):
+        if graph is None:
+            return fwd_bwd(x if x.is_cuda else x.to(dev, non_blocking=True))
+        static_x.copy_(x, non_blocking=True)
+        graph.replay()
+        return static_loss
+
     def step():
         state["i"] = (state["i"] + 1) % nsets
-        fwd_bwd(imgs[state["i"]])
+        run_pass(imgs[state["i"]])
 
     def e2e_step():
-        host_loss.copy_(fwd_bwd(host_img.to(dev, non_blocking=True)).detach(), non_blocking=True)
+        host_loss.copy_(run_pass(host_img).detach(), non_blocking=True)
 
     with ClockSampler(local) as clk:
         ms = timed_steps(step, args.steps, max(args.warmup, 3), world, dev)
@@ -932,7 +995,7 @@ def run_dense(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"ConvNeXt-T-1D backbone, kernels 31/31/27/13, batch {batch} per GPU, 800x1280x3 bf16, "
                                    "forward + backward, loss = sum of the four stage outputs, random init",
-                       "l2": "activations exceed L2", "launch": "eager",
+                       "l2": "activations exceed L2", "launch": launch,
                        "parallelism": f"dp{world}: flat gradient all-reduce"},
             "e2e": {"value": batch * world * n_e2e / (e2e_ms / 1e3), "unit": "img/s",
                     "h2d_bytes_per_step": host_img.numel() * 2, "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / n_e2e},

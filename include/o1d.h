@@ -217,6 +217,14 @@ int o1d_layernorm_cl_bwd(const void *x, const void *dy, const float *gamma, cons
                          float *dgamma, float *dbeta, void *workspace, size_t workspace_bytes,
                          long long rows, int C, float eps, int dtype, int gelu, void *stream);
 
+/* Column sums of a channels-last matrix, out[c] = sum_r x[r, c] in fp32: the bias gradient that
+ * autograd forms for the Linear layers on either side of the convolution in a block
+ * (models/convnext.py:298-300,310,312).  x [rows, C] fp32 or bf16, C a multiple of 4 / 8; summed in
+ * a fixed order.  workspace: o1d_colsum_workspace_bytes(rows, C, dtype) bytes, uninitialised. */
+size_t o1d_colsum_workspace_bytes(long long rows, int C, int dtype);
+int o1d_colsum(const void *x, float *out, void *workspace, size_t workspace_bytes, long long rows, int C,
+               int dtype, void *stream);
+
 /* Stem input projection: y[n,hw,o] = bias[o] + sum_c w[o,c] * x[n,c,hw], x an NCHW image
  * tensor with Cin <= 4 channels, y channels-last with Cout (a multiple of 8) channels: the
  * `x.permute(0,2,3,1)` + `nn.Linear(in_chans, 64)` that opens the reference's 1D stem

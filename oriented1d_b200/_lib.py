@@ -43,6 +43,8 @@ SIGNATURES = {
     "o1d_layernorm_cl_bwd_workspace_bytes": (_c_size_t, [ctypes.c_longlong, _c_int]),
     "o1d_layernorm_cl_bwd": (_c_int, [_c_void_p] * 8 + [_c_size_t, ctypes.c_longlong, _c_int, ctypes.c_float, _c_int,
                                                       _c_int, _c_void_p]),
+    "o1d_colsum_workspace_bytes": (_c_size_t, [ctypes.c_longlong, _c_int, _c_int]),
+    "o1d_colsum": (_c_int, [_c_void_p] * 3 + [_c_size_t, ctypes.c_longlong, _c_int, _c_int, _c_void_p]),
     "o1d_pointwise_in": (_c_int, [_c_void_p] * 4 + [_c_int, _c_int, ctypes.c_longlong, _c_int, _c_int, _c_void_p]),
     "o1d_transpose": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p]),
 }

@@ -104,7 +104,7 @@ class Stem1D(nn.Module):
             x = self.pw1(x)
         x = self.norm1(self.dw1(x), gelu=True)
         x = self.norm2(self.dw2(x), gelu=True)
-        return self.norm3(self.pw2(x))
+        return self.norm3(ops.linear_cl(self.pw2, x))
 
 
 class Block1D(nn.Module):
@@ -124,11 +124,11 @@ class Block1D(nn.Module):
                                          N=N, layer_offset=layer_offset, arbitrary_size=arbitrary_size)
 
     def _mlp_in(self, x, gelu=True):
-        h = self.pwconv1(self.norm(x))
+        h = ops.linear_cl(self.pwconv1, self.norm(x))
         return F.gelu(h) if gelu else h
 
     def forward(self, x):
-        y = self.pwconv2(self._mlp_in(self.dwconv(x)))
+        y = ops.linear_cl(self.pwconv2, self._mlp_in(self.dwconv(x)))
         return self._residual(x, y)
 
     def _residual(self, x, y):
@@ -154,7 +154,7 @@ class Block1DPP(Block1D):
 
     def forward(self, x):
         fused = getattr(self.dwconv2, "gelu_input", False)      # the GELU then runs inside dwconv2's kernels
-        y = self.pwconv2(self.dwconv2(self._mlp_in(self.dwconv1(x), gelu=not fused)))
+        y = ops.linear_cl(self.pwconv2, self.dwconv2(self._mlp_in(self.dwconv1(x), gelu=not fused)))
         return self._residual(x, y)
 
 
@@ -176,7 +176,7 @@ class Block2D(Block1D):
         return conv(x.permute(0, 3, 1, 2)).permute(0, 2, 3, 1)
 
     def forward(self, x):
-        y = self.pwconv2(self._mlp_in(self._dw2d(self.dwconv, x)))
+        y = ops.linear_cl(self.pwconv2, self._mlp_in(self._dw2d(self.dwconv, x)))
         return self._residual(x, y)
 
 
@@ -197,7 +197,7 @@ class Block2DPP(Block2D):
     def forward(self, x):
         fused = getattr(self.dwconv2, "gelu_input", False)
         y = self._mlp_in(self._dw2d(self.dwconv1, x), gelu=not fused).contiguous()
-        return self._residual(x, self.pwconv2(self.dwconv2(y)))
+        return self._residual(x, ops.linear_cl(self.pwconv2, self.dwconv2(y)))
 
 
 class Stem2D(nn.Sequential):

@@ -999,6 +999,46 @@ int o1d_layernorm_cl_bwd(const void *x, const void *dy, const float *gamma, cons
                                                              rows, C, eps, gelu, st, d);
 }
 
+namespace {
+int colsum_slices(long long rows, int C, int ve, int sms) {
+    const int col_blocks = ceil_div(C / ve, kColsumThreads);
+    long long s = ((long long)sms * 2 + col_blocks - 1) / col_blocks;      // about two CTAs per SM in all
+    if (s > (rows + 7) / 8) s = (rows + 7) / 8;                            // at least eight rows per slice
+    if (s > 4096) s = 4096;
+    return (int)(s < 1 ? 1 : s);
+}
+}  // namespace
+
+size_t o1d_colsum_workspace_bytes(long long rows, int C, int dtype) {
+    if (rows <= 0 || C <= 0) return 0;
+    DeviceInfo d;
+    if (device_info(&d)) return 0;
+    return (size_t)colsum_slices(rows, C, dtype == O1D_F32 ? 4 : 8, d.sms) * (size_t)C * sizeof(float);
+}
+
+int o1d_colsum(const void *x, float *out, void *workspace, size_t workspace_bytes, long long rows, int C, int dtype,
+               void *stream) {
+    if (!x || !out || rows <= 0 || C <= 0 || (dtype != O1D_F32 && dtype != O1D_BF16)) return O1D_ERR_INVALID;
+    const int ve = dtype == O1D_F32 ? 4 : 8;
+    if (C % ve != 0 || ((uintptr_t)x & 15)) return O1D_ERR_UNSUPPORTED;
+    DeviceInfo d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    const int slices = colsum_slices(rows, C, ve, d.sms);
+    if (!workspace || workspace_bytes < (size_t)slices * C * sizeof(float)) return O1D_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid(ceil_div(C / ve, kColsumThreads), slices);
+    if (dtype == O1D_F32)
+        colsum_partial_kernel<float><<<grid, kColsumThreads, 0, st>>>((const float *)x, (float *)workspace, rows, C);
+    else
+        colsum_partial_kernel<__nv_bfloat16><<<grid, kColsumThreads, 0, st>>>((const __nv_bfloat16 *)x,
+                                                                             (float *)workspace, rows, C);
+    O1D_CUDA(cudaGetLastError());
+    colsum_final_kernel<<<ceil_div(C, 32), dim3(32, 8), 0, st>>>((const float *)workspace, out, slices, C);
+    O1D_CUDA(cudaGetLastError());
+    return O1D_OK;
+}
+
 int o1d_pointwise_in(const void *x, const float *w, const float *bias, void *y, int N, int Cin, long long HW,
                      int Cout, int dtype, void *stream) {
     if (!x || !w || !y || N <= 0 || HW <= 0 || Cin <= 0 || Cout <= 0 || (dtype != O1D_F32 && dtype != O1D_BF16))

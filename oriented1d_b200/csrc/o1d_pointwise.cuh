@@ -8,6 +8,7 @@
 #pragma once
 
 #include "o1d_common.cuh"
+#include "o1d_generic.cuh"   // GVec
 
 namespace o1d {
 
@@ -62,6 +63,66 @@ pointwise_in_kernel(const T *__restrict__ x, const float *__restrict__ w, const 
             }
             *reinterpret_cast<uint4 *>(dst) = make_uint4(u[0], u[1], u[2], u[3]);
         }
+    }
+}
+
+
+// Column sums of a channels-last matrix: out[c] = sum over rows of x[r, c].  This is the bias gradient of
+// the Linear layers around the convolution in a block (models/convnext.py:298-300,310,312 through
+// autograd, which sums grad_output over its rows).  CTA (bx, by): columns [bx*256*VE, ...) as one 16-byte
+// vector per thread, rows by, by + gridDim.y, ...; fp32 partial per (by, column); a second kernel
+// (layernorm_cl_bwd_final_kernel's pattern, here colsum_final_kernel) adds the row slices in a fixed
+// order.  Every load is a full 16-byte vector of a contiguous 4 KB row segment.
+constexpr int kColsumThreads = 256;
+template <typename T>
+__global__ void __launch_bounds__(kColsumThreads)
+colsum_partial_kernel(const T *__restrict__ x, float *__restrict__ partial, int64_t rows, int C) {
+    constexpr int VE = 16 / (int)sizeof(T);
+    const int vec = blockIdx.x * kColsumThreads + threadIdx.x, nvec = C / VE;
+    if (vec >= nvec) return;
+    float acc[VE];
+#pragma unroll
+    for (int j = 0; j < VE; j++) acc[j] = 0.f;
+    const T *col = x + (size_t)vec * VE;
+    int64_t r = blockIdx.y;
+    // four rows in flight per thread
+    for (; r + 3 * (int64_t)gridDim.y < rows; r += 4 * (int64_t)gridDim.y) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) v[u] = __ldg(reinterpret_cast<const uint4 *>(col + (r + u * (int64_t)gridDim.y) * C));
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            float f[VE];
+            GVec<T>::unpack(v[u], f);
+#pragma unroll
+            for (int j = 0; j < VE; j++) acc[j] += f[j];
+        }
+    }
+    for (; r < rows; r += gridDim.y) {
+        float f[VE];
+        GVec<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(col + r * C)), f);
+#pragma unroll
+        for (int j = 0; j < VE; j++) acc[j] += f[j];
+    }
+    float *dst = partial + (size_t)blockIdx.y * C + (size_t)vec * VE;
+#pragma unroll
+    for (int j = 0; j < VE; j++) dst[j] = acc[j];
+}
+
+// out[c] = sum over slices (in a fixed order) of partial[slice][c].  Block (32, 8) as in the LayerNorm backward.
+__global__ void colsum_final_kernel(const float *__restrict__ partial, float *__restrict__ out, int slices, int C) {
+    __shared__ float part[8][33];
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    float s = 0.f;
+    if (c < C)
+        for (int b = threadIdx.y; b < slices; b += 8) s += partial[(size_t)b * C + c];
+    part[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < C) {
+        float t = 0.f;
+#pragma unroll
+        for (int y = 0; y < 8; y++) t += part[y][threadIdx.x];
+        out[c] = t;
     }
 }
 

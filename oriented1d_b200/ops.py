@@ -261,6 +261,57 @@ class LayerNormCL(torch.autograd.Function):
                 db.to(bias.dtype) if ctx.needs_input_grad[2] else None, None, None)
 
 
+def colsum(x):
+    """Sum over all but the last (contiguous) axis, in fp32 and in a fixed order: [..., C] -> [C]."""
+    _need_cuda(x)
+    x = x.contiguous()
+    C = x.shape[-1]
+    rows = x.numel() // C
+    out = torch.empty((C,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        code = _dtype_code(x)
+        nbytes = lib.o1d_colsum_workspace_bytes(rows, C, code)
+        ws = torch.empty((max(nbytes, 4),), dtype=torch.uint8, device=x.device)
+        check(lib.o1d_colsum(x.data_ptr(), out.data_ptr(), ws.data_ptr(), nbytes, rows, C, code, _stream()),
+              "o1d_colsum")
+    return out
+
+
+class LinearCL(torch.autograd.Function):
+    """F.linear on channels-last activations whose bias gradient is this library's column sum
+    (autograd's own is a generic reduction that runs at a fifth of the memory rate on these
+    shapes); the two matrix products stay with the GEMM library, as in nn.Linear."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        ctx.has_bias = bias is not None
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        return torch.nn.functional.linear(x, weight, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = (dy2 @ weight).reshape(x.shape)
+        if ctx.needs_input_grad[1]:
+            dw = dy2.t() @ x.reshape(-1, x.shape[-1])
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = colsum(dy2).to(ctx.bias_dtype)
+        return dx, dw, db
+
+
+def linear_cl(module, x):
+    """module(x) for an nn.Linear; on CUDA with gradients enabled the bias gradient runs here."""
+    C = module.out_features
+    if (x.is_cuda and torch.is_grad_enabled() and module.bias is not None and x.dtype == module.weight.dtype
+            and x.dtype in (torch.float32, torch.bfloat16) and C % (4 if x.dtype == torch.float32 else 8) == 0):
+        return LinearCL.apply(x, module.weight, module.bias)
+    return module(x)
+
+
 def pointwise_in(x, weight, bias):
     """Channels-last ``Linear`` over the few channels of an NCHW image: x [N,Cin,H,W] (Cin <= 4),
     weight [Cout,Cin], bias [Cout] or None -> [N,H,W,Cout] (models/convnext.py:143,170-176 in one

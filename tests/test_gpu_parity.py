@@ -722,6 +722,31 @@ def test_layernorm_channels_last_backward(C, rows, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("rows,C", [((3, 5, 7), 64), ((2, 56, 56), 384), ((64, 14, 14), 2048), ((1, 1, 1), 8),
+                                    ((5, 7, 7), 4096), ((2, 9), 1000)])
+def test_colsum_and_linear_bias_gradient(rows, C, dtype):
+    """o1d_colsum against a float64 sum, and the Linear wrapper's three gradients against
+    autograd's on the same inputs."""
+    g = torch.Generator(device="cpu").manual_seed(C + rows[0])
+    dy = torch.randn(rows + (C,), generator=g).to(DEV).to(dtype)
+    s = o1d.ops.colsum(dy)
+    ref = dy.double().reshape(-1, C).sum(0)
+    assert float((s.double() - ref).abs().max()) <= 1e-5 * float(ref.abs().max().clamp_min(1.0)) * (dy.numel() // C) ** 0.5
+    assert torch.equal(s, o1d.ops.colsum(dy))                         # fixed order
+    cin = 24
+    lin = torch.nn.Linear(cin, C).to(DEV).to(dtype)
+    x = torch.randn(rows + (cin,), generator=g).to(DEV).to(dtype)
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    o1d.ops.linear_cl(lin, xa).backward(dy)
+    ga = [xa.grad.clone(), lin.weight.grad.clone(), lin.bias.grad.clone()]
+    lin.zero_grad()
+    lin(xb).backward(dy)
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -6
+    for a, b in zip(ga, [xb.grad, lin.weight.grad, lin.bias.grad]):
+        assert float((a.double() - b.double()).abs().max()) <= tol * float(b.double().abs().max().clamp_min(1e-6))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 @pytest.mark.parametrize("cin,cout", [(3, 64), (1, 8), (4, 96)])
 def test_pointwise_in(dtype, cin, cout):
     """Stem input projection (NCHW image -> channels-last, Linear over the input channels)
