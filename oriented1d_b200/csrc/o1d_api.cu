@@ -337,12 +337,15 @@ int try_wline(const void *x, const float *w, const float *bias, const PlanHeader
 // Forward / stride-1 input gradient through the walker kernels (square fp32 NHWC maps, canonical lines).
 int try_walk(const void *x, const float *w, const float *bias, const PlanHeader &ph, const void *plan_host,
              const void *plan_dev, void *y, int N, int H, int W, int C, int K, int stride, int layout, int dtype,
-             int add_identity, int flip, cudaStream_t st, const DeviceInfo &d) {
+             int add_identity, int flip, cudaStream_t st, const DeviceInfo &d, bool faster_only) {
     if (g_force_generic || !ph.all_canon || ph.chan_off == 0) return kNotTiled;
     const int esize = dtype == O1D_F32 ? 4 : 2;
     const int8_t *chan_host = reinterpret_cast<const int8_t *>(static_cast<const char *>(plan_host) + ph.chan_off);
     WalkConfig cfg;
     if (!walk_configure(chan_host, N, H, W, C, K, stride, layout, esize, d.smem_optin, d.sms, &cfg)) return kNotTiled;
+    // Automatic route: only where it is the faster family - 56x56 layers without slanted channels
+    // (rows, columns, diagonals in any mix: 138-153 us against 161-183 us for the tiled kernels, batch 128).
+    if (faster_only && !(cfg.line_only && cfg.L == 56)) return kNotTiled;
     if (((uintptr_t)y & 15) != 0) return kNotTiled;
     const cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
     const cuuint64_t strides[3] = {(cuuint64_t)C * esize, (cuuint64_t)W * C * esize, (cuuint64_t)H * W * C * esize};
@@ -373,9 +376,9 @@ int route_forward(const void *x, const float *w, const float *bias, const PlanHe
     if (act || pre)       // activation on load / its derivative on store: tiled kernels, else general
         return try_tiled(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity,
                          flip, act, pre, st, d);
-    if (g_prefer == 5) {                    // items computed in place in their NHWC layout
+    if (g_prefer == 0 || g_prefer == 5) {   // items computed in place in their NHWC layout
         rc = try_walk(x, w, bias, ph, plan_host, plan_dev, y, N, H, W, C, K, stride, layout, dtype, add_identity, flip,
-                      st, d);
+                      st, d, /*faster_only=*/g_prefer == 0);
         if (rc != kNotTiled) return rc;
     }
     if (g_prefer == 0 || g_prefer == 4) {   // stage maps with whole lines per thread

@@ -12,8 +12,11 @@ bool walk_configure(const int8_t *chan, int N, int H, int W, int C, int K, int s
         return false;
     const int L = H;
     if (L != 28 && L != 56) return false;      // whole segments of kSeg columns, at most 32 row pairs
-    for (int c = 0; c < C; c++)
+    cfg->line_only = 1;
+    for (int c = 0; c < C; c++) {
         if (chan[c] < 0 || chan[c] > 7) return false;
+        if (chan[c] & 1) cfg->line_only = 0;
+    }
     const int P = L | 1;
     const int nbands = (L + walk::kBandRows - 1) / walk::kBandRows;
     if (nbands > walk::kMaxBands) return false;

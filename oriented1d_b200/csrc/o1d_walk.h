@@ -14,6 +14,7 @@ struct WalkConfig {
     int off_plane, off_wts, off_misc, plane_words;
     int smem_bytes, grid;
     int box_c, box_w, box_rows;     // TMA box: box_c channels x box_w pixels x box_rows rows x 1 image
+    int line_only;                  // no slanted channel in the layer (rows, columns and diagonals only)
 };
 
 // Does the walker family take this request?  `chan` is the host copy of the plan's table of

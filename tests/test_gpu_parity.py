@@ -431,6 +431,28 @@ def test_walker_kernels(oracle, mode, K, N, C, hw):
     assert o1d.ops.device_status() == 0
 
 
+def test_line_only_layers_take_the_walker_route(oracle):
+    """A 56x56 fp32 layer whose channels are all rows, columns or diagonals (no slanted line) is served
+    by the walker family on the automatic route (the reference module's default, angle = 0, is such a
+    layer, dwoconv1d.py:93-107); results against the oracle, forward and input gradient."""
+    C, hw, K, N = 32, 56, 31, 2
+    x, w, dy = make_inputs(77, N, C, hw, hw, K)
+    th = np.asarray([(i % 4) * np.pi / 4 for i in range(C)], np.float32)
+    plan = o1d.Plan(th, K)
+    wd = torch.from_numpy(w).to(DEV)
+    y = o1d.fprop(_to_dev(x, True), wd, None, plan, 1, True)
+    assert o1d.ops.last_route() == "walk"
+    dx = o1d.dgrad(_to_dev(dy, True), wd, plan, hw, hw, 1, True)
+    assert o1d.ops.last_route() == "walk"
+    assert rel_err(_to_nchw(y, True), oracle.fprop(x, w, th, 1)) <= TOL_FPROP
+    assert rel_err(_to_nchw(dx, True), oracle.dgrad(dy, w, th, 1)) <= TOL_DGRAD
+    # a slanted channel anywhere in the layer keeps the tiled kernels
+    th2 = th.copy(); th2[5] = np.float32(np.pi / 8)
+    o1d.fprop(_to_dev(x, True), wd, None, o1d.Plan(th2, K), 1, True)
+    assert o1d.ops.last_route() == "tiled"
+    assert o1d.ops.device_status() == 0
+
+
 def test_walker_kernels_full_batch():
     """Batch 128 through the walker family: every CTA streams about ten items through its two tiles;
     bit-equal to the same images run two at a time, and equal to the tiled kernels up to rounding."""
