@@ -623,7 +623,8 @@ def run_case(args):
         bias = torch.randn((C,), generator=g).to(dev)
         sets = [(torch.randn((n, H, W, C), generator=g).to(dev).to(dtype),
                  torch.randn((n, P, Q, C), generator=g).to(dev).to(dtype)) for _ in range(2)]
-        alg = (n * H * W * C + n * P * Q * C) * es if op not in ("ln", "tr") else 2 * n * H * W * C * es
+        alg = ((n * H * W * C + n * P * Q * C) * es if op not in ("ln", "tr", "lnbwd", "colsum") else
+               3 * n * H * W * C * es if op == "lnbwd" else n * H * W * C * es if op == "colsum" else 2 * n * H * W * C * es)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     times = []
@@ -638,6 +639,10 @@ def run_case(args):
             o1d.wgrad(dy, x, plan, stride, True, True)
         elif op == "ln":
             o1d.ops.layer_norm_cl(x, bias, bias, 1e-6, False)
+        elif op == "lnbwd":
+            o1d.ops.layer_norm_cl_bwd(x, dy, bias, 1e-6)
+        elif op == "colsum":
+            o1d.ops.colsum(dy)
         elif op == "pw":
             o1d.ops.pointwise_in(x, w, bias)
         elif op == "tr":

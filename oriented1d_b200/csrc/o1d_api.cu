@@ -1002,21 +1002,45 @@ int o1d_layernorm_cl_bwd(const void *x, const void *dy, const float *gamma, cons
                                                              rows, C, eps, gelu, st, d);
 }
 
+extern "C++" {
 namespace {
+// rows a CTA reads per pass (1, 2, 4, 8 or 16): narrow matrices give every lane a vector
+int colsum_row_lanes(int nvec) {
+    int rl = 1;
+    while (rl < 16 && nvec * rl * 2 <= kColsumThreads) rl *= 2;
+    return rl;
+}
 int colsum_slices(long long rows, int C, int ve, int sms) {
-    const int col_blocks = ceil_div(C / ve, kColsumThreads);
-    long long s = ((long long)sms * 2 + col_blocks - 1) / col_blocks;      // about two CTAs per SM in all
-    if (s > (rows + 7) / 8) s = (rows + 7) / 8;                            // at least eight rows per slice
+    const int nvec = C / ve, rl = colsum_row_lanes(nvec);
+    const int col_blocks = ceil_div(nvec, kColsumThreads / rl);
+    long long s = ((long long)sms * 4 + col_blocks - 1) / col_blocks;      // about four CTAs per SM in all
+    const long long most = (rows + 8LL * rl - 1) / (8LL * rl);             // at least eight passes per slice
+    if (s > most) s = most;
     if (s > 4096) s = 4096;
     return (int)(s < 1 ? 1 : s);
 }
+template <typename T>
+void launch_colsum(const void *x, float *partial, long long rows, int C, int slices, cudaStream_t st) {
+    const int nvec = C / (16 / (int)sizeof(T)), rl = colsum_row_lanes(nvec);
+    dim3 grid(ceil_div(nvec, kColsumThreads / rl), slices);
+    switch (rl) {
+        case 1: colsum_partial_kernel<T, 1><<<grid, kColsumThreads, 0, st>>>((const T *)x, partial, rows, C); break;
+        case 2: colsum_partial_kernel<T, 2><<<grid, kColsumThreads, 0, st>>>((const T *)x, partial, rows, C); break;
+        case 4: colsum_partial_kernel<T, 4><<<grid, kColsumThreads, 0, st>>>((const T *)x, partial, rows, C); break;
+        case 8: colsum_partial_kernel<T, 8><<<grid, kColsumThreads, 0, st>>>((const T *)x, partial, rows, C); break;
+        default: colsum_partial_kernel<T, 16><<<grid, kColsumThreads, 0, st>>>((const T *)x, partial, rows, C); break;
+    }
+}
 }  // namespace
+}  // extern "C++"
 
 size_t o1d_colsum_workspace_bytes(long long rows, int C, int dtype) {
     if (rows <= 0 || C <= 0) return 0;
     DeviceInfo d;
     if (device_info(&d)) return 0;
-    return (size_t)colsum_slices(rows, C, dtype == O1D_F32 ? 4 : 8, d.sms) * (size_t)C * sizeof(float);
+    const int ve = dtype == O1D_F32 ? 4 : 8;
+    if (C % ve != 0) return 0;
+    return (size_t)colsum_slices(rows, C, ve, d.sms) * (size_t)C * sizeof(float);
 }
 
 int o1d_colsum(const void *x, float *out, void *workspace, size_t workspace_bytes, long long rows, int C, int dtype,
@@ -1030,12 +1054,8 @@ int o1d_colsum(const void *x, float *out, void *workspace, size_t workspace_byte
     const int slices = colsum_slices(rows, C, ve, d.sms);
     if (!workspace || workspace_bytes < (size_t)slices * C * sizeof(float)) return O1D_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
-    dim3 grid(ceil_div(C / ve, kColsumThreads), slices);
-    if (dtype == O1D_F32)
-        colsum_partial_kernel<float><<<grid, kColsumThreads, 0, st>>>((const float *)x, (float *)workspace, rows, C);
-    else
-        colsum_partial_kernel<__nv_bfloat16><<<grid, kColsumThreads, 0, st>>>((const __nv_bfloat16 *)x,
-                                                                             (float *)workspace, rows, C);
+    if (dtype == O1D_F32) launch_colsum<float>(x, (float *)workspace, rows, C, slices, st);
+    else launch_colsum<__nv_bfloat16>(x, (float *)workspace, rows, C, slices, st);
     O1D_CUDA(cudaGetLastError());
     colsum_final_kernel<<<ceil_div(C, 32), dim3(32, 8), 0, st>>>((const float *)workspace, out, slices, C);
     O1D_CUDA(cudaGetLastError());

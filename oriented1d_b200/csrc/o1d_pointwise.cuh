@@ -74,39 +74,60 @@ pointwise_in_kernel(const T *__restrict__ x, const float *__restrict__ w, const 
 // (layernorm_cl_bwd_final_kernel's pattern, here colsum_final_kernel) adds the row slices in a fixed
 // order.  Every load is a full 16-byte vector of a contiguous 4 KB row segment.
 constexpr int kColsumThreads = 256;
-template <typename T>
+// RL = rows a CTA reads per pass = 256 / (vectors per row rounded up to a power of two), so that narrow
+// matrices still use every lane; the RL row lanes of a column are added in lane order through shared memory.
+template <typename T, int RL>
 __global__ void __launch_bounds__(kColsumThreads)
 colsum_partial_kernel(const T *__restrict__ x, float *__restrict__ partial, int64_t rows, int C) {
-    constexpr int VE = 16 / (int)sizeof(T);
-    const int vec = blockIdx.x * kColsumThreads + threadIdx.x, nvec = C / VE;
-    if (vec >= nvec) return;
+    constexpr int VE = 16 / (int)sizeof(T), VPB = kColsumThreads / RL;       // vectors of a row per CTA
+    __shared__ float red[RL > 1 ? kColsumThreads * VE : 1];
+    const int vl = threadIdx.x % VPB, rl = threadIdx.x / VPB;
+    const int vec = blockIdx.x * VPB + vl, nvec = C / VE;
+    const bool act = vec < nvec;
     float acc[VE];
 #pragma unroll
     for (int j = 0; j < VE; j++) acc[j] = 0.f;
-    const T *col = x + (size_t)vec * VE;
-    int64_t r = blockIdx.y;
-    // four rows in flight per thread
-    for (; r + 3 * (int64_t)gridDim.y < rows; r += 4 * (int64_t)gridDim.y) {
-        uint4 v[4];
+    if (act) {
+        const T *col = x + (size_t)vec * VE;
+        const int64_t step = (int64_t)gridDim.y * RL;
+        int64_t r = (int64_t)blockIdx.y * RL + rl;
+        for (; r + 3 * step < rows; r += 4 * step) {         // four rows in flight per thread
+            uint4 v[4];
 #pragma unroll
-        for (int u = 0; u < 4; u++) v[u] = __ldg(reinterpret_cast<const uint4 *>(col + (r + u * (int64_t)gridDim.y) * C));
+            for (int u = 0; u < 4; u++) v[u] = __ldg(reinterpret_cast<const uint4 *>(col + (r + u * step) * C));
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < 4; u++) {
+                float f[VE];
+                GVec<T>::unpack(v[u], f);
+#pragma unroll
+                for (int j = 0; j < VE; j++) acc[j] += f[j];
+            }
+        }
+        for (; r < rows; r += step) {
             float f[VE];
-            GVec<T>::unpack(v[u], f);
+            GVec<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(col + r * C)), f);
 #pragma unroll
             for (int j = 0; j < VE; j++) acc[j] += f[j];
         }
     }
-    for (; r < rows; r += gridDim.y) {
-        float f[VE];
-        GVec<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(col + r * C)), f);
+    if (RL > 1) {
 #pragma unroll
-        for (int j = 0; j < VE; j++) acc[j] += f[j];
+        for (int j = 0; j < VE; j++) red[(rl * VE + j) * VPB + vl] = acc[j];
+        __syncthreads();
+        if (rl == 0 && act) {
+#pragma unroll
+            for (int j = 0; j < VE; j++) {
+                float s = 0.f;
+                for (int q = 0; q < RL; q++) s += red[(q * VE + j) * VPB + vl];
+                acc[j] = s;
+            }
+        }
     }
-    float *dst = partial + (size_t)blockIdx.y * C + (size_t)vec * VE;
+    if (rl == 0 && act) {
+        float *dst = partial + (size_t)blockIdx.y * C + (size_t)vec * VE;
 #pragma unroll
-    for (int j = 0; j < VE; j++) dst[j] = acc[j];
+        for (int j = 0; j < VE; j++) dst[j] = acc[j];
+    }
 }
 
 // out[c] = sum over slices (in a fixed order) of partial[slice][c].  Block (32, 8) as in the LayerNorm backward.
