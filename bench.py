@@ -855,7 +855,7 @@ def run_train(args):
     # launches per step off the host.  With several ranks the step stays eager (the all-reduce sits in it).
     static_x, static_t = torch.empty_like(imgs[0]), torch.empty_like(labels[0])
     graph, static_loss, launch = None, None, "eager"
-    if world == 1 and not args.no_graph:
+    if not args.no_graph and (world == 1 or args.graph_collective):
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
@@ -868,7 +868,7 @@ def run_train(args):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 static_loss = train_step(static_x, static_t)
-            launch = "CUDA graph of the whole step"
+            launch = "CUDA graph of the whole step" + (" (all-reduce captured)" if world > 1 else "")
         except Exception as e:                      # noqa: BLE001 - any capture failure: run eagerly
             print(f"[bench] step not captured ({type(e).__name__}: {e}); running eagerly", file=sys.stderr)
             graph = None
@@ -916,8 +916,13 @@ def run_train(args):
                     "h2d_bytes_per_step": host_img.numel() * 2 + host_lab.numel() * 8, "d2h_bytes_per_step": 4,
                     "ms_per_step": e2e_ms / n_e2e},
             "gpu_launches": 4 * n_conv * args.steps,      # fprop, dgrad, wgrad (2 kernels) per oriented conv
-            "clocks": clk.summary(), "roofline": None, "cpu_baseline": None}))
+            "clocks": clk.summary(), "roofline": None, "cpu_baseline": None}), flush=True)
     if world > 1:
+        if graph is not None:        # a graph that holds captured collectives goes before the communicator
+            torch.cuda.synchronize()
+            graph.reset()
+            graph = None
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -1030,6 +1035,8 @@ def main():
                          "4 prefer whole-line")
     ap.add_argument("--fuse-gelu", action="store_true",
                     help="train workload: apply each block's GELU inside its second oriented conv's kernels")
+    ap.add_argument("--graph-collective", action="store_true",
+                    help="train workload on several GPUs: capture the step, NCCL all-reduce included, into a CUDA graph")
     ap.add_argument("--no-model", action="store_true", help="sweep workload: skip the model figure")
     args = ap.parse_args()
     if args.route and args.impl == "ours":
