@@ -5,18 +5,18 @@
 // (image n, 8 consecutive channels) exactly as it lies in global memory: [rows][P pixels][8 ch],
 // P = L+1 (the extra column is outside the tensor and arrives as zeros; an odd pitch spreads
 // vertical neighbours over the banks).  A producer warp moves items with TMA: tile t is loaded
-// band by band (8 rows per copy), computed IN PLACE by eight compute warps, and stored back band by
+// band by band (8 rows per copy), computed IN PLACE by eleven compute warps, and stored back band by
 // band with TMA stores; the next item's bands are loaded into the tile as soon as the store of the
 // same band has read it.  While one tile computes, the other one drains and refills, so the HBM
 // traffic of one item hides behind the arithmetic of its neighbour.
 //
 // Arithmetic, per channel, by line kind (o1d_lines.cuh):
 //   * axis (0, 90 degrees) and diagonal (45, 135) channels: a thread walks one image line (row,
-//     column or wrapped diagonal) pixel by pixel with the 31 most recent inputs in registers (the
-//     window rotates through an unrolled body of 31 steps), so a step costs one shared-memory load,
-//     one store and 31 FMAs.  The result of position i overwrites cell i of the tile: that cell
-//     belongs to this line of this channel alone and was read into the window 16 steps earlier.
-//     A warp holds (line channels of the chunk) x (32 / that many) lines; the weights are per lane.
+//     column or diagonal) with the last 38 inputs in registers; per round it loads 8 new inputs,
+//     forms 8 outputs of 31 FMAs each and shifts the window by 8 registers.  The result of position
+//     i overwrites cell i of the tile: that cell belongs to this line of this channel alone and was
+//     read into the window 16 positions earlier.  A warp holds (channels of one kind in the chunk) x
+//     (32 / that many) lines; the weights are per lane; tasks are handed out from a shared counter.
 //   * slanted channels (22.5, 67.5, 112.5, 157.5 degrees): the channel's plane is first copied out
 //     of the tile into a small fp32 plane in the canonical frame of the 22.5 degree line (transposed
 //     and/or mirrored as o1d_lines.cuh prescribes) with zero rows and columns around it; a thread
